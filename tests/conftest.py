@@ -1,0 +1,32 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
+
+
+@pytest.fixture(scope="session")
+def oracle_port():
+    from oracle import oracle
+    oracle.build(ref=False)
+    return oracle.get("port")
+
+
+@pytest.fixture(scope="session")
+def oracle_ref():
+    from oracle import oracle
+    if not oracle.have_ref():
+        try:
+            oracle.build(ref=True)
+        except Exception:
+            pass
+    if not oracle.have_ref():
+        pytest.skip("reference CPU functors not built (no reference tree and no prebuilt library)")
+    return oracle.get("ref")
