@@ -1,0 +1,445 @@
+#!/usr/bin/env python
+"""Benchmark of the block-op hot path: reduce_mask -> sparse_gather -> sparse_scatter_var.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--occupancy 0.1] [--scaling weak|strong] [--suite ops]
+
+Workload (one "step" = one pass of the three ops over one batch): the sparse ResNet-bottleneck
+configuration -- x fp16 [32,400,352,256], a rectangle-union mask, 18x18 windows on a 16 pixel pitch
+with a one pixel halo: reduce_mask (max, tol 0.5) -> sparse_gather(transpose=True) ->
+sparse_scatter_var(add=True, transpose=True, 16x16 interior) of a conv-output-shaped stack back onto
+x.  The dense convolutions between gather and scatter belong to the host framework and are not part
+of this library, so they are not in the step.  Data is synthetic and seeded (sbnet_b200/configs.py).
+
+One JSON line is printed by rank 0.  `value` is blocks/s over all ranks with inputs resident in HBM;
+`e2e` is the same pipeline fed from pinned host buffers with the copies inside the timed region;
+`roofline` describes the kernel that takes the largest share of the step; `cpu_baseline` is the
+reference's CPU functors timed on this machine's cores on a bounded sample.
+
+`--impl reference` times the reference's own CPU implementation (oracle/_ref when it was compiled
+from the reference tree, else the C restatement) on bounded samples of the same workload.
+`--suite ops` prints one JSON line per op-level configuration (mask / gather / scatter sizes of the
+other benchmark configurations) instead of the pipeline line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from sbnet_b200 import configs as cfg  # noqa: E402
+
+FALLBACK_HBM_GBS = 6650.0
+L2_BYTES = 126 * 1024 * 1024
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+                for nm, v in zip(names, r[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(nm)
+            except Exception:
+                continue
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---- workload ------------------------------------------------------------------------------------
+
+def pipeline_shapes(args, world):
+    N = args.batch if args.scaling == "weak" else max(args.batch // world, 1)
+    return N, args.height, args.width, args.channels
+
+
+def make_host_inputs(args, rank, world):
+    """Seeded host-side inputs of one rank (numpy)."""
+    N, H, W, C = pipeline_shapes(args, world)
+    seed = 1000 * rank + 7
+    mask = cfg.rect_union_mask(N, H, W, seed=seed, occupancy=args.occupancy)
+    return N, H, W, C, mask
+
+
+def union_stats(mask, g_in, g_out, N, H, W):
+    """Active blocks and distinct covered pixels (for the algorithmic-byte formulas), on the CPU."""
+    m = mask[..., 0] > 0.5
+    bch, bcw = g_in.bcount
+    act = np.zeros((N, bch, bcw), dtype=bool)
+    for bh in range(bch):
+        h0 = g_in.boffset[0] + bh * g_in.bstride[0]
+        rows = m[:, max(h0, 0):min(h0 + g_in.bsize[0], H), :]
+        for bw in range(bcw):
+            w0 = g_in.boffset[1] + bw * g_in.bstride[1]
+            act[:, bh, bw] = rows[:, :, max(w0, 0):min(w0 + g_in.bsize[1], W)].any(axis=(1, 2))
+    nB = int(act.sum())
+    idx = np.argwhere(act).astype(np.int16)
+    U_in = cfg.union_pixels(idx, nB, g_in, N, H, W)
+    U_out = cfg.union_pixels(idx, nB, g_out, N, H, W)
+    return nB, U_in, U_out, idx
+
+
+# ---- our arm -------------------------------------------------------------------------------------
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from sbnet_b200 import build, lib, ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path in the product)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if rank == 0:
+        build.build_library()
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        dist.barrier()
+    lib.load()
+
+    N, H, W, C, mask_h = make_host_inputs(args, rank, world)
+    g_in, g_out = cfg.halo_geom(H, W), cfg.inner_geom(H, W)
+    nB, U_in, U_out, _ = union_stats(mask_h, g_in, g_out, N, H, W)
+    sz = 2
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    x = torch.empty((N, H, W, C), dtype=torch.float16, device=dev)
+    for n in range(N):  # generated in slices: a one-shot fp32 randn of this size would double the footprint
+        x[n] = torch.randn((H, W, C), generator=gen, device=dev, dtype=torch.float32).half()
+    # conv-output-shaped stack [nB,C,16,16]; small magnitudes so K accumulations stay far from fp16 max
+    q = (torch.randn((nB, C, 16, 16), generator=gen, device=dev, dtype=torch.float32) * 0.01).half()
+    stack = torch.empty((nB, C, 18, 18), dtype=torch.float16, device=dev)
+    # masks rotate through enough copies to exceed L2 on their own
+    n_masks = max(2, int(L2_BYTES // mask_h.nbytes) + 2)
+    masks = [torch.from_numpy(mask_h).to(dev) for _ in range(min(n_masks, 8))]
+    torch.cuda.synchronize()
+
+    bytes_mask = cfg.algorithmic_bytes("reduce_mask", nB=nB, geom=g_in, C=1, itemsize=4, U=0, N=N,
+                                       H=H, W=W, count=nB)
+    bytes_gather = cfg.algorithmic_bytes("gather", nB=nB, geom=g_in, C=C, itemsize=sz, U=U_in)
+    bytes_scatter = cfg.algorithmic_bytes("scatter_add", nB=nB, geom=g_out, C=C, itemsize=sz, U=U_out)
+
+    counts_all = torch.zeros(world, dtype=torch.int32, device=dev)
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+
+    def step(i, marks=None):
+        m = masks[i % len(masks)]
+        if marks is not None:
+            marks[0].record()
+        idx, cnt = ops.reduce_mask(m, *g_in.as_lists(), tol=0.5, avgpool=False)
+        if marks is not None:
+            marks[1].record()
+        work = None
+        if world > 1:  # the only exchange of the path: every rank's block count
+            work = dist.all_gather_into_tensor(counts_all, ops.scratch_for(dev, torch.cuda.current_stream(dev).cuda_stream)[0][:1],
+                                               async_op=True)
+        nb = int(cnt[0])
+        assert nb == nB, (nb, nB)
+        if marks is not None:
+            marks[2].record()
+        ops.sparse_gather(x, cnt, idx, g_in.bsize, g_in.bstride, g_in.boffset, transpose=True, out=stack)
+        if marks is not None:
+            marks[3].record()
+        ops.sparse_scatter_var(q, cnt, idx, x, g_out.bsize, g_out.bstride, g_out.boffset, add=True,
+                               transpose=True)
+        if marks is not None:
+            marks[4].record()
+        if work is not None:
+            work.wait()
+        return nb
+
+    def fence():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    fence()
+    marks = [[ev() for _ in range(5)] for _ in range(args.steps)]
+    t0, t1 = ev(), ev()
+    with ClockSampler(local) as clocks:
+        fence()
+        t0.record()
+        blocks = 0
+        for i in range(args.steps):
+            blocks += step(args.warmup + i, marks[i])
+        t1.record()
+        fence()
+    ms_total = t0.elapsed_time(t1)
+    op_ms = {"reduce_mask": [], "gather": [], "scatter": []}
+    for mk in marks:
+        op_ms["reduce_mask"].append(mk[0].elapsed_time(mk[1]))
+        op_ms["gather"].append(mk[2].elapsed_time(mk[3]))
+        op_ms["scatter"].append(mk[3].elapsed_time(mk[4]))
+
+    # ---- end to end: host buffers in, host result out, copies inside the timed region ----
+    e2e = None
+    if not args.no_e2e:
+        e2e_steps = max(1, min(args.steps, args.e2e_steps))
+        hx = torch.empty((N, H, W, C), dtype=torch.float16, pin_memory=True)
+        hx.copy_(x)
+        hq = torch.empty(q.shape, dtype=torch.float16, pin_memory=True)
+        hq.copy_(q)
+        hm = torch.from_numpy(mask_h).pin_memory()
+        hy = torch.empty((N, H, W, C), dtype=torch.float16, pin_memory=True)
+        dm = masks[0]
+        fence()
+
+        def e2e_step():
+            dm.copy_(hm, non_blocking=True)
+            x.copy_(hx, non_blocking=True)
+            q.copy_(hq, non_blocking=True)
+            idx, cnt = ops.reduce_mask(dm, *g_in.as_lists(), tol=0.5, avgpool=False)
+            ops.sparse_gather(x, cnt, idx, g_in.bsize, g_in.bstride, g_in.boffset, transpose=True, out=stack)
+            ops.sparse_scatter_var(q, cnt, idx, x, g_out.bsize, g_out.bstride, g_out.boffset, add=True,
+                                   transpose=True)
+            hy.copy_(x, non_blocking=True)
+            return int(cnt[0])
+
+        e2e_step()
+        fence()
+        a, b = ev(), ev()
+        a.record()
+        eb = 0
+        for _ in range(e2e_steps):
+            eb += e2e_step()
+        b.record()
+        fence()
+        e2e_ms = a.elapsed_time(b)
+        e2e = dict(ms=e2e_ms, blocks=eb, steps=e2e_steps,
+                   h2d=hx.numel() * 2 + hq.numel() * 2 + hm.numel() * 4, d2h=hy.numel() * 2)
+        del hx, hq, hy
+
+    # ---- reduce over ranks: max time, summed blocks ----
+    stats = torch.tensor([ms_total, e2e["ms"] if e2e else 0.0], dtype=torch.float64, device=dev)
+    sums = torch.tensor([blocks, e2e["blocks"] if e2e else 0], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+    ms_total, e2e_ms = stats.tolist()
+    blocks_all, e2e_blocks_all = sums.tolist()
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        med = {k: statistics.median(v) for k, v in op_ms.items()}
+        alg = {"reduce_mask": bytes_mask, "gather": bytes_gather, "scatter": bytes_scatter}
+        gbs = {k: alg[k] / (med[k] * 1e-3) / 1e9 for k in med}
+        dom = max(("gather", "scatter"), key=lambda k: med[k])
+        kernel_name = {"gather": "planes_kernel<gather,f16> (sparse_gather transpose=True)",
+                       "scatter": "planes_kernel<scatter_add,f16> (sparse_scatter_var add=True transpose=True)"}[dom]
+        line = {
+            "metric": "sparse block pipeline throughput (reduce_mask -> sparse_gather -> sparse_scatter_var)",
+            "value": blocks_all / (ms_total * 1e-3),
+            "unit": "blocks/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_total / args.steps,
+            "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic",
+            "config": {
+                "workload": "sparse ResNet bottleneck block ops, batch-sharded (BASELINE config 5 without the framework's convs)",
+                "x": [N, H, W, C], "per_rank_batch": N, "global_batch": N * world,
+                "mask": f"rectangle union, {args.occupancy:.0%} pixel occupancy",
+                "bsize": [18, 18], "bstride": [16, 16], "boffset": [-1, -1],
+                "active_blocks_per_rank": nB, "candidate_blocks_per_rank": N * g_in.bcount[0] * g_in.bcount[1],
+                "l2": "x (2.3 GB per rank) exceeds L2; masks rotate through copies and are evicted by the x traffic between uses",
+                "parallelism": f"dp{world}",
+            },
+            "ops": {k: {"us": med[k] * 1e3, "algorithmic_bytes": alg[k], "GB/s": gbs[k],
+                        "frac_of_" + peak_kind: gbs[k] / peak} for k in med},
+            "roofline": {"bound": "hbm", "kernel": kernel_name, "achieved": gbs[dom], "peak": peak,
+                         "peak_source": peak_kind, "unit": "GB/s", "frac": gbs[dom] / peak,
+                         "traffic": None},
+            "gpu_launches": 3 * args.steps,
+            "clocks": clocks.summary(),
+        }
+        if e2e:
+            line["e2e"] = {"value": e2e_blocks_all / (e2e_ms * 1e-3), "unit": "blocks/s",
+                           "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                           "steps": e2e["steps"], "ms_per_step": e2e_ms / e2e["steps"]}
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_pipeline(args, mask_h, N, H, W, C, budget_s=args.cpu_budget)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# ---- CPU legs ------------------------------------------------------------------------------------
+
+def cpu_pipeline(args, mask_h, N, H, W, C, budget_s=12.0, steps=1):
+    """Times the reference CPU functors on a bounded sample: the first image(s) of the batch for
+    reduce_mask and the first M active blocks for gather / scatter-add, M grown until one pass takes
+    a few seconds.  blocks/s = M / (t_mask * M/nB_image + t_gather + t_scatter)."""
+    from oracle import oracle
+    kind = "ref" if oracle.have_ref() else "port"
+    if kind == "port":
+        oracle.build(ref=False)
+    o = oracle.get(kind)
+    cores = o.max_threads()
+    o.set_threads(cores)
+    g_in, g_out = cfg.halo_geom(H, W), cfg.inner_geom(H, W)
+    m1 = np.ascontiguousarray(mask_h[:1])
+    t = time.perf_counter()
+    idx, cnt = o.reduce_mask(m1, *g_in.as_lists(), tol=0.5, avgpool=False)
+    t_mask = time.perf_counter() - t
+    nb_img = int(cnt[0])
+    x1 = cfg.normal((1, H, W, C), 5, np.float16)
+    M, per_block = min(8, nb_img), None
+    spent = 0.0
+    res = None
+    while True:
+        c = np.array([M], dtype=np.int32)
+        t = time.perf_counter()
+        st = o.sparse_gather(x1, c, idx, g_in.bsize, g_in.bstride, g_in.boffset, transpose=True)
+        t_g = time.perf_counter() - t
+        qh = np.ascontiguousarray(st[:, :, 1:17, 1:17])
+        t = time.perf_counter()
+        o.sparse_scatter_var(qh, c, idx, x1, g_out.bsize, g_out.bstride, g_out.boffset, add=True,
+                             transpose=True)
+        t_s = time.perf_counter() - t
+        spent += t_g + t_s
+        res = (M, t_g, t_s)
+        per_block = (t_g + t_s) / M
+        nxt = min(nb_img, int(M * 4))
+        if nxt == M or spent + per_block * nxt > budget_s:
+            break
+        M = nxt
+    M, t_g, t_s = res
+    total = t_mask * (M / max(nb_img, 1)) + t_g + t_s
+    return {"value": M / total, "unit": "blocks/s", "cores": cores,
+            "kind": "reference" if kind == "ref" else "port",
+            "sample": f"image 0 of the batch: reduce_mask on 1 image ({t_mask*1e3:.1f} ms, single thread), "
+                      f"gather+scatter-add on its first {M} of {nb_img} active blocks "
+                      f"({t_g:.2f} s + {t_s:.2f} s)",
+            "us_per_block": {"gather": t_g / M * 1e6, "scatter_add": t_s / M * 1e6}}
+
+
+def run_reference(args):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    N, H, W, C, mask_h = make_host_inputs(args, 0, world)
+    vals = []
+    base = None
+    t_all = time.perf_counter()
+    for _ in range(args.warmup + args.steps):
+        base = cpu_pipeline(args, mask_h, N, H, W, C, budget_s=args.cpu_budget / 2)
+        vals.append(base["value"])
+        if time.perf_counter() - t_all > 150:
+            break
+    timed = vals[min(args.warmup, len(vals) - 1):]
+    value = statistics.median(timed)
+    base["value"] = value
+    g_in = cfg.halo_geom(H, W)
+    line = {
+        "impl": "reference",
+        "metric": "sparse block pipeline throughput (reduce_mask -> sparse_gather -> sparse_scatter_var)",
+        "value": value, "unit": "blocks/s", "n_gpus": world, "steps": len(timed),
+        "warmup": min(args.warmup, len(vals) - 1), "ms_per_step": None, "higher_is_better": True,
+        "scaling": args.scaling, "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "sparse ResNet bottleneck block ops (BASELINE config 5 without the framework's convs), CPU functors on a bounded sample",
+                   "x": [N, H, W, C], "mask": f"rectangle union, {args.occupancy:.0%} pixel occupancy",
+                   "bsize": [18, 18], "bstride": [16, 16], "boffset": [-1, -1],
+                   "candidate_blocks_per_rank": N * g_in.bcount[0] * g_in.bcount[1]},
+        "cpu_baseline": base,
+        "e2e": {"value": value, "unit": "blocks/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--occupancy", type=float, default=0.10)
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--height", type=int, default=400)
+    ap.add_argument("--width", type=int, default=352)
+    ap.add_argument("--channels", type=int, default=256)
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--cpu-budget", type=float, default=12.0)
+    ap.add_argument("--suite", choices=["ops"], default=None)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.suite == "ops":
+        from sbnet_b200 import opbench
+        opbench.main(args)
+    elif args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,145 @@
+/*
+ * sbnet_b200 -- C ABI of the B200 (sm_100a) implementation of SBNet's block ops.
+ *
+ * Every entry point replaces one seam of the reference library (paths below are relative to
+ * sbnet_tensorflow/sbnet_ops/ of uber-research/sbnet).  A TensorFlow OpKernel (or any other host)
+ * calls these with raw device pointers exactly where the reference's Compute() methods call their
+ * functors; see INTEGRATION.md for the binding.
+ *
+ * Conventions
+ *  - All tensor pointers are DEVICE pointers unless a parameter says "host".  The caller owns every
+ *    buffer; the library allocates nothing.
+ *  - Geometry is passed as in the reference functors: offsets may be negative, strides may be
+ *    smaller (overlap) or larger (gaps) than sizes, blocks may hang over any image border.
+ *  - `stream` is a cudaStream_t passed as void*.  Work is enqueued on it; only sbnet_reduce_mask with
+ *    a non-NULL count_host waits for it.
+ *  - Return value: 0 = success; negative = SBNET_ERR_* (the argument was rejected, nothing was
+ *    launched; sbnet_last_error() has the text); positive = a cudaError_t from the CUDA runtime.
+ *    The library never terminates the process (the reference calls exit(), op_utils.h:27-37).
+ *  - Re-entrant: no global mutable state; calls on different streams may run concurrently as long
+ *    as they do not share scratch or output buffers.
+ */
+#ifndef SBNET_B200_H
+#define SBNET_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SBNET_OK 0
+#define SBNET_ERR_INVALID_ARGUMENT (-1) /* maps to tensorflow::errors::InvalidArgument */
+#define SBNET_ERR_UNSUPPORTED (-2)      /* valid but outside what the kernels index (>= 2^31 items) */
+
+/* element types of x / y / block stacks */
+#define SBNET_F32 0
+#define SBNET_F16 1 /* extension: the reference registers T = float only (sparse_gather.cc:49) */
+
+/* sbnet_reduce_mask flags */
+#define SBNET_SCRATCH_CLEAN 1 /* scratch[1..2] are already zero (see below): skip the memset */
+
+/* int32 words of device scratch sbnet_reduce_mask needs */
+#define SBNET_REDUCE_MASK_SCRATCH_INTS 4
+
+int sbnet_version(void);
+
+/* Text of the last SBNET_ERR_* returned on the calling thread ("" if none). */
+const char* sbnet_last_error(void);
+
+/*
+ * ReduceMask -- replaces ReduceMaskFunctor<GPUDevice,T>::operator() (reduce_mask.h:23-44, launcher
+ * reduce_mask.cu:39-88, kernels reduce_mask.cu.h:54-188 and zero_block_counters.cu.h:26-51) plus the
+ * count read-back and empty-mask rule of ReduceMaskOp::Compute (reduce_mask.cc:198-220).
+ *
+ *   mask                  [N,H,W] (or [N,H,W,1]) fp32
+ *   tol, avgpool          op attrs: a block is active if any pixel > tol (max) or
+ *                         sum(in-range pixels)/(bSzH*bSzW) > tol (avg)
+ *   active_block_indices  [N*bCntH*bCntW, 3] int16 (n, bh, bw); the first count rows are written,
+ *                         in arbitrary order
+ *   scratch_dev           SBNET_REDUCE_MASK_SCRATCH_INTS int32.  On return (stream order)
+ *                         scratch_dev[0] holds the published count, which device-side consumers
+ *                         (the *_dyn entry points) may read without a host round trip;
+ *                         scratch_dev[1..2] are internal and are left at zero.  Pass
+ *                         SBNET_SCRATCH_CLEAN in `flags` when the buffer was zero-filled once and has
+ *                         since only been used by stream-ordered calls of this function; otherwise
+ *                         the library clears it with a cudaMemsetAsync first.
+ *   count_host            host int32 (the op's bin_counts output, reduce_mask.cc:198-220) or NULL.
+ *                         When given, the call synchronises `stream` and stores the count.  Pinned
+ *                         host memory is written directly by the kernel; pageable memory costs an
+ *                         extra copy.  An empty result is reported as ONE block with index (0,0,0),
+ *                         as the reference does.
+ */
+int sbnet_reduce_mask(const float* mask, int N, int H, int W, float tol, int avgpool,
+                      int bOffsH, int bOffsW, int bSzH, int bSzW, int bStrH, int bStrW,
+                      int bCntH, int bCntW, int16_t* active_block_indices, int32_t* scratch_dev,
+                      int32_t* count_host, int flags, void* stream);
+
+/*
+ * SparseGather -- replaces SparseGatherFunctor<GPUDevice,T>::operator() (sparse_gather.h:23-41,
+ * launcher sparse_gather.cu:62-154, kernels sparse_blocks.cu.h:68-172,292-347).
+ *
+ *   x  [N,H,W,C] NHWC;  y  [numActive,bSzH,bSzW,C], or [numActive,C,bSzH,bSzW] when transpose != 0.
+ *   Pixels outside the image read as zero.  numActive == 0 is a successful no-op.
+ */
+int sbnet_sparse_gather(const void* x, int dtype, int N, int H, int W, int C, void* y,
+                        int bOffsH, int bOffsW, int bSzH, int bSzW, int bStrH, int bStrW,
+                        int numActive, const int16_t* active_block_indices, int transpose,
+                        void* stream);
+
+/*
+ * SparseScatter / SparseScatterVar -- replaces SparseScatterFunctor<GPUDevice,T>::operator()
+ * (sparse_gather.h:43-65, launcher sparse_gather.cu:158-266, kernels sparse_blocks.cu.h:174-289,
+ * 309-366) and the argument rule of SparseScatterOp::Compute (sparse_gather.cc:322-326).
+ *
+ *   x  block stack ([numActive,bSzH,bSzW,C] or transposed [numActive,C,bSzH,bSzW]);
+ *   y  [N,H,W,C], updated in place: y = x (add == 0), y += x (add != 0).  Pixels outside the image
+ *   are dropped.  add != 0 with atomic == 0 requires disjoint blocks (bStr >= bSz in both
+ *   dimensions) and is rejected with SBNET_ERR_INVALID_ARGUMENT otherwise; atomic != 0 uses vector
+ *   reductions and accepts any overlap.  With add == 0 and overlapping blocks the surviving value
+ *   of a shared pixel is whichever block wrote last (as in the reference).
+ *   The non-Var op is sbnet_copy_tensor(y, ybase) followed by this call on the same stream.
+ */
+int sbnet_sparse_scatter(const void* x, int dtype, int N, int H, int W, int C, void* y,
+                         int bOffsH, int bOffsW, int bSzH, int bSzW, int bStrH, int bStrW,
+                         int numActive, const int16_t* active_block_indices, int add,
+                         int transpose, int atomic, void* stream);
+
+/*
+ * Device-count variants (no counterpart in the reference, whose op interface forces a host read of
+ * bin_counts between reduce_mask and gather, reduce_mask.cc:204 / sparse_gather.cc:190-192):
+ * the number of blocks is read on the device from *num_active_dev (e.g. scratch_dev of
+ * sbnet_reduce_mask) and clamped to maxActive, so mask -> gather -> scatter can be enqueued without
+ * a host synchronisation.  Buffers must be sized for maxActive blocks.
+ */
+int sbnet_sparse_gather_dyn(const void* x, int dtype, int N, int H, int W, int C, void* y,
+                            int bOffsH, int bOffsW, int bSzH, int bSzW, int bStrH, int bStrW,
+                            int maxActive, const int32_t* num_active_dev,
+                            const int16_t* active_block_indices, int transpose, void* stream);
+int sbnet_sparse_scatter_dyn(const void* x, int dtype, int N, int H, int W, int C, void* y,
+                             int bOffsH, int bOffsW, int bSzH, int bSzW, int bStrH, int bStrW,
+                             int maxActive, const int32_t* num_active_dev,
+                             const int16_t* active_block_indices, int add, int transpose,
+                             int atomic, void* stream);
+
+/*
+ * CopyTensor -- replaces CopyTensorFunctor<GPUDevice,T>::operator() (sparse_gather.h:68-76,
+ * sparse_gather.cu:268-276): dst[0..bytes) = src[0..bytes), stream ordered, WITHOUT the
+ * reference's cudaStreamSynchronize.  The size is in bytes (the reference's int element count
+ * overflows past 2^31 elements).
+ */
+int sbnet_copy_tensor(void* dst, const void* src, size_t bytes, void* stream);
+
+/*
+ * CudaTimerStart / CudaTimerEnd -- replace the two timing ops (sparse_gather.cc:390-466): start
+ * records an event on the legacy default stream and returns its handle; end records a second
+ * event, waits for it, returns the elapsed milliseconds and destroys both events.
+ */
+int sbnet_cuda_timer_start(int64_t* handle);
+int sbnet_cuda_timer_end(int64_t handle, float* elapsed_ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SBNET_B200_H */

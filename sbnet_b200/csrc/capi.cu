@@ -1,0 +1,244 @@
+// The C ABI (include/sbnet_b200.h): argument checks the reference performs in its OpKernels
+// (sbnet_ops/reduce_mask.cc:132-138, sbnet_ops/sparse_gather.cc:164,173,322-327), then the launch.
+#include <limits.h>
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "../../include/sbnet_b200.h"
+#include "common.cuh"
+#include "kernels.h"
+
+#define SBNET_EXPORT extern "C" __attribute__((visibility("default")))
+
+namespace {
+
+thread_local char g_err[320] = "";
+
+int reject(int code, const char* fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+inline int cuda_status(cudaError_t e)
+{
+    if (e != cudaSuccess)
+        snprintf(g_err, sizeof(g_err), "CUDA error %d: %s", (int)e, cudaGetErrorString(e));
+    return (int)e;
+}
+
+// Geometry limits shared by all ops: positive sizes/strides and every pixel coordinate inside 31 bits.
+int check_geometry(const char* op, int bOffsH, int bOffsW, int bSzH, int bSzW, int bStrH, int bStrW,
+                   long long maxBlockH, long long maxBlockW)
+{
+    if (bSzH < 1 || bSzW < 1)
+        return reject(SBNET_ERR_INVALID_ARGUMENT, "%s: block size must be positive, got [%d, %d]", op,
+                      bSzH, bSzW);
+    if (bStrH < 1 || bStrW < 1)
+        return reject(SBNET_ERR_INVALID_ARGUMENT, "%s: block stride must be positive, got [%d, %d]",
+                      op, bStrH, bStrW);
+    const long long lim = 1ll << 30;
+    const long long absH = bOffsH < 0 ? -(long long)bOffsH : bOffsH;
+    const long long absW = bOffsW < 0 ? -(long long)bOffsW : bOffsW;
+    if (absH + maxBlockH * bStrH + bSzH >= lim || absW + maxBlockW * bStrW + bSzW >= lim ||
+        (long long)bSzH * bSzW >= lim)
+        return reject(SBNET_ERR_UNSUPPORTED, "%s: block geometry exceeds 2^30 pixels", op);
+    return SBNET_OK;
+}
+
+int blocks_call(const char* op, int mode, const void* stackOrX, int dtype, int N, int H, int W, int C,
+                void* image, void* stack, int bOffsH, int bOffsW, int bSzH, int bSzW, int bStrH,
+                int bStrW, int numActive, const int32_t* numActiveDev, const int16_t* idx,
+                int transpose, void* stream)
+{
+    (void)stackOrX;
+    if (dtype != SBNET_F32 && dtype != SBNET_F16)
+        return reject(SBNET_ERR_INVALID_ARGUMENT, "%s: unknown dtype %d", op, dtype);
+    if (N < 1 || H < 1 || W < 1 || C < 1)
+        return reject(SBNET_ERR_INVALID_ARGUMENT,
+                      "%s: tensor must be rank 4 with positive dimensions, got [%d, %d, %d, %d]", op,
+                      N, H, W, C);
+    if (numActive < 0)
+        return reject(SBNET_ERR_INVALID_ARGUMENT, "%s: negative block count %d", op, numActive);
+    if (int rc = check_geometry(op, bOffsH, bOffsW, bSzH, bSzW, bStrH, bStrW, 32767, 32767))
+        return rc;
+    if (numActive == 0)
+        return SBNET_OK;
+    if (image == nullptr || stack == nullptr || idx == nullptr)
+        return reject(SBNET_ERR_INVALID_ARGUMENT, "%s: null tensor pointer", op);
+    const long long lim = 1ll << 31;
+    const long long blockElems = (long long)bSzH * bSzW * C;
+    const long long chunks = ((long long)C * 4 + 127) / 128;
+    if (blockElems >= lim || (long long)numActive * bSzH >= lim ||
+        (long long)numActive * chunks * ((long long)bSzH * bSzW / 128 + 1) >= lim)
+        return reject(SBNET_ERR_UNSUPPORTED, "%s: more than 2^31 work items", op);
+
+    sbnet::BlockArgs a;
+    a.image = image, a.stack = stack, a.idx = idx, a.num_active_dev = numActiveDev;
+    a.numActive = numActive, a.N = N, a.H = H, a.W = W, a.C = C;
+    a.bOffsH = bOffsH, a.bOffsW = bOffsW, a.bSzH = bSzH, a.bSzW = bSzW, a.bStrH = bStrH,
+    a.bStrW = bStrW;
+    return cuda_status(sbnet::launch_blocks(a, dtype, mode, transpose != 0, (cudaStream_t)stream));
+}
+
+int scatter_mode(const char* op, int add, int atomic, int bSzH, int bSzW, int bStrH, int bStrW,
+                 int* mode)
+{
+    if (add && !atomic && !(bStrH >= bSzH && bStrW >= bSzW))
+        return reject(SBNET_ERR_INVALID_ARGUMENT,
+                      "%s: Only non-overlapping blocks are supported with add=True, atomic=False", op);
+    *mode = !add ? sbnet::kScatterSet : (atomic ? sbnet::kScatterAtomic : sbnet::kScatterAdd);
+    return SBNET_OK;
+}
+
+} // namespace
+
+SBNET_EXPORT int sbnet_version(void) { return 100; }
+
+SBNET_EXPORT const char* sbnet_last_error(void) { return g_err; }
+
+SBNET_EXPORT int sbnet_reduce_mask(const float* mask, int N, int H, int W, float tol, int avgpool,
+                                   int bOffsH, int bOffsW, int bSzH, int bSzW, int bStrH, int bStrW,
+                                   int bCntH, int bCntW, int16_t* active_block_indices,
+                                   int32_t* scratch_dev, int32_t* count_host, int flags,
+                                   void* stream)
+{
+    const char* op = "ReduceMask";
+    if (N < 1 || H < 1 || W < 1)
+        return reject(SBNET_ERR_INVALID_ARGUMENT, "%s: mask must be [N,H,W,1] with positive dimensions, "
+                      "got [%d, %d, %d]", op, N, H, W);
+    if (bCntH < 1 || bCntW < 1)
+        return reject(SBNET_ERR_INVALID_ARGUMENT, "%s: block counts must be positive, got [%d, %d]", op,
+                      bCntH, bCntW);
+    if (N > 32767 || bCntH > 32767 || bCntW > 32767)
+        return reject(SBNET_ERR_INVALID_ARGUMENT,
+                      "%s: N, bCntH and bCntW must fit the int16 index triples (<= 32767), got %d, %d, %d",
+                      op, N, bCntH, bCntW);
+    if (int rc = check_geometry(op, bOffsH, bOffsW, bSzH, bSzW, bStrH, bStrW, bCntH, bCntW))
+        return rc;
+    if (mask == nullptr || active_block_indices == nullptr || scratch_dev == nullptr)
+        return reject(SBNET_ERR_INVALID_ARGUMENT, "%s: null tensor pointer", op);
+
+    cudaStream_t s = (cudaStream_t)stream;
+    int32_t* hostDev = nullptr;   // device-visible alias of count_host when it is pinned
+    if (count_host != nullptr) {
+        cudaPointerAttributes attr;
+        if (cudaPointerGetAttributes(&attr, count_host) == cudaSuccess &&
+            attr.type == cudaMemoryTypeHost && attr.devicePointer != nullptr)
+            hostDev = static_cast<int32_t*>(attr.devicePointer);
+        else
+            (void)cudaGetLastError();
+    }
+    if (!(flags & SBNET_SCRATCH_CLEAN))
+        if (cudaError_t e = cudaMemsetAsync(scratch_dev, 0, sizeof(int32_t) * SBNET_REDUCE_MASK_SCRATCH_INTS, s))
+            return cuda_status(e);
+    if (cudaError_t e = sbnet::launch_reduce_mask(mask, N, H, W, tol, avgpool != 0, bOffsH, bOffsW, bSzH,
+                                                  bSzW, bStrH, bStrW, bCntH, bCntW,
+                                                  active_block_indices, scratch_dev, hostDev, s))
+        return cuda_status(e);
+    if (count_host != nullptr) {
+        if (hostDev == nullptr)
+            if (cudaError_t e = cudaMemcpyAsync(count_host, scratch_dev, sizeof(int32_t),
+                                                cudaMemcpyDeviceToHost, s))
+                return cuda_status(e);
+        if (cudaError_t e = cudaStreamSynchronize(s))
+            return cuda_status(e);
+    }
+    return SBNET_OK;
+}
+
+SBNET_EXPORT int sbnet_sparse_gather(const void* x, int dtype, int N, int H, int W, int C, void* y,
+                                     int bOffsH, int bOffsW, int bSzH, int bSzW, int bStrH,
+                                     int bStrW, int numActive, const int16_t* active_block_indices,
+                                     int transpose, void* stream)
+{
+    return blocks_call("SparseGather", sbnet::kGather, x, dtype, N, H, W, C, const_cast<void*>(x), y,
+                       bOffsH, bOffsW, bSzH, bSzW, bStrH, bStrW, numActive, nullptr,
+                       active_block_indices, transpose, stream);
+}
+
+SBNET_EXPORT int sbnet_sparse_gather_dyn(const void* x, int dtype, int N, int H, int W, int C,
+                                         void* y, int bOffsH, int bOffsW, int bSzH, int bSzW,
+                                         int bStrH, int bStrW, int maxActive,
+                                         const int32_t* num_active_dev,
+                                         const int16_t* active_block_indices, int transpose,
+                                         void* stream)
+{
+    if (num_active_dev == nullptr)
+        return reject(SBNET_ERR_INVALID_ARGUMENT, "SparseGather: num_active_dev is null");
+    return blocks_call("SparseGather", sbnet::kGather, x, dtype, N, H, W, C, const_cast<void*>(x), y,
+                       bOffsH, bOffsW, bSzH, bSzW, bStrH, bStrW, maxActive, num_active_dev,
+                       active_block_indices, transpose, stream);
+}
+
+SBNET_EXPORT int sbnet_sparse_scatter(const void* x, int dtype, int N, int H, int W, int C, void* y,
+                                      int bOffsH, int bOffsW, int bSzH, int bSzW, int bStrH,
+                                      int bStrW, int numActive, const int16_t* active_block_indices,
+                                      int add, int transpose, int atomic, void* stream)
+{
+    int mode = 0;
+    if (int rc = scatter_mode("SparseScatter", add, atomic, bSzH, bSzW, bStrH, bStrW, &mode))
+        return rc;
+    return blocks_call("SparseScatter", mode, x, dtype, N, H, W, C, y, const_cast<void*>(x), bOffsH,
+                       bOffsW, bSzH, bSzW, bStrH, bStrW, numActive, nullptr, active_block_indices,
+                       transpose, stream);
+}
+
+SBNET_EXPORT int sbnet_sparse_scatter_dyn(const void* x, int dtype, int N, int H, int W, int C,
+                                          void* y, int bOffsH, int bOffsW, int bSzH, int bSzW,
+                                          int bStrH, int bStrW, int maxActive,
+                                          const int32_t* num_active_dev,
+                                          const int16_t* active_block_indices, int add,
+                                          int transpose, int atomic, void* stream)
+{
+    int mode = 0;
+    if (num_active_dev == nullptr)
+        return reject(SBNET_ERR_INVALID_ARGUMENT, "SparseScatter: num_active_dev is null");
+    if (int rc = scatter_mode("SparseScatter", add, atomic, bSzH, bSzW, bStrH, bStrW, &mode))
+        return rc;
+    return blocks_call("SparseScatter", mode, x, dtype, N, H, W, C, y, const_cast<void*>(x), bOffsH,
+                       bOffsW, bSzH, bSzW, bStrH, bStrW, maxActive, num_active_dev,
+                       active_block_indices, transpose, stream);
+}
+
+SBNET_EXPORT int sbnet_copy_tensor(void* dst, const void* src, size_t bytes, void* stream)
+{
+    if (bytes != 0 && (dst == nullptr || src == nullptr))
+        return reject(SBNET_ERR_INVALID_ARGUMENT, "CopyTensor: null pointer");
+    return cuda_status(sbnet::launch_copy(dst, src, bytes, (cudaStream_t)stream));
+}
+
+SBNET_EXPORT int sbnet_cuda_timer_start(int64_t* handle)
+{
+    if (handle == nullptr)
+        return reject(SBNET_ERR_INVALID_ARGUMENT, "CudaTimerStart: null handle");
+    cudaEvent_t ev;
+    if (cudaError_t e = cudaEventCreate(&ev))
+        return cuda_status(e);
+    if (cudaError_t e = cudaEventRecord(ev, 0)) {
+        cudaEventDestroy(ev);
+        return cuda_status(e);
+    }
+    *handle = (int64_t)reinterpret_cast<intptr_t>(ev);
+    return SBNET_OK;
+}
+
+SBNET_EXPORT int sbnet_cuda_timer_end(int64_t handle, float* elapsed_ms)
+{
+    if (handle == 0 || elapsed_ms == nullptr)
+        return reject(SBNET_ERR_INVALID_ARGUMENT, "CudaTimerEnd: null handle or output");
+    cudaEvent_t start = reinterpret_cast<cudaEvent_t>((intptr_t)handle), stop;
+    if (cudaError_t e = cudaEventCreate(&stop))
+        return cuda_status(e);
+    cudaError_t e = cudaEventRecord(stop, 0);
+    if (e == cudaSuccess)
+        e = cudaEventSynchronize(stop);
+    if (e == cudaSuccess)
+        e = cudaEventElapsedTime(elapsed_ms, start, stop);
+    cudaEventDestroy(stop);
+    cudaEventDestroy(start);
+    return cuda_status(e);
+}

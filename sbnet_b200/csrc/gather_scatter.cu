@@ -1,0 +1,452 @@
+// sparse_gather / sparse_scatter for sm_100a -- general kernels (any block size, stride, offset,
+// channel count, fp32 or fp16).
+//
+// Replaces the reference's blockGatherTiled0/1 and blockScatterTiled0/1 families and their launcher
+// (sbnet_ops/sparse_blocks.cu.h:68-366, sbnet_ops/sparse_gather.cu:41-266).  Semantics follow the
+// reference CPU functors (sbnet_ops/sparse_gather.cc:61-132): the in-range test is per PIXEL, so
+// gather zero-fills and scatter drops whatever part of a block hangs over any image border.
+//
+// Two layouts of the block stack:
+//  * [nB, R, S, C] ("rows"): a block row of S pixels is one contiguous run of S*C elements both in
+//    the NHWC image and in the stack, so the op is a clipped copy of contiguous runs.  Threads move
+//    the widest vector (16/8/4/2 bytes) that divides C*sizeof(T), several per thread in flight, no
+//    shared memory.
+//  * [nB, C, R, S] ("planes", transpose=true): a CTA stages a tile of pixels x channels (128 bytes of
+//    channels per pixel) in shared memory with an odd word pitch, so that the image side moves
+//    128-byte channel runs and the stack side moves runs of consecutive pixels of one channel plane,
+//    both conflict-free.
+// Scatter has three write modes: overwrite, read-add-write (legal only for disjoint blocks) and
+// vector reductions (red.global.add .v4.f32 / .v4.f16x2 and narrower) for overlapping halos.
+//
+// The launch is a fixed-size grid of CTAs striding over work items, so the number of active blocks
+// may come from device memory (written by reduce_mask earlier on the same stream) instead of the
+// host.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace sbnet {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;
+
+__device__ __forceinline__ int active_count(const BlockArgs& a)
+{
+    if (a.num_active_dev == nullptr)
+        return a.numActive;
+    const int n = __ldg(a.num_active_dev);
+    return n < a.numActive ? n : a.numActive;
+}
+
+template <int VB> __device__ __forceinline__ typename Vec<VB>::type ld_plain(const typename Vec<VB>::type* p)
+{
+    return *p;
+}
+
+// Applies one vector to the image in the given scatter mode.
+template <int VB, int MODE, typename T>
+__device__ __forceinline__ void image_write(typename Vec<VB>::type* dst, typename Vec<VB>::type v,
+                                            typename Vec<VB>::type old)
+{
+    if constexpr (MODE == kScatterSet)
+        *dst = v;
+    else if constexpr (MODE == kScatterAdd)
+        *dst = vadd<T>(old, v);
+    else
+        Red<T>::add(dst, v);
+}
+
+// ---- [nB,R,S,C] layout ---------------------------------------------------------------------------
+struct RowPlan {
+    FastDiv vecsPerRow;     // S * C * sizeof(T) / VB
+    FastDiv itemsPerBlock;
+    int vecsPerPixel;       // C * sizeof(T) / VB
+    int rowsPerItem;
+};
+
+template <int VB, int MODE, typename T>
+__global__ void __launch_bounds__(kThreads, 4) rows_kernel(const BlockArgs a, const RowPlan p)
+{
+    typedef typename Vec<VB>::type V;
+    const int nActive = active_count(a);
+    const long long nItems = (long long)nActive * p.itemsPerBlock.div;
+    const long long rowPitch = (long long)a.W * p.vecsPerPixel;   // image row, in vectors
+    const int vpr = (int)p.vecsPerRow.div;
+
+    for (long long item = blockIdx.x; item < nItems; item += gridDim.x) {
+        uint32_t ib, chunk;
+        p.itemsPerBlock.divmod((uint32_t)item, ib, chunk);
+        const int r0 = (int)chunk * p.rowsPerItem;
+        const int nRows = min(p.rowsPerItem, a.bSzH - r0);
+        const int n = a.idx[ib * 3 + 0];
+        const int h0 = a.bOffsH + a.idx[ib * 3 + 1] * a.bStrH + r0;
+        const int w0 = a.bOffsW + a.idx[ib * 3 + 2] * a.bStrW;
+        // in-range part of a block row, in vectors from the row's first pixel
+        const int qLo = max(0, -w0) * p.vecsPerPixel;
+        const int qHi = max(0, min(a.bSzW, a.W - w0)) * p.vecsPerPixel;
+        V* img = reinterpret_cast<V*>(a.image) +
+                 (((long long)n * a.H + h0) * a.W + w0) * (long long)p.vecsPerPixel;
+        V* stk = reinterpret_cast<V*>(a.stack) + ((long long)ib * a.bSzH + r0) * vpr;
+        const int total = nRows * vpr;
+
+        for (int v0 = threadIdx.x; v0 < total; v0 += kThreads * kUnroll) {
+            V val[kUnroll], old[kUnroll];
+            long long ioff[kUnroll];
+            bool inr[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int v = v0 + u * kThreads;
+                uint32_t r, q;
+                p.vecsPerRow.divmod((uint32_t)min(v, total - 1), r, q);
+                const int h = h0 + (int)r;
+                inr[u] = v < total && h >= 0 && h < a.H && (int)q >= qLo && (int)q < qHi;
+                ioff[u] = (long long)r * rowPitch + q;
+                if constexpr (MODE == kGather) {
+                    val[u] = inr[u] ? ld_stream(img + ioff[u]) : vzero<VB>();
+                } else {
+                    val[u] = inr[u] ? ld_stream(stk + v) : vzero<VB>();
+                    if constexpr (MODE == kScatterAdd)
+                        old[u] = inr[u] ? ld_plain<VB>(img + ioff[u]) : vzero<VB>();
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int v = v0 + u * kThreads;
+                if constexpr (MODE == kGather) {
+                    if (v < total)
+                        stk[v] = val[u];
+                } else {
+                    if (inr[u])
+                        image_write<VB, MODE, T>(img + ioff[u], val[u], old[u]);
+                }
+            }
+        }
+    }
+}
+
+// ---- [nB,C,R,S] layout ---------------------------------------------------------------------------
+constexpr int kTileBytes = 44352;   // 336 pixels x 33 words
+
+struct PlanePlan {
+    FastDiv blockW;          // S
+    FastDiv cChunks;         // channel chunks per block
+    FastDiv pChunks;         // pixel chunks per block
+    FastDiv vecsPerPixelFull, vecsPerPixelLast;   // vectors per pixel in a full / the last chunk
+    FastDiv pixFull, pixLast;                     // pixels in a full / the last pixel chunk
+    int chanPerChunk;        // channels per chunk (128 bytes worth, or all of C)
+    int pixPerChunk;
+    int pitch;               // shared-memory pitch of one pixel, in elements (odd number of words)
+};
+
+template <int VB, typename T> __device__ __forceinline__ void tile_store(T* p, typename Vec<VB>::type v)
+{
+    if constexpr (VB == 2) {
+        *reinterpret_cast<uint16_t*>(p) = v;
+    } else {
+        uint32_t w[VB / 4];
+        memcpy(w, &v, VB);
+#pragma unroll
+        for (int i = 0; i < VB / 4; ++i)
+            reinterpret_cast<uint32_t*>(p)[i] = w[i];
+    }
+}
+template <int VB, typename T> __device__ __forceinline__ typename Vec<VB>::type tile_load(const T* p)
+{
+    typename Vec<VB>::type v;
+    if constexpr (VB == 2) {
+        v = *reinterpret_cast<const uint16_t*>(p);
+    } else {
+        uint32_t w[VB / 4];
+#pragma unroll
+        for (int i = 0; i < VB / 4; ++i)
+            w[i] = reinterpret_cast<const uint32_t*>(p)[i];
+        memcpy(&v, w, VB);
+    }
+    return v;
+}
+
+template <int VB, int MODE, typename T>
+__global__ void __launch_bounds__(kThreads, 4) planes_kernel(const BlockArgs a, const PlanePlan p)
+{
+    typedef typename Vec<VB>::type V;
+    constexpr int EPV = VB / (int)sizeof(T);   // elements per vector
+    __shared__ __align__(16) unsigned char tileRaw[kTileBytes];
+    T* tile = reinterpret_cast<T*>(tileRaw);
+
+    const int nActive = active_count(a);
+    const uint32_t itemsPerBlock = p.cChunks.div * p.pChunks.div;
+    const long long nItems = (long long)nActive * itemsPerBlock;
+    const int RS = a.bSzH * a.bSzW;
+    T* image = reinterpret_cast<T*>(a.image);
+    T* stack = reinterpret_cast<T*>(a.stack);
+
+    for (long long item = blockIdx.x; item < nItems; item += gridDim.x) {
+        uint32_t rest, cc, ib, pc;
+        p.cChunks.divmod((uint32_t)item, rest, cc);   // channel chunk varies fastest
+        p.pChunks.divmod(rest, ib, pc);
+        const bool lastC = cc + 1 == p.cChunks.div, lastP = pc + 1 == p.pChunks.div;
+        const int c0 = (int)cc * p.chanPerChunk;
+        const int nChan = min(p.chanPerChunk, a.C - c0);
+        const int p0 = (int)pc * p.pixPerChunk;
+        const int nPix = min(p.pixPerChunk, RS - p0);
+        const FastDiv vpp = lastC ? p.vecsPerPixelLast : p.vecsPerPixelFull;
+        const FastDiv pixDiv = lastP ? p.pixLast : p.pixFull;
+        const int n = a.idx[ib * 3 + 0];
+        const int h0 = a.bOffsH + a.idx[ib * 3 + 1] * a.bStrH;
+        const int w0 = a.bOffsW + a.idx[ib * 3 + 2] * a.bStrW;
+        const T* imgN = image + (long long)n * a.H * a.W * a.C + c0;
+        T* planes = stack + ((long long)ib * a.C + c0) * RS + p0;   // [nChan][RS] view, pixel p0
+        const int nVec = nPix * (int)vpp.div;
+        const int nElem = nPix * nChan;
+
+        if constexpr (MODE == kGather) {
+            // image -> tile: one vector of channels per thread-step, kUnroll loads in flight
+            for (int v0 = threadIdx.x; v0 < nVec; v0 += kThreads * kUnroll) {
+                V val[kUnroll];
+                uint32_t px[kUnroll], j[kUnroll];
+#pragma unroll
+                for (int u = 0; u < kUnroll; ++u) {
+                    const int v = v0 + u * kThreads;
+                    vpp.divmod((uint32_t)min(v, nVec - 1), px[u], j[u]);
+                    uint32_t r, s;
+                    p.blockW.divmod((uint32_t)p0 + px[u], r, s);
+                    const int h = h0 + (int)r, w = w0 + (int)s;
+                    const bool inr = v < nVec && h >= 0 && h < a.H && w >= 0 && w < a.W;
+                    val[u] = inr ? ld_stream(reinterpret_cast<const V*>(
+                                       imgN + ((long long)h * a.W + w) * a.C + j[u] * EPV))
+                                 : vzero<VB>();
+                }
+#pragma unroll
+                for (int u = 0; u < kUnroll; ++u)
+                    if (v0 + u * kThreads < nVec)
+                        tile_store<VB, T>(tile + px[u] * p.pitch + j[u] * EPV, val[u]);
+            }
+            __syncthreads();
+            // tile -> stack: consecutive threads write consecutive pixels of one channel plane
+            for (int o = threadIdx.x; o < nElem; o += kThreads) {
+                uint32_t c, px;
+                pixDiv.divmod((uint32_t)o, c, px);
+                planes[(long long)c * RS + px] = tile[px * p.pitch + c];
+            }
+            __syncthreads();
+        } else {
+            // stack -> tile
+            for (int o0 = threadIdx.x; o0 < nElem; o0 += kThreads * 8) {
+                T val[8];
+                uint32_t c[8], px[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int o = o0 + u * kThreads;
+                    pixDiv.divmod((uint32_t)min(o, nElem - 1), c[u], px[u]);
+                    val[u] = planes[(long long)c[u] * RS + px[u]];
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (o0 + u * kThreads < nElem)
+                        tile[px[u] * p.pitch + c[u]] = val[u];
+            }
+            __syncthreads();
+            // tile -> image
+            for (int v = threadIdx.x; v < nVec; v += kThreads) {
+                uint32_t px, j, r, s;
+                vpp.divmod((uint32_t)v, px, j);
+                p.blockW.divmod((uint32_t)p0 + px, r, s);
+                const int h = h0 + (int)r, w = w0 + (int)s;
+                if (h >= 0 && h < a.H && w >= 0 && w < a.W) {
+                    V* dst = reinterpret_cast<V*>(const_cast<T*>(imgN) +
+                                                  ((long long)h * a.W + w) * a.C + j * EPV);
+                    const V val = tile_load<VB, T>(tile + px * p.pitch + j * EPV);
+                    V old = vzero<VB>();
+                    if constexpr (MODE == kScatterAdd)
+                        old = *dst;
+                    image_write<VB, MODE, T>(dst, val, old);
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+int sm_count()
+{
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+        return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+static int pick_vector_bytes(const BlockArgs& a, int itemsize)
+{
+    const size_t pixelBytes = (size_t)a.C * itemsize;
+    const uintptr_t ptrs = reinterpret_cast<uintptr_t>(a.image) | reinterpret_cast<uintptr_t>(a.stack);
+    for (int vb = 16; vb > itemsize; vb >>= 1)
+        if (pixelBytes % vb == 0 && (ptrs & (vb - 1)) == 0)
+            return vb;
+    return itemsize;
+}
+
+template <int VB, int MODE, typename T>
+static void launch_rows(const BlockArgs& a, cudaStream_t stream)
+{
+    const int itemsize = (int)sizeof(T);
+    RowPlan p;
+    p.vecsPerPixel = (int)((size_t)a.C * itemsize / VB);
+    const long long vpr = (long long)a.bSzW * p.vecsPerPixel;
+    p.vecsPerRow = FastDiv((uint32_t)vpr);
+    // an item is a run of block rows of roughly 32 KB; prefer a divisor of the block height
+    const long long rowBytes = vpr * VB;
+    int rows = (int)((32768 + rowBytes - 1) / rowBytes);
+    rows = rows < 1 ? 1 : (rows > a.bSzH ? a.bSzH : rows);
+    for (int r = rows; r >= 1 && r * 2 > rows; --r)
+        if (a.bSzH % r == 0) {
+            rows = r;
+            break;
+        }
+    p.rowsPerItem = rows;
+    const int ipb = (a.bSzH + rows - 1) / rows;
+    p.itemsPerBlock = FastDiv((uint32_t)ipb);
+    const long long nItems = (long long)a.numActive * ipb;
+    const long long cap = (long long)sm_count() * 8;
+    const int grid = (int)(nItems < cap ? nItems : cap);
+    rows_kernel<VB, MODE, T><<<grid, kThreads, 0, stream>>>(a, p);
+}
+
+template <int VB, int MODE, typename T>
+static void launch_planes(const BlockArgs& a, cudaStream_t stream)
+{
+    const int itemsize = (int)sizeof(T);
+    PlanePlan p;
+    const int RS = a.bSzH * a.bSzW;
+    const int chunkElems = 128 / itemsize;
+    p.chanPerChunk = a.C < chunkElems ? a.C : chunkElems;
+    // pitch: an odd number of 32-bit words (2-byte elements with a 2-byte vector: any odd count)
+    if (itemsize == 4 || VB == 2) {
+        p.pitch = p.chanPerChunk | 1;
+    } else {
+        const int words = (p.chanPerChunk + 1) / 2;
+        p.pitch = (words | 1) * 2;
+    }
+    const int maxPix = kTileBytes / (p.pitch * itemsize);
+    p.pixPerChunk = RS < maxPix ? RS : maxPix;
+    const int nC = (a.C + p.chanPerChunk - 1) / p.chanPerChunk;
+    const int nP = (RS + p.pixPerChunk - 1) / p.pixPerChunk;
+    const int lastChan = a.C - (nC - 1) * p.chanPerChunk;
+    const int lastPix = RS - (nP - 1) * p.pixPerChunk;
+    p.blockW = FastDiv((uint32_t)a.bSzW);
+    p.cChunks = FastDiv((uint32_t)nC);
+    p.pChunks = FastDiv((uint32_t)nP);
+    p.vecsPerPixelFull = FastDiv((uint32_t)(p.chanPerChunk * itemsize / VB));
+    p.vecsPerPixelLast = FastDiv((uint32_t)(lastChan * itemsize / VB));
+    p.pixFull = FastDiv((uint32_t)p.pixPerChunk);
+    p.pixLast = FastDiv((uint32_t)lastPix);
+    const long long nItems = (long long)a.numActive * nC * nP;
+    const long long cap = (long long)sm_count() * 4;
+    const int grid = (int)(nItems < cap ? nItems : cap);
+    planes_kernel<VB, MODE, T><<<grid, kThreads, 0, stream>>>(a, p);
+}
+
+template <int MODE, typename T>
+static void dispatch_vb(const BlockArgs& a, bool transpose, int vb, cudaStream_t stream)
+{
+#define SBNET_GO(VBYTES)                                       \
+    do {                                                       \
+        if (transpose)                                         \
+            launch_planes<VBYTES, MODE, T>(a, stream);         \
+        else                                                   \
+            launch_rows<VBYTES, MODE, T>(a, stream);           \
+    } while (0)
+    switch (vb) {
+    case 16: SBNET_GO(16); break;
+    case 8: SBNET_GO(8); break;
+    case 4: SBNET_GO(4); break;
+    default:
+        if constexpr (sizeof(T) == 2)
+            SBNET_GO(2);
+        break;
+    }
+#undef SBNET_GO
+}
+
+template <typename T>
+static void dispatch_mode(const BlockArgs& a, int mode, bool transpose, int vb, cudaStream_t stream)
+{
+    switch (mode) {
+    case kGather: dispatch_vb<kGather, T>(a, transpose, vb, stream); break;
+    case kScatterSet: dispatch_vb<kScatterSet, T>(a, transpose, vb, stream); break;
+    case kScatterAdd: dispatch_vb<kScatterAdd, T>(a, transpose, vb, stream); break;
+    default: dispatch_vb<kScatterAtomic, T>(a, transpose, vb, stream); break;
+    }
+}
+
+cudaError_t launch_blocks(const BlockArgs& a, int dtype, int mode, bool transpose,
+                          cudaStream_t stream)
+{
+    if (a.numActive <= 0)
+        return cudaSuccess;
+    const int itemsize = dtype == 0 ? 4 : 2;
+    const int vb = pick_vector_bytes(a, itemsize);
+    if (dtype == 0)
+        dispatch_mode<float>(a, mode, transpose, vb, stream);
+    else
+        dispatch_mode<__half>(a, mode, transpose, vb, stream);
+    return cudaGetLastError();
+}
+
+// ---- flat copy (the non-Var scatter's "y = ybase") -----------------------------------------------
+__global__ void __launch_bounds__(kThreads) copy_kernel(uint4* __restrict__ dst,
+                                                        const uint4* __restrict__ src, size_t nVec,
+                                                        unsigned char* dstTail,
+                                                        const unsigned char* srcTail, int tailBytes)
+{
+    const size_t stride = (size_t)gridDim.x * kThreads;
+    size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x;
+    for (; i + 3 * stride < nVec; i += 4 * stride) {
+        const uint4 v0 = ld_stream(src + i), v1 = ld_stream(src + i + stride),
+                    v2 = ld_stream(src + i + 2 * stride), v3 = ld_stream(src + i + 3 * stride);
+        dst[i] = v0, dst[i + stride] = v1, dst[i + 2 * stride] = v2, dst[i + 3 * stride] = v3;
+    }
+    for (; i < nVec; i += stride)
+        dst[i] = ld_stream(src + i);
+    if (blockIdx.x == 0 && (int)threadIdx.x < tailBytes)
+        dstTail[threadIdx.x] = srcTail[threadIdx.x];
+}
+
+__global__ void copy_bytes_kernel(unsigned char* dst, const unsigned char* src, size_t n)
+{
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        dst[i] = src[i];
+}
+
+cudaError_t launch_copy(void* dst, const void* src, size_t bytes, cudaStream_t stream)
+{
+    if (bytes == 0 || dst == src)
+        return cudaSuccess;
+    const long long cap = (long long)sm_count() * 8;
+    if (((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15) == 0) {
+        const size_t nVec = bytes / 16;
+        const int tail = (int)(bytes - nVec * 16);
+        long long want = (long long)((nVec + kThreads * 4 - 1) / (kThreads * 4));
+        const int grid = (int)(want < 1 ? 1 : (want < cap ? want : cap));
+        copy_kernel<<<grid, kThreads, 0, stream>>>(
+            reinterpret_cast<uint4*>(dst), reinterpret_cast<const uint4*>(src), nVec,
+            reinterpret_cast<unsigned char*>(dst) + nVec * 16,
+            reinterpret_cast<const unsigned char*>(src) + nVec * 16, tail);
+    } else {
+        long long want = (long long)((bytes + kThreads - 1) / kThreads);
+        const int grid = (int)(want < cap ? want : cap);
+        copy_bytes_kernel<<<grid, kThreads, 0, stream>>>(reinterpret_cast<unsigned char*>(dst),
+                                                         reinterpret_cast<const unsigned char*>(src),
+                                                         bytes);
+    }
+    return cudaGetLastError();
+}
+
+} // namespace sbnet

@@ -1,0 +1,25 @@
+// Launchers behind the C ABI (internal; the public surface is include/sbnet_b200.h).
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace sbnet {
+
+struct BlockArgs;
+
+// scratch: 4 x int32 on the device; [1] and [2] must be zero on entry and are zero again on exit.
+cudaError_t launch_reduce_mask(const float* mask, int N, int H, int W, float tol, bool avgpool,
+                               int bOffsH, int bOffsW, int bSzH, int bSzW, int bStrH, int bStrW,
+                               int bCntH, int bCntW, int16_t* idx, int32_t* scratch,
+                               int32_t* host_count_dev, cudaStream_t stream);
+
+// mode: 0 gather, 1 scatter overwrite, 2 scatter add (disjoint blocks), 3 scatter atomic add
+cudaError_t launch_blocks(const BlockArgs& a, int dtype, int mode, bool transpose,
+                          cudaStream_t stream);
+
+cudaError_t launch_copy(void* dst, const void* src, size_t bytes, cudaStream_t stream);
+
+int sm_count();
+
+} // namespace sbnet

@@ -1,0 +1,288 @@
+// reduce_mask for sm_100a: block-local max / average pooling of a dense [N,H,W] fp32 mask,
+// thresholding, and compaction of the active (n, bh, bw) triples -- in ONE launch.
+//
+// Replaces the reference's zeroBlockCounters + reduceMask pair and the host-side empty-mask fix-up
+// (sbnet_ops/reduce_mask.cu:69-85, reduce_mask.cu.h:54-157, zero_block_counters.cu.h:26-51,
+// reduce_mask.cc:203-220).  Results follow the reference CPU functor (reduce_mask.cc:66-96): same
+// set of indices, same count; the order of the list is arrival order, as on the reference GPU path.
+//
+// Layout of the work: one CTA owns a horizontal BAND of the image -- the rows of one block row bh
+// of one image n -- and a tile of consecutive block columns.  Threads own image columns (four at a
+// time, one 128-bit load per row) and run down the band's rows keeping all loads of a batch in
+// flight; the per-column partial results go to shared memory, then one thread per block combines
+// the columns of its window.  Every mask byte is fetched from DRAM once (neighbouring bands share
+// their halo rows through L2).
+//
+// Exactness.  Max pooling is "any pixel > tol", which does not depend on evaluation order.  Average
+// pooling compares fl(sum/area) with tol, and the reference sums the window row-major in fp32; the
+// column-then-row order used here can differ in the last bits.  Each block therefore also carries
+// the sum of magnitudes, which bounds the difference between ANY two summation orders; only when
+// the threshold falls inside that bound (practically never for 0/1 masks, rarely for real-valued
+// ones) is the block re-evaluated by one thread in the reference's exact order.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace sbnet {
+
+constexpr int kRmThreads = 256;
+constexpr int kRmMaxCols = 4096;   // image columns one CTA stages (x2 floats of shared memory)
+constexpr int kRowBatch = 9;       // loads kept in flight per thread while running down a band
+
+struct RmArgs {
+    const float* mask;
+    int16_t* idx;
+    int32_t* scratch;      // [0] published count, [1] append cursor, [2] finished-CTA ticket
+    int32_t* host_count;   // optional device-visible address of a pinned host int
+    int N, H, W;
+    float tol;
+    int bOffsH, bOffsW, bSzH, bSzW, bStrH, bStrW, bCntH, bCntW;
+    int tileBlocks;        // block columns per CTA
+    float area;            // (float)(bSzH*bSzW)
+};
+
+// The reference's evaluation order for one block, used for the rare ambiguous average and by the
+// fallback kernel for geometries the band kernel does not take.
+template <bool AVG>
+__device__ bool block_active_exact(const RmArgs& a, int n, int bh, int bw)
+{
+    const int h0 = a.bOffsH + bh * a.bStrH, w0 = a.bOffsW + bw * a.bStrW;
+    const int hBeg = max(h0, 0), wBeg = max(w0, 0);
+    const int hEnd = min(h0 + a.bSzH, a.H), wEnd = min(w0 + a.bSzW, a.W);
+    const float* img = a.mask + (size_t)n * a.H * a.W;
+    float sum = 0.0f;
+    bool any = false;
+    for (int hh = hBeg; hh < hEnd; ++hh) {
+        const float* row = img + (size_t)hh * a.W;
+        for (int ww = wBeg; ww < wEnd; ++ww) {
+            const float v = row[ww];
+            if (AVG)
+                sum = __fadd_rn(sum, v);
+            else
+                any |= (v > a.tol);
+        }
+    }
+    return AVG ? (__fdiv_rn(sum, a.area) > a.tol) : any;
+}
+
+// Appends the active blocks of one warp with a single atomic: ballot, popc, one reservation.
+__device__ __forceinline__ void append_active(const RmArgs& a, bool active, int n, int bh, int bw)
+{
+    const unsigned ballot = __ballot_sync(0xffffffffu, active);
+    if (ballot == 0)
+        return;
+    const int lane = threadIdx.x & 31;
+    const int leader = __ffs(ballot) - 1;
+    int base = 0;
+    if (lane == leader)
+        base = atomicAdd(a.scratch + 1, __popc(ballot));
+    base = __shfl_sync(0xffffffffu, base, leader);
+    if (active) {
+        int16_t* out = a.idx + (size_t)(base + __popc(ballot & ((1u << lane) - 1u))) * 3;
+        out[0] = (int16_t)n;
+        out[1] = (int16_t)bh;
+        out[2] = (int16_t)bw;
+    }
+}
+
+// Last CTA out publishes the count (an empty result becomes the single block (0,0,0), as the
+// reference op does on the host) and leaves cursor and ticket at zero for the next call.
+__device__ __forceinline__ void finish(const RmArgs& a, unsigned totalCtas)
+{
+    __syncthreads();
+    if (threadIdx.x != 0)
+        return;
+    __threadfence();
+    const unsigned ticket = atomicAdd(reinterpret_cast<unsigned*>(a.scratch + 2), 1u);
+    if (ticket != totalCtas - 1)
+        return;
+    __threadfence();
+    int count = atomicAdd(a.scratch + 1, 0);
+    if (count == 0) {
+        a.idx[0] = a.idx[1] = a.idx[2] = 0;
+        count = 1;
+    }
+    a.scratch[0] = count;
+    a.scratch[1] = 0;
+    a.scratch[2] = 0;
+    if (a.host_count) {
+        *reinterpret_cast<volatile int32_t*>(a.host_count) = count;
+        __threadfence_system();
+    }
+}
+
+template <bool AVG, bool VEC4>
+__global__ void __launch_bounds__(kRmThreads) reduce_mask_band(const RmArgs a)
+{
+    // per staged column: sum (or any-flag) and, for AVG, the sum of magnitudes
+    __shared__ float colVal[kRmMaxCols];
+    __shared__ float colMag[AVG ? kRmMaxCols : 1];
+
+    const int n = blockIdx.z, bh = blockIdx.y;
+    const int bw0 = blockIdx.x * a.tileBlocks;
+    const int bwEnd = min(bw0 + a.tileBlocks, a.bCntW);
+    const int h0 = a.bOffsH + bh * a.bStrH;
+    const int hBeg = max(h0, 0), hEnd = min(h0 + a.bSzH, a.H);
+
+    // columns this tile touches, widened to whole 4-column groups when loads are vectorised
+    int cBeg = max(a.bOffsW + bw0 * a.bStrW, 0);
+    int cEnd = min(a.bOffsW + (bwEnd - 1) * a.bStrW + a.bSzW, a.W);
+    if (VEC4) {
+        cBeg &= ~3;
+        cEnd = min((cEnd + 3) & ~3, a.W);
+    }
+    const int nCols = max(cEnd - cBeg, 0);
+    const float* img = a.mask + (size_t)n * a.H * a.W;
+
+    constexpr int V = VEC4 ? 4 : 1;
+    for (int cv = threadIdx.x * V; cv < nCols; cv += kRmThreads * V) {
+        float acc[V], mag[V];
+#pragma unroll
+        for (int j = 0; j < V; ++j)
+            acc[j] = 0.0f, mag[j] = 0.0f;
+        const float* colp = img + cBeg + cv;
+        for (int hb = hBeg; hb < hEnd; hb += kRowBatch) {
+            float v[kRowBatch][V];
+#pragma unroll
+            for (int k = 0; k < kRowBatch; ++k) {
+                const int hh = min(hb + k, hEnd - 1);   // clamped rows are loaded but not counted
+                if constexpr (VEC4) {
+                    const float4 q = __ldg(reinterpret_cast<const float4*>(colp + (size_t)hh * a.W));
+                    v[k][0] = q.x, v[k][1] = q.y, v[k][2] = q.z, v[k][3] = q.w;
+                } else {
+                    v[k][0] = __ldg(colp + (size_t)hh * a.W);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < kRowBatch; ++k) {
+                if (hb + k < hEnd) {
+#pragma unroll
+                    for (int j = 0; j < V; ++j) {
+                        if (AVG) {
+                            acc[j] = __fadd_rn(acc[j], v[k][j]);
+                            mag[j] = __fadd_rn(mag[j], fabsf(v[k][j]));
+                        } else {
+                            acc[j] = (v[k][j] > a.tol) ? 1.0f : acc[j];
+                        }
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            colVal[cv + j] = acc[j];
+            if (AVG)
+                colMag[cv + j] = mag[j];
+        }
+    }
+    __syncthreads();
+
+    // one thread per block column of the tile; whole warps stay together for the ballot
+    const int nBlk = bwEnd - bw0;
+    for (int b = threadIdx.x; b < ((nBlk + 31) & ~31); b += kRmThreads) {
+        bool active = false;
+        const int bw = bw0 + b;
+        if (b < nBlk && hBeg < hEnd) {
+            const int w0 = a.bOffsW + bw * a.bStrW;
+            const int wBeg = max(w0, 0), wEnd = min(w0 + a.bSzW, a.W);
+            float s = 0.0f, m = 0.0f;
+            for (int ww = wBeg; ww < wEnd; ++ww) {
+                if (AVG) {
+                    s = __fadd_rn(s, colVal[ww - cBeg]);
+                    m = __fadd_rn(m, colMag[ww - cBeg]);
+                } else {
+                    s = fmaxf(s, colVal[ww - cBeg]);
+                }
+            }
+            if (!AVG) {
+                active = s > 0.0f;
+            } else {
+                // |sum in any order - exact sum| <= ~terms * 2^-24 * m; two orders differ by at
+                // most twice that.  A factor-two margin on top covers the rounding of m itself.
+                const float terms = (float)(hEnd - hBeg) * (float)max(wEnd - wBeg, 0);
+                const float rel = terms * 5.9604645e-8f;
+                const float delta = 4.0f * rel * m;   // exactly 0 for an all-zero window
+                const bool yes = __fdiv_rn(s - delta, a.area) > a.tol;
+                const bool no = !(__fdiv_rn(s + delta, a.area) > a.tol);
+                if (rel < 0.125f && m < 3.0e38f && yes)
+                    active = true;
+                else if (rel < 0.125f && m < 3.0e38f && no)
+                    active = false;
+                else
+                    active = block_active_exact<true>(a, n, bh, bw);
+            }
+        } else if (b < nBlk) {
+            // a band with no in-range row: empty window => max: inactive; avg: 0/area > tol
+            active = AVG ? (__fdiv_rn(0.0f, a.area) > a.tol) : false;
+        }
+        append_active(a, active, n, bh, bw);
+    }
+    finish(a, gridDim.x * gridDim.y * gridDim.z);
+}
+
+// Fallback for windows wider than a CTA can stage: one thread per block, reference order.
+template <bool AVG>
+__global__ void __launch_bounds__(kRmThreads) reduce_mask_naive(const RmArgs a)
+{
+    const long long total = (long long)a.N * a.bCntH * a.bCntW;
+    const long long stride = (long long)gridDim.x * kRmThreads;
+    const long long rounds = (total + stride - 1) / stride;
+    for (long long r = 0; r < rounds; ++r) {
+        const long long i = r * stride + (long long)blockIdx.x * kRmThreads + threadIdx.x;
+        bool active = false;
+        int n = 0, bh = 0, bw = 0;
+        if (i < total) {
+            bw = (int)(i % a.bCntW);
+            bh = (int)((i / a.bCntW) % a.bCntH);
+            n = (int)(i / ((long long)a.bCntW * a.bCntH));
+            active = block_active_exact<AVG>(a, n, bh, bw);
+        }
+        append_active(a, active, n, bh, bw);
+    }
+    finish(a, gridDim.x);
+}
+
+cudaError_t launch_reduce_mask(const float* mask, int N, int H, int W, float tol, bool avgpool,
+                               int bOffsH, int bOffsW, int bSzH, int bSzW, int bStrH, int bStrW,
+                               int bCntH, int bCntW, int16_t* idx, int32_t* scratch,
+                               int32_t* host_count_dev, cudaStream_t stream)
+{
+    RmArgs a;
+    a.mask = mask, a.idx = idx, a.scratch = scratch, a.host_count = host_count_dev;
+    a.N = N, a.H = H, a.W = W, a.tol = tol;
+    a.bOffsH = bOffsH, a.bOffsW = bOffsW, a.bSzH = bSzH, a.bSzW = bSzW;
+    a.bStrH = bStrH, a.bStrW = bStrW, a.bCntH = bCntH, a.bCntW = bCntW;
+    a.area = (float)(bSzH * bSzW);
+
+    // widest run of block columns whose pixel span (plus 4-column rounding) fits the staging area
+    const long long spare = (long long)kRmMaxCols - 8 - bSzW;
+    if (spare >= 0) {
+        long long tb = spare / bStrW + 1;
+        a.tileBlocks = (int)(tb < bCntW ? tb : bCntW);
+        const dim3 grid((bCntW + a.tileBlocks - 1) / a.tileBlocks, bCntH, N);
+        const bool vec4 = (W % 4 == 0) && ((reinterpret_cast<uintptr_t>(mask) & 15) == 0);
+        if (avgpool) {
+            if (vec4)
+                reduce_mask_band<true, true><<<grid, kRmThreads, 0, stream>>>(a);
+            else
+                reduce_mask_band<true, false><<<grid, kRmThreads, 0, stream>>>(a);
+        } else {
+            if (vec4)
+                reduce_mask_band<false, true><<<grid, kRmThreads, 0, stream>>>(a);
+            else
+                reduce_mask_band<false, false><<<grid, kRmThreads, 0, stream>>>(a);
+        }
+    } else {
+        a.tileBlocks = 1;
+        const long long total = (long long)N * bCntH * bCntW;
+        const int grid = (int)((total + kRmThreads - 1) / kRmThreads < 1184
+                                   ? (total + kRmThreads - 1) / kRmThreads
+                                   : 1184);
+        if (avgpool)
+            reduce_mask_naive<true><<<grid, kRmThreads, 0, stream>>>(a);
+        else
+            reduce_mask_naive<false><<<grid, kRmThreads, 0, stream>>>(a);
+    }
+    return cudaGetLastError();
+}
+
+} // namespace sbnet

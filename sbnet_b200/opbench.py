@@ -1,0 +1,170 @@
+"""Op-level measurements behind ``bench.py --suite ops``: one JSON line per case.
+
+Cases are the op-level benchmark configurations: reduce_mask on a bird's-eye-view sized mask
+([8,800,704], avg and max pooling), sparse_gather on x [8,512,512,128] (fp32 / fp16, both layouts,
+5 / 20 / 50 % active blocks) and sparse_scatter[_var] (fp32 atomic add with overlapping halos onto
+[8,512,512,64]; fp16 transposed overwrite).  Every launch is timed on its own with CUDA events on the
+launching stream after an L2 flush (a 256 MiB fill), so small cases are measured from DRAM; the
+median is reported with the algorithmic bytes of the call and the fraction of the HBM peak.
+"""
+from __future__ import annotations
+
+import json
+import statistics
+
+import numpy as np
+
+from . import configs as cfg
+
+
+def _peak():
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class Timer:
+    def __init__(self, torch, dev, steps, warmup):
+        self.t, self.dev, self.steps, self.warmup = torch, dev, steps, warmup
+        self.flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+    def run(self, fn, flush=True):
+        t = self.t
+        for _ in range(self.warmup):
+            fn()
+        t.cuda.synchronize()
+        pairs = []
+        for _ in range(self.steps):
+            if flush:
+                self.flush_buf.fill_(1)
+            a, b = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            pairs.append((a, b))
+        t.cuda.synchronize()
+        ms = [a.elapsed_time(b) for a, b in pairs]
+        return statistics.median(ms), min(ms)
+
+
+def emit(name, med_ms, min_ms, nbytes, extra):
+    peak, kind = _peak()
+    gbs = nbytes / (med_ms * 1e-3) / 1e9
+    line = {"case": name, "us": med_ms * 1e3, "us_min": min_ms * 1e3, "algorithmic_bytes": int(nbytes),
+            "GB/s": gbs, "frac_of_" + kind: gbs / peak, "peak_GB/s": peak}
+    line.update(extra)
+    print(json.dumps(line), flush=True)
+
+
+def main(args):
+    import torch
+    from . import build, ops
+    build.build_library()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    tm = Timer(torch, dev, max(args.steps, 5), max(args.warmup, 3))
+
+    # ---- reduce_mask, bird's-eye-view scale ----
+    c2 = cfg.config2(0)
+    g = c2["geom"]
+    masks = [torch.from_numpy(c2["mask"]).to(dev) for _ in range(8)]
+    occ = float(c2["mask"].mean())
+    for run in c2["runs"]:
+        idx, cnt = ops.reduce_mask(masks[0], *g.as_lists(), tol=run["tol"], avgpool=run["avgpool"])
+        nb = int(cnt[0])
+        nbytes = cfg.algorithmic_bytes("reduce_mask", nB=nb, geom=g, C=1, itemsize=4, U=0, N=8, H=800,
+                                       W=704, count=nb)
+        tag = "avg" if run["avgpool"] else "max"
+        med, mn = tm.run(lambda: ops.reduce_mask_async(masks[0], *g.as_lists(), tol=run["tol"],
+                                                       avgpool=run["avgpool"]))
+        emit(f"reduce_mask_{tag}_kernel", med, mn, nbytes, {"active": nb, "occupancy": occ})
+        med, mn = tm.run(lambda: ops.reduce_mask(masks[0], *g.as_lists(), tol=run["tol"],
+                                                 avgpool=run["avgpool"]))
+        emit(f"reduce_mask_{tag}_with_count_readback", med, mn, nbytes, {"active": nb})
+        # back to back over rotating copies (144 MB of masks > L2), no flush: launch-amortised figure
+        k = [0]
+
+        def rot():
+            k[0] += 1
+            ops.reduce_mask_async(masks[k[0] % 8], *g.as_lists(), tol=run["tol"], avgpool=run["avgpool"])
+        for _ in range(8):
+            rot()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(64):
+            rot()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / 64
+        emit(f"reduce_mask_{tag}_back_to_back", ms, ms, nbytes, {"active": nb, "launches": 64})
+    del masks
+
+    # ---- sparse_gather on [8,512,512,128] ----
+    N, H, W, C = 8, 512, 512, 128
+    g = cfg.halo_geom(H, W)
+    for dtype, tname in ((torch.float32, "f32"), (torch.float16, "f16")):
+        x = torch.randn((N, H, W, C), device=dev, dtype=torch.float32).to(dtype)
+        for dens in (0.05, 0.20, 0.50):
+            idx_h, cnt_h = cfg.random_block_list(N, g.bcount, dens, seed=int(dens * 100))
+            nb = int(cnt_h[0])
+            U = cfg.union_pixels(idx_h, nb, g, N, H, W)
+            idx, cnt = torch.from_numpy(idx_h).to(dev), torch.from_numpy(cnt_h)
+            nbytes = cfg.algorithmic_bytes("gather", nB=nb, geom=g, C=C, itemsize=x.element_size(), U=U)
+            for tr in (False, True):
+                shape = (nb, C, 18, 18) if tr else (nb, 18, 18, C)
+                out = torch.empty(shape, dtype=dtype, device=dev)
+                med, mn = tm.run(lambda: ops.sparse_gather(x, cnt, idx, g.bsize, g.bstride, g.boffset,
+                                                           transpose=tr, out=out))
+                emit(f"gather_{tname}_t{int(tr)}_d{int(dens*100)}", med, mn, nbytes,
+                     {"blocks": nb, "blocks/s": nb / (med * 1e-3)})
+                del out
+        del x
+
+    # ---- sparse_scatter on [8,512,512,64] ----
+    C = 64
+    for dens in (0.05, 0.20, 0.50):
+        idx_h, cnt_h = cfg.random_block_list(N, g.bcount, dens, seed=int(dens * 100) + 1)
+        nb = int(cnt_h[0])
+        idx, cnt = torch.from_numpy(idx_h).to(dev), torch.from_numpy(cnt_h)
+        # (a) fp32 atomic add with overlapping halos, Var (in place) and non-Var (copy + scatter)
+        U = cfg.union_pixels(idx_h, nb, g, N, H, W)
+        base = torch.randn((N, H, W, C), device=dev)
+        stack = torch.randn((nb, 18, 18, C), device=dev)
+        nbytes = cfg.algorithmic_bytes("scatter_add", nB=nb, geom=g, C=C, itemsize=4, U=U)
+        med, mn = tm.run(lambda: ops.sparse_scatter_var(stack, cnt, idx, base, g.bsize, g.bstride,
+                                                        g.boffset, add=True, atomic=True))
+        emit(f"scatter_var_f32_atomic_d{int(dens*100)}", med, mn, nbytes,
+             {"blocks": nb, "blocks/s": nb / (med * 1e-3)})
+        ybuf = torch.empty_like(base)
+
+        def nonvar():
+            ops.copy_tensor(ybuf, base)
+            ops.sparse_scatter_var(stack, cnt, idx, ybuf, g.bsize, g.bstride, g.boffset, add=True,
+                                   atomic=True)
+        med, mn = tm.run(nonvar)
+        emit(f"scatter_f32_atomic_d{int(dens*100)}", med, mn,
+             nbytes + cfg.algorithmic_bytes("scatter_copy", nB=0, geom=g, C=C, itemsize=4, U=0, N=N, H=H, W=W),
+             {"blocks": nb, "blocks/s": nb / (med * 1e-3)})
+        del base, stack, ybuf
+        # (b) fp16 transposed overwrite, 16x16 disjoint blocks
+        gi = cfg.inner_geom(H, W)
+        U = cfg.union_pixels(idx_h, nb, gi, N, H, W)
+        base = torch.randn((N, H, W, C), device=dev).half()
+        stack = torch.randn((nb, C, 16, 16), device=dev).half()
+        nbytes = cfg.algorithmic_bytes("scatter", nB=nb, geom=gi, C=C, itemsize=2, U=U)
+        med, mn = tm.run(lambda: ops.sparse_scatter_var(stack, cnt, idx, base, gi.bsize, gi.bstride,
+                                                        gi.boffset, add=False, transpose=True))
+        emit(f"scatter_var_f16_t1_set_d{int(dens*100)}", med, mn, nbytes,
+             {"blocks": nb, "blocks/s": nb / (med * 1e-3)})
+        del base, stack
+
+    # ---- plain copy (the non-Var op's base copy) ----
+    a = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
+    b = torch.empty_like(a)
+    med, mn = tm.run(lambda: ops.copy_tensor(b, a))
+    emit("copy_tensor_1GiB", med, mn, 2 << 30, {})

@@ -1,0 +1,237 @@
+"""The reference's op interface on torch CUDA tensors, backed by the C ABI.
+
+Names, argument order and meaning follow the registered TensorFlow ops
+(``sbnet_ops/reduce_mask.cc:100-110``, ``sbnet_ops/sparse_gather.cc:48-57,242-268``) as the reference's
+callers use them (``benchmark/sparse_conv_lib.py:452-459,547-587``): geometry is passed as length-2
+``[H, W]`` host sequences, ``bin_counts`` is a length-1 int32 HOST tensor, ``active_block_indices`` is
+a ``[N*bCntH*bCntW, 3]`` int16 device tensor.  torch is used for device memory and the current stream
+only; every computation happens in ``libsbnet_b200.so``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from collections import namedtuple
+from typing import Sequence
+
+import torch
+
+from . import lib as _lib
+
+ReduceMaskResult = namedtuple("ReduceMask", ["active_block_indices", "bin_counts"])
+
+_DTYPES = {torch.float32: _lib.SBNET_F32, torch.float16: _lib.SBNET_F16}
+_scratch: dict = {}
+
+
+def _pair(v, name) -> tuple:
+    if isinstance(v, torch.Tensor):
+        v = v.detach().cpu().tolist()
+    v = list(v)
+    if len(v) != 2:  # reduce_mask.cc:132-138, sparse_gather.cc:170-175
+        raise ValueError(f"{name} should be one-dimensional with shape[0] == 2.")
+    return int(v[0]), int(v[1])
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (there is no CPU path in this library)")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def _count(bin_counts) -> int:
+    if isinstance(bin_counts, torch.Tensor):
+        if bin_counts.is_cuda:
+            raise ValueError("bin_counts lives in host memory (use the *_dyn functions for a device count)")
+        return int(bin_counts.reshape(-1)[0])
+    return int(list(bin_counts)[0]) if not isinstance(bin_counts, int) else int(bin_counts)
+
+
+def scratch_for(device, stream: int) -> tuple:
+    """Per (device, stream) reduce_mask scratch, zero-filled once; later calls pass SCRATCH_CLEAN."""
+    key = (torch.device(device).index, stream)
+    hit = _scratch.get(key)
+    if hit is None:
+        buf = torch.zeros(_lib.SBNET_REDUCE_MASK_SCRATCH_INTS, dtype=torch.int32, device=device)
+        _scratch[key] = buf
+        return buf, 0
+    return hit, _lib.SBNET_SCRATCH_CLEAN
+
+
+def reduce_mask(mask: torch.Tensor, dynamic_bcount: Sequence[int], dynamic_bsize: Sequence[int],
+                dynamic_bstride: Sequence[int], dynamic_boffset: Sequence[int], tol: float,
+                avgpool: bool = False) -> ReduceMaskResult:
+    """``ReduceMask``: pools ``mask`` ([N,H,W,1] or [N,H,W] fp32) per block and lists the active blocks.
+
+    Returns ``(active_block_indices, bin_counts)``; ``bin_counts`` is a pinned host tensor whose value
+    is final when the call returns (the op interface requires the count on the host)."""
+    _require_cuda(mask, "mask")
+    if mask.dtype != torch.float32:
+        raise ValueError("mask must be float32")
+    if mask.dim() == 4 and mask.shape[3] != 1 or mask.dim() not in (3, 4):
+        raise ValueError("mask must be [N,H,W,1]")
+    N, H, W = mask.shape[0], mask.shape[1], mask.shape[2]
+    bch, bcw = _pair(dynamic_bcount, "dynamic_bcount")
+    bsh, bsw = _pair(dynamic_bsize, "dynamic_bsize")
+    bth, btw = _pair(dynamic_bstride, "dynamic_bstride")
+    boh, bow = _pair(dynamic_boffset, "dynamic_boffset")
+    with torch.cuda.device(mask.device):
+        stream = _stream(mask.device)
+        idx = torch.empty((max(N * bch * bcw, 0), 3), dtype=torch.int16, device=mask.device)
+        counts = torch.empty(1, dtype=torch.int32, pin_memory=True)
+        scratch, flags = scratch_for(mask.device, stream)
+        _lib.check(_lib.load().sbnet_reduce_mask(
+            mask.data_ptr(), N, H, W, float(tol), int(bool(avgpool)), boh, bow, bsh, bsw, bth, btw,
+            bch, bcw, idx.data_ptr(), scratch.data_ptr(), counts.data_ptr(), flags, stream))
+    return ReduceMaskResult(idx, counts)
+
+
+def reduce_mask_async(mask, dynamic_bcount, dynamic_bsize, dynamic_bstride, dynamic_boffset, tol,
+                      avgpool=False):
+    """Same as :func:`reduce_mask` but never touches the host: returns ``(active_block_indices,
+    count_dev)`` where ``count_dev`` is a device int32 view holding the count in stream order, for
+    the ``*_dyn`` gather / scatter calls."""
+    _require_cuda(mask, "mask")
+    N, H, W = mask.shape[0], mask.shape[1], mask.shape[2]
+    bch, bcw = _pair(dynamic_bcount, "dynamic_bcount")
+    bsh, bsw = _pair(dynamic_bsize, "dynamic_bsize")
+    bth, btw = _pair(dynamic_bstride, "dynamic_bstride")
+    boh, bow = _pair(dynamic_boffset, "dynamic_boffset")
+    with torch.cuda.device(mask.device):
+        stream = _stream(mask.device)
+        idx = torch.empty((N * bch * bcw, 3), dtype=torch.int16, device=mask.device)
+        scratch, flags = scratch_for(mask.device, stream)
+        _lib.check(_lib.load().sbnet_reduce_mask(
+            mask.data_ptr(), N, H, W, float(tol), int(bool(avgpool)), boh, bow, bsh, bsw, bth, btw,
+            bch, bcw, idx.data_ptr(), scratch.data_ptr(), None, flags, stream))
+    return idx, scratch[:1]
+
+
+def _geom(dynamic_bsize, dynamic_bstride, dynamic_boffset):
+    bsh, bsw = _pair(dynamic_bsize, "dynamic_bsize")
+    bth, btw = _pair(dynamic_bstride, "dynamic_bstride")
+    boh, bow = _pair(dynamic_boffset, "dynamic_boffset")
+    return (boh, bow, bsh, bsw, bth, btw)
+
+
+def sparse_gather(x: torch.Tensor, bin_counts, active_block_indices: torch.Tensor, dynamic_bsize,
+                  dynamic_bstride, dynamic_boffset, transpose: bool = False, out=None) -> torch.Tensor:
+    """``SparseGather``: ``[bin_counts[0], bSzH, bSzW, C]``, or ``[bin_counts[0], C, bSzH, bSzW]`` when
+    ``transpose``; pixels outside ``x`` read as zero."""
+    _require_cuda(x, "x")
+    if x.dim() != 4:  # sparse_gather.cc:164
+        raise ValueError("x must be rank 4")
+    if x.dtype not in _DTYPES:
+        raise ValueError(f"unsupported dtype {x.dtype}")
+    _require_cuda(active_block_indices, "active_block_indices")
+    N, H, W, Cc = x.shape
+    g = _geom(dynamic_bsize, dynamic_bstride, dynamic_boffset)
+    nb = _count(bin_counts)
+    shape = (nb, Cc, g[2], g[3]) if transpose else (nb, g[2], g[3], Cc)
+    with torch.cuda.device(x.device):
+        y = out if out is not None else torch.empty(shape, dtype=x.dtype, device=x.device)
+        _lib.check(_lib.load().sbnet_sparse_gather(
+            x.data_ptr(), _DTYPES[x.dtype], N, H, W, Cc, y.data_ptr(), *g, nb,
+            active_block_indices.data_ptr(), int(bool(transpose)), _stream(x.device)))
+    return y
+
+
+def sparse_scatter_var(x: torch.Tensor, bin_counts, active_block_indices: torch.Tensor,
+                       ybase: torch.Tensor, dynamic_bsize, dynamic_bstride, dynamic_boffset,
+                       add: bool, atomic: bool = False, transpose: bool = False) -> torch.Tensor:
+    """``SparseScatterVar``: writes (``add=False``) or accumulates (``add=True``) the block stack ``x``
+    into ``ybase`` in place and returns it."""
+    _require_cuda(x, "x")
+    _require_cuda(ybase, "ybase")
+    _require_cuda(active_block_indices, "active_block_indices")
+    if ybase.dim() != 4:  # sparse_gather.cc:327
+        raise ValueError("ybase must be rank 4")
+    if ybase.dtype not in _DTYPES or x.dtype != ybase.dtype:
+        raise ValueError("x and ybase must share a supported dtype")
+    N, H, W, Cc = ybase.shape
+    g = _geom(dynamic_bsize, dynamic_bstride, dynamic_boffset)
+    nb = _count(bin_counts)
+    if x.numel() != nb * g[2] * g[3] * Cc:
+        raise ValueError("x must hold bin_counts[0]*bsize[0]*bsize[1]*C elements")
+    with torch.cuda.device(ybase.device):
+        _lib.check(_lib.load().sbnet_sparse_scatter(
+            x.data_ptr(), _DTYPES[ybase.dtype], N, H, W, Cc, ybase.data_ptr(), *g, nb,
+            active_block_indices.data_ptr(), int(bool(add)), int(bool(transpose)),
+            int(bool(atomic)), _stream(ybase.device)))
+    return ybase
+
+
+def copy_tensor(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
+    _require_cuda(dst, "dst")
+    _require_cuda(src, "src")
+    nbytes = src.numel() * src.element_size()
+    if dst.numel() * dst.element_size() != nbytes:
+        raise ValueError("size mismatch")
+    with torch.cuda.device(dst.device):
+        _lib.check(_lib.load().sbnet_copy_tensor(dst.data_ptr(), src.data_ptr(), nbytes,
+                                                 _stream(dst.device)))
+    return dst
+
+
+def sparse_scatter(x, bin_counts, active_block_indices, ybase, dynamic_bsize, dynamic_bstride,
+                   dynamic_boffset, add: bool, atomic: bool = False, transpose: bool = False):
+    """``SparseScatter``: like :func:`sparse_scatter_var` on a fresh copy of ``ybase``
+    (``sbnet_ops/sparse_gather.cc:338-347``)."""
+    _require_cuda(ybase, "ybase")
+    if ybase.dim() != 4:
+        raise ValueError("ybase must be rank 4")
+    g = _geom(dynamic_bsize, dynamic_bstride, dynamic_boffset)
+    if add and not atomic and not (g[4] >= g[2] and g[5] >= g[3]):  # reject before allocating
+        raise ValueError("SparseScatter: Only non-overlapping blocks are supported with add=True, atomic=False")
+    y = copy_tensor(torch.empty_like(ybase), ybase)
+    return sparse_scatter_var(x, bin_counts, active_block_indices, y, dynamic_bsize, dynamic_bstride,
+                              dynamic_boffset, add=add, atomic=atomic, transpose=transpose)
+
+
+def sparse_gather_dyn(x, count_dev: torch.Tensor, max_blocks: int, active_block_indices, dynamic_bsize,
+                      dynamic_bstride, dynamic_boffset, transpose=False, out=None):
+    """Gather with the block count read on the device (no host synchronisation).  The result has
+    room for ``max_blocks`` blocks; only the first ``count_dev[0]`` are written."""
+    _require_cuda(x, "x")
+    N, H, W, Cc = x.shape
+    g = _geom(dynamic_bsize, dynamic_bstride, dynamic_boffset)
+    shape = (max_blocks, Cc, g[2], g[3]) if transpose else (max_blocks, g[2], g[3], Cc)
+    with torch.cuda.device(x.device):
+        y = out if out is not None else torch.empty(shape, dtype=x.dtype, device=x.device)
+        _lib.check(_lib.load().sbnet_sparse_gather_dyn(
+            x.data_ptr(), _DTYPES[x.dtype], N, H, W, Cc, y.data_ptr(), *g, int(max_blocks),
+            count_dev.data_ptr(), active_block_indices.data_ptr(), int(bool(transpose)),
+            _stream(x.device)))
+    return y
+
+
+def sparse_scatter_var_dyn(x, count_dev: torch.Tensor, max_blocks: int, active_block_indices, ybase,
+                           dynamic_bsize, dynamic_bstride, dynamic_boffset, add, atomic=False,
+                           transpose=False):
+    _require_cuda(ybase, "ybase")
+    N, H, W, Cc = ybase.shape
+    g = _geom(dynamic_bsize, dynamic_bstride, dynamic_boffset)
+    with torch.cuda.device(ybase.device):
+        _lib.check(_lib.load().sbnet_sparse_scatter_dyn(
+            x.data_ptr(), _DTYPES[ybase.dtype], N, H, W, Cc, ybase.data_ptr(), *g, int(max_blocks),
+            count_dev.data_ptr(), active_block_indices.data_ptr(), int(bool(add)),
+            int(bool(transpose)), int(bool(atomic)), _stream(ybase.device)))
+    return ybase
+
+
+def cuda_timer_start() -> int:
+    """``CudaTimerStart``: returns an event handle (``sbnet_ops/sparse_gather.cc:398-423``)."""
+    h = C.c_int64(0)
+    _lib.check(_lib.load().sbnet_cuda_timer_start(C.byref(h)))
+    return h.value
+
+
+def cuda_timer_end(handle: int) -> float:
+    """``CudaTimerEnd``: milliseconds since the matching start (``sbnet_ops/sparse_gather.cc:425-461``)."""
+    ms = C.c_float(0.0)
+    _lib.check(_lib.load().sbnet_cuda_timer_end(C.c_int64(handle), C.byref(ms)))
+    return ms.value

@@ -30,3 +30,14 @@ def oracle_ref():
     if not oracle.have_ref():
         pytest.skip("reference CPU functors not built (no reference tree and no prebuilt library)")
     return oracle.get("ref")
+
+
+@pytest.fixture(scope="session")
+def cuda_ops():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from sbnet_b200 import build
+    build.build_library()
+    from cuda_ops import CudaOps
+    return CudaOps("cuda:0")
