@@ -139,6 +139,14 @@ int sbnet_copy_tensor(void* dst, const void* src, size_t bytes, void* stream);
 int sbnet_cuda_timer_start(int64_t* handle);
 int sbnet_cuda_timer_end(int64_t handle, float* elapsed_ms);
 
+/*
+ * Diagnostic with no counterpart in the reference: the TMA-pipelined kernels bound every wait on a
+ * shared-memory barrier (about a second); a wait that gives up makes its thread block drain and
+ * return, and is counted here.  *count stays 0 in a healthy process; a non-zero value means some
+ * output was left incomplete.  Synchronises the device.
+ */
+int sbnet_wait_timeouts(unsigned int* count);
+
 #ifdef __cplusplus
 }
 #endif

@@ -242,3 +242,10 @@ SBNET_EXPORT int sbnet_cuda_timer_end(int64_t handle, float* elapsed_ms)
     cudaEventDestroy(start);
     return cuda_status(e);
 }
+
+SBNET_EXPORT int sbnet_wait_timeouts(unsigned int* count)
+{
+    if (count == nullptr)
+        return reject(SBNET_ERR_INVALID_ARGUMENT, "sbnet_wait_timeouts: null output");
+    return cuda_status(sbnet::read_wait_timeouts(count));
+}

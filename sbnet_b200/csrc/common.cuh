@@ -155,6 +155,24 @@ template <> struct Red<__half> {
 
 enum Mode : int { kGather = 0, kScatterSet = 1, kScatterAdd = 2, kScatterAtomic = 3 };
 
+template <int VB> __device__ __forceinline__ typename Vec<VB>::type ld_plain(const typename Vec<VB>::type* p)
+{
+    return *p;
+}
+
+// Applies one vector to the image in the given scatter mode.
+template <int VB, int MODE, typename T>
+__device__ __forceinline__ void image_write(typename Vec<VB>::type* dst, typename Vec<VB>::type v,
+                                            typename Vec<VB>::type old)
+{
+    if constexpr (MODE == kScatterSet)
+        *dst = v;
+    else if constexpr (MODE == kScatterAdd)
+        *dst = vadd<T>(old, v);
+    else
+        Red<T>::add(dst, v);
+}
+
 // Geometry + buffers shared by the gather and scatter launches.  `image` is the NHWC tensor,
 // `stack` the block stack ([nB,R,S,C], or [nB,C,R,S] when transposed).
 struct BlockArgs {

@@ -37,24 +37,6 @@ __device__ __forceinline__ int active_count(const BlockArgs& a)
     return n < a.numActive ? n : a.numActive;
 }
 
-template <int VB> __device__ __forceinline__ typename Vec<VB>::type ld_plain(const typename Vec<VB>::type* p)
-{
-    return *p;
-}
-
-// Applies one vector to the image in the given scatter mode.
-template <int VB, int MODE, typename T>
-__device__ __forceinline__ void image_write(typename Vec<VB>::type* dst, typename Vec<VB>::type v,
-                                            typename Vec<VB>::type old)
-{
-    if constexpr (MODE == kScatterSet)
-        *dst = v;
-    else if constexpr (MODE == kScatterAdd)
-        *dst = vadd<T>(old, v);
-    else
-        Red<T>::add(dst, v);
-}
-
 // ---- [nB,R,S,C] layout ---------------------------------------------------------------------------
 struct RowPlan {
     FastDiv vecsPerRow;     // S * C * sizeof(T) / VB
@@ -391,6 +373,13 @@ cudaError_t launch_blocks(const BlockArgs& a, int dtype, int mode, bool transpos
     if (a.numActive <= 0)
         return cudaSuccess;
     const int itemsize = dtype == 0 ? 4 : 2;
+    if (transpose) {   // aligned shapes: the TMA pipeline
+        bool taken = false;
+        if (cudaError_t e = launch_planes_tma(a, dtype, mode, stream, &taken))
+            return e;
+        if (taken)
+            return cudaSuccess;
+    }
     const int vb = pick_vector_bytes(a, itemsize);
     if (dtype == 0)
         dispatch_mode<float>(a, mode, transpose, vb, stream);

@@ -18,6 +18,12 @@ cudaError_t launch_reduce_mask(const float* mask, int N, int H, int W, float tol
 cudaError_t launch_blocks(const BlockArgs& a, int dtype, int mode, bool transpose,
                           cudaStream_t stream);
 
+// Plane-layout fast path (TMA pipeline); *taken tells whether it accepted the call.
+cudaError_t launch_planes_tma(const BlockArgs& a, int dtype, int mode, cudaStream_t stream, bool* taken);
+
+// Bounded device-side waits that gave up since the library was loaded (0 in a healthy process).
+cudaError_t read_wait_timeouts(unsigned int* out);
+
 cudaError_t launch_copy(void* dst, const void* src, size_t bytes, cudaStream_t stream);
 
 int sm_count();

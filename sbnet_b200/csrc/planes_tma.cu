@@ -1,0 +1,557 @@
+// Transposed ([nB,C,R,S]) gather and scatter as TMA pipelines (sm_100a).
+//
+// Fast path of the plane-layout ops for the shapes that matter at scale: C*sizeof(T) a multiple of
+// 128 bytes and blocks of at most 384 pixels.  Everything else runs the general kernels of
+// gather_scatter.cu.  Semantics are identical (reference: sbnet_ops/sparse_gather.cc:61-132,
+// transposed branches of sbnet_ops/sparse_blocks.cu.h:135-171 and :217-251).
+//
+// One persistent CTA per SM: a producer warp keeps a ring of shared-memory stages filled through
+// the async proxy, eight consumer warps transpose out of them.  A work item is one active block x
+// one 128-byte channel chunk, i.e. a tile of P = R*S pixels x 128 bytes.
+//
+//  gather : the producer issues ONE tiled TMA load per item from the NHWC image, box
+//           (128 B of channels, S, R); coordinates may start before 0 or run past the image and the
+//           TMA unit zero-fills there, which is exactly the op's padding rule.  The stage uses the
+//           128-byte swizzle, so consumers read 16-byte channel groups without bank conflicts,
+//           regroup them into words of one channel (1 fp32 pixel or 2 fp16 pixels), and build the
+//           tile in [channel][pixel] order in a second stage, which leaves as ONE bulk store: the
+//           channel planes of a chunk are contiguous in the stack.
+//  scatter: the producer issues ONE 1-D bulk load per item (the chunk's planes are contiguous),
+//           consumers regroup words into 16-byte channel groups and write / add / reduce them into
+//           the image with a per-pixel in-range test.  For the read-add-write mode every thread
+//           first issues all of its destination loads for the tile, so the SM keeps ~50 KB of image
+//           reads in flight despite running a single CTA.
+//
+// Every wait on an mbarrier is bounded (about a second of SM clock); a wait that gives up raises a
+// CTA-wide abort flag, counts itself in g_wait_timeouts, and the CTA drains and returns.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <stdlib.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace sbnet {
+
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumers = kConsumerWarps * 32;
+constexpr int kTmaThreads = kConsumers + 32;
+constexpr int kMaxPixels = 384;                     // 48 KB stages
+constexpr long long kWaitCycles = 1ll << 31;        // ~1.1 s at 1.9 GHz
+
+__device__ unsigned int g_wait_timeouts = 0;
+
+struct TmaPlan {
+    FastDiv cChunks;      // 128-byte channel chunks per pixel
+    FastDiv blockW;       // S
+    int pixels;           // P = R*S
+    int units;            // 32-bit words per channel plane row: P (fp32) or P/2 (fp16)
+    int tileBytes;        // 128 * P
+    int inStages, outStages;
+    int inStageBytes, outStageBytes;
+};
+
+// ---- PTX wrappers -------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p)
+{
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  false: gave up (or another role of this CTA did).
+__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abortFlag)
+{
+    const long long t0 = clock64();
+    for (uint32_t i = 0;; ++i) {
+        if (mbar_try_wait(bar, parity))
+            return true;
+        if ((i & 31u) == 31u) {
+            if (*abortFlag)
+                return false;
+            if (clock64() - t0 > kWaitCycles)
+                break;
+        }
+    }
+    atomicAdd(&g_wait_timeouts, 1u);
+    *abortFlag = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                            int c3, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+        "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_store_1d(void* dst, uint32_t src, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N> __device__ __forceinline__ void bulk_wait_read()
+{
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all()
+{
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ void fence_async_smem()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// Barrier among the consumer warps only (the producer warp never joins), with an OR vote.
+__device__ __forceinline__ bool consumers_any(bool pred)
+{
+    uint32_t out;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.or.pred p, 1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(out)
+        : "r"((uint32_t)pred), "n"(kConsumers)
+        : "memory");
+    return out != 0;
+}
+__device__ __forceinline__ void consumers_sync()
+{
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v)
+{
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
+struct Ring {
+    uint32_t in0, out0, full0, empty0;   // shared-space addresses
+};
+
+// Carves the dynamic shared memory: swizzled input stages need 1024-byte alignment.
+__device__ __forceinline__ Ring carve(unsigned char* dyn, const TmaPlan& p)
+{
+    Ring r;
+    r.in0 = (smem_u32(dyn) + 1023u) & ~1023u;
+    r.out0 = r.in0 + (uint32_t)p.inStages * p.inStageBytes;
+    r.full0 = r.out0 + (uint32_t)p.outStages * p.outStageBytes;
+    r.empty0 = r.full0 + 8u * p.inStages;
+    return r;
+}
+
+__device__ __forceinline__ void ring_init(const Ring& r, const TmaPlan& p, int* abortFlag)
+{
+    if (threadIdx.x == 0) {
+        *abortFlag = 0;
+        for (int s = 0; s < p.inStages; ++s) {
+            mbar_init(r.full0 + 8u * s, 1);
+            mbar_init(r.empty0 + 8u * s, kConsumerWarps);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ int device_count(const BlockArgs& a)
+{
+    if (a.num_active_dev == nullptr)
+        return a.numActive;
+    const int n = __ldg(a.num_active_dev);
+    return n < a.numActive ? n : a.numActive;
+}
+
+// ---- gather -------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kTmaThreads, 1)
+planes_gather_tma(const __grid_constant__ CUtensorMap imageMap, const BlockArgs a, const TmaPlan p)
+{
+    extern __shared__ unsigned char dynSmem[];
+    __shared__ int abortFlag;
+    constexpr int EPW = 4 / (int)sizeof(T);        // pixels per 32-bit word of a channel plane
+    constexpr int CPG = 16 / (int)sizeof(T);       // channels per 16-byte group
+    const Ring ring = carve(dynSmem, p);
+    ring_init(ring, p, &abortFlag);
+
+    const long long nItems = (long long)device_count(a) * p.cChunks.div;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (warp == kConsumerWarps) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            int k = 0;
+            for (long long item = blockIdx.x; item < nItems; item += gridDim.x, ++k) {
+                const int s = k % p.inStages;
+                const uint32_t parity = (uint32_t)(k / p.inStages) & 1u;
+                if (!mbar_wait(ring.empty0 + 8u * s, parity ^ 1u, &abortFlag))
+                    break;
+                uint32_t ib, cc;
+                p.cChunks.divmod((uint32_t)item, ib, cc);
+                const int n = a.idx[ib * 3 + 0];
+                const int h0 = a.bOffsH + a.idx[ib * 3 + 1] * a.bStrH;
+                const int w0 = a.bOffsW + a.idx[ib * 3 + 2] * a.bStrW;
+                mbar_expect_tx(ring.full0 + 8u * s, (uint32_t)p.tileBytes);
+                tma_load_4d(ring.in0 + (uint32_t)s * p.inStageBytes, &imageMap,
+                            (int)cc * (128 / (int)sizeof(T)), w0, h0, n, ring.full0 + 8u * s);
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    T* stack = reinterpret_cast<T*>(a.stack);
+    const int U = p.units;
+    const int nTasks = ((U + 15) >> 4) * 128;
+    int k = 0;
+    bool failed = false;
+    for (long long item = blockIdx.x; item < nItems; item += gridDim.x, ++k) {
+        const int s = k % p.inStages, o = k % p.outStages;
+        const uint32_t parity = (uint32_t)(k / p.inStages) & 1u;
+        int ok = 1;
+        if (lane == 0)
+            ok = mbar_wait(ring.full0 + 8u * s, parity, &abortFlag) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);   // reconverges the warp before the CTA-level vote
+        if (consumers_any(ok == 0)) {   // also orders: thread 0 has drained the store that used out[o]
+            failed = true;
+            break;
+        }
+        const uint32_t in = ring.in0 + (uint32_t)s * p.inStageBytes;
+        const uint32_t out = ring.out0 + (uint32_t)o * p.outStageBytes;
+        for (int t = threadIdx.x; t < nTasks; t += kConsumers) {
+            const int uLocal = t & 15, grp = t >> 4;
+            const int j = grp & 7, u = ((grp >> 3) << 4) + uLocal;
+            if (u >= U)
+                continue;
+            if constexpr (EPW == 2) {
+                const int r0 = 2 * u, r1 = 2 * u + 1;
+                const uint4 A = lds128(in + r0 * 128 + ((j ^ (r0 & 7)) << 4));
+                const uint4 B = lds128(in + r1 * 128 + ((j ^ (r1 & 7)) << 4));
+                const uint32_t base = out + ((uint32_t)(CPG * j) * U + u) * 4u;
+                sts32(base + 0u * U * 4u, __byte_perm(A.x, B.x, 0x5410));
+                sts32(base + 1u * U * 4u, __byte_perm(A.x, B.x, 0x7632));
+                sts32(base + 2u * U * 4u, __byte_perm(A.y, B.y, 0x5410));
+                sts32(base + 3u * U * 4u, __byte_perm(A.y, B.y, 0x7632));
+                sts32(base + 4u * U * 4u, __byte_perm(A.z, B.z, 0x5410));
+                sts32(base + 5u * U * 4u, __byte_perm(A.z, B.z, 0x7632));
+                sts32(base + 6u * U * 4u, __byte_perm(A.w, B.w, 0x5410));
+                sts32(base + 7u * U * 4u, __byte_perm(A.w, B.w, 0x7632));
+            } else {
+                const uint4 A = lds128(in + u * 128 + ((j ^ (u & 7)) << 4));
+                const uint32_t base = out + ((uint32_t)(CPG * j) * U + u) * 4u;
+                sts32(base + 0u * U * 4u, A.x);
+                sts32(base + 1u * U * 4u, A.y);
+                sts32(base + 2u * U * 4u, A.z);
+                sts32(base + 3u * U * 4u, A.w);
+            }
+        }
+        fence_async_smem();     // the bulk store reads what the generic proxy just wrote
+        __syncwarp();
+        consumers_sync();
+        if (lane == 0)
+            mbar_arrive(ring.empty0 + 8u * s);
+        if (threadIdx.x == 0) {
+            uint32_t ib, cc;
+            p.cChunks.divmod((uint32_t)item, ib, cc);
+            T* dst = stack + ((long long)ib * a.C + (long long)cc * (128 / (int)sizeof(T))) * p.pixels;
+            bulk_store_1d(dst, out, (uint32_t)p.tileBytes);
+            // the other out stage is written next: its previous store must have finished reading
+            bulk_wait_read<1>();
+        }
+        __syncwarp();
+    }
+    (void)failed;
+    if (threadIdx.x == 0)
+        bulk_wait_all();
+}
+
+// ---- scatter ------------------------------------------------------------------------------------
+template <int MODE, typename T>
+__global__ void __launch_bounds__(kTmaThreads, 1) planes_scatter_tma(const BlockArgs a, const TmaPlan p)
+{
+    extern __shared__ unsigned char dynSmem[];
+    __shared__ int abortFlag;
+    constexpr int EPW = 4 / (int)sizeof(T);
+    constexpr int CPG = 16 / (int)sizeof(T);
+    // tasks per thread: ceil(units/16) groups of 16 units x 8 channel groups over 256 threads
+    constexpr int kMaxTasks = ((kMaxPixels / EPW + 15) / 16 + 1) / 2;
+    const Ring ring = carve(dynSmem, p);
+    ring_init(ring, p, &abortFlag);
+
+    const long long nItems = (long long)device_count(a) * p.cChunks.div;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T* stack = reinterpret_cast<const T*>(a.stack);
+
+    if (warp == kConsumerWarps) {
+        if (lane == 0) {
+            int k = 0;
+            for (long long item = blockIdx.x; item < nItems; item += gridDim.x, ++k) {
+                const int s = k % p.inStages;
+                const uint32_t parity = (uint32_t)(k / p.inStages) & 1u;
+                if (!mbar_wait(ring.empty0 + 8u * s, parity ^ 1u, &abortFlag))
+                    break;
+                uint32_t ib, cc;
+                p.cChunks.divmod((uint32_t)item, ib, cc);
+                const T* src = stack + ((long long)ib * a.C + (long long)cc * (128 / (int)sizeof(T))) * p.pixels;
+                mbar_expect_tx(ring.full0 + 8u * s, (uint32_t)p.tileBytes);
+                bulk_load_1d(ring.in0 + (uint32_t)s * p.inStageBytes, src, (uint32_t)p.tileBytes,
+                             ring.full0 + 8u * s);
+            }
+        }
+        return;
+    }
+
+    T* image = reinterpret_cast<T*>(a.image);
+    const int U = p.units;
+    const int nTasks = ((U + 15) >> 4) * 128;
+    int k = 0;
+    for (long long item = blockIdx.x; item < nItems; item += gridDim.x, ++k) {
+        const int s = k % p.inStages;
+        const uint32_t parity = (uint32_t)(k / p.inStages) & 1u;
+        uint32_t ib, cc;
+        p.cChunks.divmod((uint32_t)item, ib, cc);
+        const int n = a.idx[ib * 3 + 0];
+        const int h0 = a.bOffsH + a.idx[ib * 3 + 1] * a.bStrH;
+        const int w0 = a.bOffsW + a.idx[ib * 3 + 2] * a.bStrW;
+        T* imgN = image + (long long)n * a.H * a.W * a.C + (long long)cc * (128 / (int)sizeof(T));
+
+        // destination vector of (pixel, 16-byte group), or nullptr when the pixel is outside
+        auto dest = [&](int pix, int j) -> uint4* {
+            uint32_t r, sx;
+            p.blockW.divmod((uint32_t)pix, r, sx);
+            const int h = h0 + (int)r, w = w0 + (int)sx;
+            if (h < 0 || h >= a.H || w < 0 || w >= a.W)
+                return nullptr;
+            return reinterpret_cast<uint4*>(imgN + ((long long)h * a.W + w) * a.C + j * CPG);
+        };
+
+        // read-add-write: all destination loads of this thread's share of the tile go out first
+        uint4 old[kMaxTasks][EPW];
+        if constexpr (MODE == kScatterAdd) {
+#pragma unroll
+            for (int q = 0; q < kMaxTasks; ++q) {
+                const int t = threadIdx.x + q * kConsumers;
+                const int uLocal = t & 15, grp = t >> 4;
+                const int j = grp & 7, u = ((grp >> 3) << 4) + uLocal;
+#pragma unroll
+                for (int e = 0; e < EPW; ++e) {
+                    old[q][e] = make_uint4(0, 0, 0, 0);
+                    if (t < nTasks && u < U) {
+                        const uint4* d = dest(u * EPW + e, j);
+                        if (d)
+                            old[q][e] = *d;
+                    }
+                }
+            }
+        }
+
+        // warps run independently: each polls the stage itself and releases it itself
+        int ok = 1;
+        if (lane == 0)
+            ok = mbar_wait(ring.full0 + 8u * s, parity, &abortFlag) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (ok == 0)
+            break;
+        const uint32_t in = ring.in0 + (uint32_t)s * p.inStageBytes;
+#pragma unroll
+        for (int q = 0; q < kMaxTasks; ++q) {
+            const int t = threadIdx.x + q * kConsumers;
+            const int uLocal = t & 15, grp = t >> 4;
+            const int j = grp & 7, u = ((grp >> 3) << 4) + uLocal;
+            if (t >= nTasks || u >= U)
+                continue;
+            const uint32_t base = in + ((uint32_t)(CPG * j) * U + u) * 4u;
+            if constexpr (EPW == 2) {
+                uint32_t w[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    w[i] = lds32(base + (uint32_t)i * U * 4u);
+                const uint4 v0 = make_uint4(__byte_perm(w[0], w[1], 0x5410), __byte_perm(w[2], w[3], 0x5410),
+                                            __byte_perm(w[4], w[5], 0x5410), __byte_perm(w[6], w[7], 0x5410));
+                const uint4 v1 = make_uint4(__byte_perm(w[0], w[1], 0x7632), __byte_perm(w[2], w[3], 0x7632),
+                                            __byte_perm(w[4], w[5], 0x7632), __byte_perm(w[6], w[7], 0x7632));
+                if (uint4* d = dest(2 * u, j))
+                    image_write<16, MODE, T>(d, v0, old[q][0]);
+                if (uint4* d = dest(2 * u + 1, j))
+                    image_write<16, MODE, T>(d, v1, old[q][EPW - 1]);
+            } else {
+                const uint4 v = make_uint4(lds32(base), lds32(base + (uint32_t)U * 4u),
+                                           lds32(base + 2u * U * 4u), lds32(base + 3u * U * 4u));
+                if (uint4* d = dest(u, j))
+                    image_write<16, MODE, T>(d, v, old[q][0]);
+            }
+        }
+        __syncwarp();          // this warp is done reading the stage
+        if (lane == 0)
+            mbar_arrive(ring.empty0 + 8u * s);
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+static PFN_cuTensorMapEncodeTiled encode_fn()
+{
+    static PFN_cuTensorMapEncodeTiled fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(ptr);
+        else
+            (void)cudaGetLastError();
+        tried = true;
+    }
+    return fn;
+}
+
+bool planes_tma_eligible(const BlockArgs& a, int itemsize)
+{
+    const char* off = getenv("SBNET_DISABLE_TMA");
+    if (off && off[0] == '1')
+        return false;
+    const long long P = (long long)a.bSzH * a.bSzW;
+    const size_t pixelBytes = (size_t)a.C * itemsize;
+    if (pixelBytes % 128 != 0 || P > kMaxPixels || (itemsize == 2 && (P & 1)))
+        return false;
+    if (a.bSzH > 256 || a.bSzW > 256)
+        return false;
+    if ((reinterpret_cast<uintptr_t>(a.image) | reinterpret_cast<uintptr_t>(a.stack)) & 15)
+        return false;
+    return true;
+}
+
+static cudaError_t set_smem(const void* fn, int bytes)
+{
+    return cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
+cudaError_t launch_planes_tma(const BlockArgs& a, int dtype, int mode, cudaStream_t stream, bool* taken)
+{
+    *taken = false;
+    const int itemsize = dtype == 0 ? 4 : 2;
+    if (!planes_tma_eligible(a, itemsize))
+        return cudaSuccess;
+
+    TmaPlan p;
+    const int P = a.bSzH * a.bSzW;
+    p.cChunks = FastDiv((uint32_t)((size_t)a.C * itemsize / 128));
+    p.blockW = FastDiv((uint32_t)a.bSzW);
+    p.pixels = P;
+    p.units = itemsize == 4 ? P : P / 2;
+    p.tileBytes = 128 * P;
+    const long long nItems = (long long)a.numActive * p.cChunks.div;
+    const int grid = (int)(nItems < sm_count() ? nItems : sm_count());
+
+    if (mode == kGather) {
+        PFN_cuTensorMapEncodeTiled enc = encode_fn();
+        if (enc == nullptr)
+            return cudaSuccess;   // no driver entry point: the general kernel takes the call
+        CUtensorMap map;
+        const cuuint64_t dims[4] = {(cuuint64_t)a.C, (cuuint64_t)a.W, (cuuint64_t)a.H, (cuuint64_t)a.N};
+        const cuuint64_t strides[3] = {(cuuint64_t)a.C * itemsize, (cuuint64_t)a.W * a.C * itemsize,
+                                       (cuuint64_t)a.H * a.W * a.C * itemsize};
+        const cuuint32_t box[4] = {(cuuint32_t)(128 / itemsize), (cuuint32_t)a.bSzW, (cuuint32_t)a.bSzH, 1};
+        const cuuint32_t estr[4] = {1, 1, 1, 1};
+        const CUresult rc = enc(&map, itemsize == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16,
+                                4, a.image, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (rc != CUDA_SUCCESS)
+            return cudaSuccess;   // shape the encoder rejects: general kernel
+        p.outStages = 2;
+        p.inStageBytes = (p.tileBytes + 1023) & ~1023;
+        p.outStageBytes = (p.tileBytes + 127) & ~127;
+        p.inStages = 3 * p.inStageBytes + 2 * p.outStageBytes <= 225 * 1024 ? 3 : 2;
+        const int smem = 1024 + p.inStages * p.inStageBytes + p.outStages * p.outStageBytes + 16 * p.inStages;
+        if (dtype == 0) {
+            if (cudaError_t e = set_smem((const void*)planes_gather_tma<float>, smem))
+                return e;
+            planes_gather_tma<float><<<grid, kTmaThreads, smem, stream>>>(map, a, p);
+        } else {
+            if (cudaError_t e = set_smem((const void*)planes_gather_tma<__half>, smem))
+                return e;
+            planes_gather_tma<__half><<<grid, kTmaThreads, smem, stream>>>(map, a, p);
+        }
+        *taken = true;
+        return cudaGetLastError();
+    }
+
+    p.inStages = 4, p.outStages = 0;
+    p.inStageBytes = (p.tileBytes + 127) & ~127;
+    p.outStageBytes = 0;
+    const int smem = 1024 + p.inStages * p.inStageBytes + 16 * p.inStages;
+#define SBNET_SCATTER_TMA(MODE_, T_)                                                              \
+    do {                                                                                          \
+        if (cudaError_t e = set_smem((const void*)planes_scatter_tma<MODE_, T_>, smem))       \
+            return e;                                                                             \
+        planes_scatter_tma<MODE_, T_><<<grid, kTmaThreads, smem, stream>>>(a, p);                 \
+    } while (0)
+    if (dtype == 0) {
+        if (mode == kScatterSet)
+            SBNET_SCATTER_TMA(kScatterSet, float);
+        else if (mode == kScatterAdd)
+            SBNET_SCATTER_TMA(kScatterAdd, float);
+        else
+            SBNET_SCATTER_TMA(kScatterAtomic, float);
+    } else {
+        if (mode == kScatterSet)
+            SBNET_SCATTER_TMA(kScatterSet, __half);
+        else if (mode == kScatterAdd)
+            SBNET_SCATTER_TMA(kScatterAdd, __half);
+        else
+            SBNET_SCATTER_TMA(kScatterAtomic, __half);
+    }
+#undef SBNET_SCATTER_TMA
+    *taken = true;
+    return cudaGetLastError();
+}
+
+cudaError_t read_wait_timeouts(unsigned int* out)
+{
+    return cudaMemcpyFromSymbol(out, g_wait_timeouts, sizeof(unsigned int));
+}
+
+} // namespace sbnet

@@ -30,6 +30,7 @@ SIGNATURES = {
     "sbnet_copy_tensor": (_i, [_p, _p, _sz, _p]),
     "sbnet_cuda_timer_start": (_i, [C.POINTER(C.c_int64)]),
     "sbnet_cuda_timer_end": (_i, [C.c_int64, C.POINTER(_f)]),
+    "sbnet_wait_timeouts": (_i, [C.POINTER(C.c_uint)]),
 }
 
 _lib = None
