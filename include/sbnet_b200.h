@@ -38,7 +38,7 @@ extern "C" {
 #define SBNET_F16 1 /* extension: the reference registers T = float only (sparse_gather.cc:49) */
 
 /* sbnet_reduce_mask flags */
-#define SBNET_SCRATCH_CLEAN 1 /* scratch[1..2] are already zero (see below): skip the memset */
+#define SBNET_SCRATCH_CLEAN 1 /* scratch[2..3] are already zero (see below): skip the memset */
 
 /* int32 words of device scratch sbnet_reduce_mask needs */
 #define SBNET_REDUCE_MASK_SCRATCH_INTS 4
@@ -58,10 +58,10 @@ const char* sbnet_last_error(void);
  *                         sum(in-range pixels)/(bSzH*bSzW) > tol (avg)
  *   active_block_indices  [N*bCntH*bCntW, 3] int16 (n, bh, bw); the first count rows are written,
  *                         in arbitrary order
- *   scratch_dev           SBNET_REDUCE_MASK_SCRATCH_INTS int32.  On return (stream order)
- *                         scratch_dev[0] holds the published count, which device-side consumers
- *                         (the *_dyn entry points) may read without a host round trip;
- *                         scratch_dev[1..2] are internal and are left at zero.  Pass
+ *   scratch_dev           SBNET_REDUCE_MASK_SCRATCH_INTS int32, 16-byte aligned.  On return (stream
+ *                         order) scratch_dev[0] holds the published count, which device-side
+ *                         consumers (the *_dyn entry points) may read without a host round trip;
+ *                         scratch_dev[2..3] are internal and are left at zero.  Pass
  *                         SBNET_SCRATCH_CLEAN in `flags` when the buffer was zero-filled once and has
  *                         since only been used by stream-ordered calls of this function; otherwise
  *                         the library clears it with a cudaMemsetAsync first.

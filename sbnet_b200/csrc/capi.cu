@@ -121,6 +121,8 @@ SBNET_EXPORT int sbnet_reduce_mask(const float* mask, int N, int H, int W, float
         return rc;
     if (mask == nullptr || active_block_indices == nullptr || scratch_dev == nullptr)
         return reject(SBNET_ERR_INVALID_ARGUMENT, "%s: null tensor pointer", op);
+    if (reinterpret_cast<uintptr_t>(scratch_dev) & 15)
+        return reject(SBNET_ERR_INVALID_ARGUMENT, "%s: scratch_dev must be 16-byte aligned", op);
 
     cudaStream_t s = (cudaStream_t)stream;
     int32_t* hostDev = nullptr;   // device-visible alias of count_host when it is pinned

@@ -264,6 +264,17 @@ int sm_count()
     return cached[dev];
 }
 
+// CTAs of `kernel` that fit one SM at once; persistent grids are sized to exactly one resident wave.
+template <typename K> static int resident_ctas(K kernel, int threads)
+{
+    int perSm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, kernel, threads, 0) != cudaSuccess || perSm < 1) {
+        (void)cudaGetLastError();
+        perSm = 1;
+    }
+    return perSm * sm_count();
+}
+
 static int pick_vector_bytes(const BlockArgs& a, int itemsize)
 {
     const size_t pixelBytes = (size_t)a.C * itemsize;
@@ -295,8 +306,8 @@ static void launch_rows(const BlockArgs& a, cudaStream_t stream)
     const int ipb = (a.bSzH + rows - 1) / rows;
     p.itemsPerBlock = FastDiv((uint32_t)ipb);
     const long long nItems = (long long)a.numActive * ipb;
-    const long long cap = (long long)sm_count() * 8;
-    const int grid = (int)(nItems < cap ? nItems : cap);
+    static const int wave = resident_ctas(rows_kernel<VB, MODE, T>, kThreads);
+    const int grid = (int)(nItems < wave ? nItems : wave);
     rows_kernel<VB, MODE, T><<<grid, kThreads, 0, stream>>>(a, p);
 }
 
@@ -329,8 +340,8 @@ static void launch_planes(const BlockArgs& a, cudaStream_t stream)
     p.pixFull = FastDiv((uint32_t)p.pixPerChunk);
     p.pixLast = FastDiv((uint32_t)lastPix);
     const long long nItems = (long long)a.numActive * nC * nP;
-    const long long cap = (long long)sm_count() * 4;
-    const int grid = (int)(nItems < cap ? nItems : cap);
+    static const int wave = resident_ctas(planes_kernel<VB, MODE, T>, kThreads);
+    const int grid = (int)(nItems < wave ? nItems : wave);
     planes_kernel<VB, MODE, T><<<grid, kThreads, 0, stream>>>(a, p);
 }
 
@@ -372,6 +383,12 @@ cudaError_t launch_blocks(const BlockArgs& a, int dtype, int mode, bool transpos
 {
     if (a.numActive <= 0)
         return cudaSuccess;
+    // fp16 read-add-write over disjoint blocks is done with the packed-half reduction instead: every
+    // destination element receives exactly one addend, and red.add.noftz.f16x2 rounds to nearest even
+    // without flushing subnormals, so the result is bit-identical while the SM never waits on the
+    // destination read.  (fp32 keeps the explicit read-add-write: red.add.f32 flushes subnormals.)
+    if (mode == kScatterAdd && dtype != 0)
+        mode = kScatterAtomic;
     const int itemsize = dtype == 0 ? 4 : 2;
     if (transpose) {   // aligned shapes: the TMA pipeline
         bool taken = false;
@@ -418,7 +435,8 @@ cudaError_t launch_copy(void* dst, const void* src, size_t bytes, cudaStream_t s
 {
     if (bytes == 0 || dst == src)
         return cudaSuccess;
-    const long long cap = (long long)sm_count() * 8;
+    static const int wave = resident_ctas(copy_kernel, kThreads);
+    const long long cap = wave;
     if (((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15) == 0) {
         const size_t nVec = bytes / 16;
         const int tail = (int)(bytes - nVec * 16);

@@ -26,12 +26,12 @@ namespace sbnet {
 
 constexpr int kRmThreads = 256;
 constexpr int kRmMaxCols = 4096;   // image columns one CTA stages (x2 floats of shared memory)
-constexpr int kRowBatch = 9;       // loads kept in flight per thread while running down a band
+constexpr int kRowBatch = 18;      // loads kept in flight per thread while running down a band
 
 struct RmArgs {
     const float* mask;
     int16_t* idx;
-    int32_t* scratch;      // [0] published count, [1] append cursor, [2] finished-CTA ticket
+    int32_t* scratch;      // [0] published count, [2..3] 64-bit cursor|ticket word (16-byte aligned)
     int32_t* host_count;   // optional device-visible address of a pinned host int
     int N, H, W;
     float tol;
@@ -64,46 +64,23 @@ __device__ bool block_active_exact(const RmArgs& a, int n, int bh, int bw)
     return AVG ? (__fdiv_rn(sum, a.area) > a.tol) : any;
 }
 
-// Appends the active blocks of one warp with a single atomic: ballot, popc, one reservation.
-__device__ __forceinline__ void append_active(const RmArgs& a, bool active, int n, int bh, int bw)
+// scratch words [2..3] form one 64-bit word: low half = append cursor, high half = CTAs finished.
+__device__ __forceinline__ unsigned long long* cursor64(const RmArgs& a)
 {
-    const unsigned ballot = __ballot_sync(0xffffffffu, active);
-    if (ballot == 0)
-        return;
-    const int lane = threadIdx.x & 31;
-    const int leader = __ffs(ballot) - 1;
-    int base = 0;
-    if (lane == leader)
-        base = atomicAdd(a.scratch + 1, __popc(ballot));
-    base = __shfl_sync(0xffffffffu, base, leader);
-    if (active) {
-        int16_t* out = a.idx + (size_t)(base + __popc(ballot & ((1u << lane) - 1u))) * 3;
-        out[0] = (int16_t)n;
-        out[1] = (int16_t)bh;
-        out[2] = (int16_t)bw;
-    }
+    return reinterpret_cast<unsigned long long*>(a.scratch + 2);
 }
 
-// Last CTA out publishes the count (an empty result becomes the single block (0,0,0), as the
-// reference op does on the host) and leaves cursor and ticket at zero for the next call.
-__device__ __forceinline__ void finish(const RmArgs& a, unsigned totalCtas)
+// The CTA that finishes last publishes the count (an empty result becomes the single block
+// (0,0,0), as the reference op does on the host) and leaves the cursor word at zero for the next
+// call.  `count` is the final number of appended blocks.
+__device__ __forceinline__ void publish(const RmArgs& a, int count)
 {
-    __syncthreads();
-    if (threadIdx.x != 0)
-        return;
-    __threadfence();
-    const unsigned ticket = atomicAdd(reinterpret_cast<unsigned*>(a.scratch + 2), 1u);
-    if (ticket != totalCtas - 1)
-        return;
-    __threadfence();
-    int count = atomicAdd(a.scratch + 1, 0);
     if (count == 0) {
         a.idx[0] = a.idx[1] = a.idx[2] = 0;
         count = 1;
     }
     a.scratch[0] = count;
-    a.scratch[1] = 0;
-    a.scratch[2] = 0;
+    *cursor64(a) = 0ull;
     if (a.host_count) {
         *reinterpret_cast<volatile int32_t*>(a.host_count) = count;
         __threadfence_system();
@@ -116,6 +93,9 @@ __global__ void __launch_bounds__(kRmThreads) reduce_mask_band(const RmArgs a)
     // per staged column: sum (or any-flag) and, for AVG, the sum of magnitudes
     __shared__ float colVal[kRmMaxCols];
     __shared__ float colMag[AVG ? kRmMaxCols : 1];
+    __shared__ unsigned ballots[kRmMaxCols / 32 + 1];   // verdicts of the tile, 32 blocks per word
+    __shared__ unsigned wordBase[kRmMaxCols / 32 + 1];  // exclusive prefix of popc(ballots)
+    __shared__ unsigned ctaBase;
 
     const int n = blockIdx.z, bh = blockIdx.y;
     const int bw0 = blockIdx.x * a.tileBlocks;
@@ -143,13 +123,17 @@ __global__ void __launch_bounds__(kRmThreads) reduce_mask_band(const RmArgs a)
         for (int hb = hBeg; hb < hEnd; hb += kRowBatch) {
             float v[kRowBatch][V];
 #pragma unroll
-            for (int k = 0; k < kRowBatch; ++k) {
-                const int hh = min(hb + k, hEnd - 1);   // clamped rows are loaded but not counted
-                if constexpr (VEC4) {
-                    const float4 q = __ldg(reinterpret_cast<const float4*>(colp + (size_t)hh * a.W));
-                    v[k][0] = q.x, v[k][1] = q.y, v[k][2] = q.z, v[k][3] = q.w;
-                } else {
-                    v[k][0] = __ldg(colp + (size_t)hh * a.W);
+            for (int k = 0; k < kRowBatch; ++k) {   // all loads of the batch are issued before any use
+#pragma unroll
+                for (int j = 0; j < V; ++j)
+                    v[k][j] = 0.0f;
+                if (hb + k < hEnd) {
+                    if constexpr (VEC4) {
+                        const float4 q = __ldg(reinterpret_cast<const float4*>(colp + (size_t)(hb + k) * a.W));
+                        v[k][0] = q.x, v[k][1] = q.y, v[k][2] = q.z, v[k][3] = q.w;
+                    } else {
+                        v[k][0] = __ldg(colp + (size_t)(hb + k) * a.W);
+                    }
                 }
             }
 #pragma unroll
@@ -176,9 +160,10 @@ __global__ void __launch_bounds__(kRmThreads) reduce_mask_band(const RmArgs a)
     }
     __syncthreads();
 
-    // one thread per block column of the tile; whole warps stay together for the ballot
+    // verdicts: one thread per block column of the tile, 32 verdicts per ballot word
     const int nBlk = bwEnd - bw0;
-    for (int b = threadIdx.x; b < ((nBlk + 31) & ~31); b += kRmThreads) {
+    const int nWords = (nBlk + 31) >> 5;
+    for (int b = threadIdx.x; b < nWords * 32; b += kRmThreads) {
         bool active = false;
         const int bw = bw0 + b;
         if (b < nBlk && hBeg < hEnd) {
@@ -214,18 +199,45 @@ __global__ void __launch_bounds__(kRmThreads) reduce_mask_band(const RmArgs a)
             // a band with no in-range row: empty window => max: inactive; avg: 0/area > tol
             active = AVG ? (__fdiv_rn(0.0f, a.area) > a.tol) : false;
         }
-        append_active(a, active, n, bh, bw);
+        const unsigned ballot = __ballot_sync(0xffffffffu, active);
+        if ((threadIdx.x & 31) == 0)
+            ballots[b >> 5] = ballot;
     }
-    finish(a, gridDim.x * gridDim.y * gridDim.z);
+    __syncthreads();
+
+    // ONE atomic per CTA reserves its run of the index list and takes a finish ticket with it
+    if (threadIdx.x == 0) {
+        unsigned total = 0;
+        for (int w = 0; w < nWords; ++w) {
+            wordBase[w] = total;
+            total += __popc(ballots[w]);
+        }
+        const unsigned long long old = atomicAdd(cursor64(a), (1ull << 32) | total);
+        ctaBase = (unsigned)old;
+        if ((unsigned)(old >> 32) == gridDim.x * gridDim.y * gridDim.z - 1)
+            publish(a, (int)((unsigned)old + total));
+    }
+    __syncthreads();
+    for (int b = threadIdx.x; b < nBlk; b += kRmThreads) {
+        const unsigned ballot = ballots[b >> 5], bit = 1u << (b & 31);
+        if (ballot & bit) {
+            int16_t* out = a.idx + (size_t)(ctaBase + wordBase[b >> 5] + __popc(ballot & (bit - 1u))) * 3;
+            out[0] = (int16_t)n;
+            out[1] = (int16_t)bh;
+            out[2] = (int16_t)(bw0 + b);
+        }
+    }
 }
 
-// Fallback for windows wider than a CTA can stage: one thread per block, reference order.
+// Fallback for windows wider than a CTA can stage: one thread per block, reference order; one
+// reservation per warp (ballot, popc), one finish ticket per CTA.
 template <bool AVG>
 __global__ void __launch_bounds__(kRmThreads) reduce_mask_naive(const RmArgs a)
 {
     const long long total = (long long)a.N * a.bCntH * a.bCntW;
     const long long stride = (long long)gridDim.x * kRmThreads;
     const long long rounds = (total + stride - 1) / stride;
+    const int lane = threadIdx.x & 31;
     for (long long r = 0; r < rounds; ++r) {
         const long long i = r * stride + (long long)blockIdx.x * kRmThreads + threadIdx.x;
         bool active = false;
@@ -236,9 +248,28 @@ __global__ void __launch_bounds__(kRmThreads) reduce_mask_naive(const RmArgs a)
             n = (int)(i / ((long long)a.bCntW * a.bCntH));
             active = block_active_exact<AVG>(a, n, bh, bw);
         }
-        append_active(a, active, n, bh, bw);
+        const unsigned ballot = __ballot_sync(0xffffffffu, active);
+        if (ballot == 0)
+            continue;
+        const int leader = __ffs(ballot) - 1;
+        unsigned base = 0;
+        if (lane == leader)
+            base = (unsigned)atomicAdd(cursor64(a), (unsigned long long)__popc(ballot));
+        base = __shfl_sync(0xffffffffu, base, leader);
+        if (active) {
+            int16_t* out = a.idx + (size_t)(base + __popc(ballot & ((1u << lane) - 1u))) * 3;
+            out[0] = (int16_t)n;
+            out[1] = (int16_t)bh;
+            out[2] = (int16_t)bw;
+        }
     }
-    finish(a, gridDim.x);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned long long old = atomicAdd(cursor64(a), 1ull << 32);
+        if ((unsigned)(old >> 32) == gridDim.x - 1)
+            publish(a, (int)(unsigned)old);
+    }
 }
 
 cudaError_t launch_reduce_mask(const float* mask, int N, int H, int W, float tol, bool avgpool,

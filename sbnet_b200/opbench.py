@@ -60,9 +60,58 @@ def emit(name, med_ms, min_ms, nbytes, extra):
     print(json.dumps(line), flush=True)
 
 
+def one(args):
+    """``bench.py --suite one --case NAME [--density D]``: a few launches of ONE op on a mid-sized
+    input (larger than L2, well under a GB), for profiler captures.  Prints one JSON line."""
+    import torch
+    from . import build, ops
+    build.build_library()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    tm = Timer(torch, dev, max(args.steps, 3), 3)
+    name, dens = args.case, args.density
+    N, H, W = 8, 512, 512
+    if name.startswith("reduce_mask"):
+        c2 = cfg.config2(0)
+        g = c2["geom"]
+        m = torch.from_numpy(c2["mask"]).to(dev)
+        avg = name.endswith("avg")
+        fn = lambda: ops.reduce_mask_async(m, *g.as_lists(), tol=0.1 if avg else 0.5, avgpool=avg)  # noqa: E731
+        nbytes = m.numel() * 4
+    else:
+        kind, tname, layout = name.split("_")[:3]           # gather_f16_t1, scatter_f32_t0_atomic ...
+        mode = name.split("_")[3] if kind == "scatter" else None
+        dtype = torch.float16 if tname == "f16" else torch.float32
+        tr = layout == "t1"
+        C = args.channels if args.channels != 256 or kind == "gather" else 64
+        C = 128 if (kind == "gather" and args.channels == 256) else C
+        halo = kind == "gather" or mode == "atomic"
+        g = cfg.halo_geom(H, W) if halo else cfg.inner_geom(H, W)
+        idx_h, cnt_h = cfg.random_block_list(N, g.bcount, dens, seed=11)
+        nb = int(cnt_h[0])
+        U = cfg.union_pixels(idx_h, nb, g, N, H, W)
+        idx, cnt = torch.from_numpy(idx_h).to(dev), torch.from_numpy(cnt_h)
+        x = torch.randn((N, H, W, C), device=dev).to(dtype)
+        shape = (nb, C, *g.bsize) if tr else (nb, *g.bsize, C)
+        st = torch.randn(shape, device=dev).to(dtype)
+        if kind == "gather":
+            fn = lambda: ops.sparse_gather(x, cnt, idx, g.bsize, g.bstride, g.boffset, transpose=tr, out=st)  # noqa: E731
+            nbytes = cfg.algorithmic_bytes("gather", nB=nb, geom=g, C=C, itemsize=x.element_size(), U=U)
+        else:
+            add, atomic = mode in ("add", "atomic"), mode == "atomic"
+            fn = lambda: ops.sparse_scatter_var(st, cnt, idx, x, g.bsize, g.bstride, g.boffset, add=add,  # noqa: E731
+                                                atomic=atomic, transpose=tr)
+            nbytes = cfg.algorithmic_bytes("scatter_add" if add else "scatter", nB=nb, geom=g, C=C,
+                                           itemsize=x.element_size(), U=U)
+    med, mn = tm.run(fn, flush=True)
+    emit(name, med, mn, nbytes, {"density": dens})
+
+
 def main(args):
     import torch
     from . import build, ops
+    if getattr(args, "suite", None) == "one":
+        return one(args)
     build.build_library()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)

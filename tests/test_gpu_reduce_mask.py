@@ -1,0 +1,128 @@
+"""reduce_mask corner cases on the GPU against the CPU checker (through the C ABI)."""
+import numpy as np
+import pytest
+
+from sbnet_b200 import configs as cfg
+
+pytestmark = pytest.mark.gpu
+
+
+def _sets_equal(cuda_ops, oracle_port, mask, g, tol, avg):
+    gi, gc = cuda_ops.reduce_mask(mask, *g.as_lists(), tol=tol, avgpool=avg)
+    oi, oc = oracle_port.reduce_mask(mask, *g.as_lists(), tol=tol, avgpool=avg)
+    assert int(gc[0]) == int(oc[0])
+    n = int(oc[0])
+    got = sorted(map(tuple, gi[:n].tolist()))
+    assert got == sorted(map(tuple, oi[:n].tolist()))
+    return n
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_average_threshold_on_a_block_value(cuda_ops, oracle_port, seed):
+    """Real-valued masks with the threshold set EXACTLY to one block's average as the reference
+    computes it (row-major fp32 sum / area): the verdict of that block depends on the last bit of
+    the sum, so the GPU must reproduce the reference's summation order there."""
+    rng = np.random.default_rng(seed)
+    N, H, W = 2, 96, 80 + 4 * (seed % 2) + (seed % 3)       # W not always a multiple of 4
+    mask = rng.standard_normal((N, H, W, 1)).astype(np.float32)
+    g = cfg.geom_for(H, W, (18, 18), (16, 16), (-1, -1))
+    for _ in range(8):
+        n, bh, bw = rng.integers(0, N), rng.integers(0, g.bcount[0]), rng.integers(0, g.bcount[1])
+        h0, w0 = -1 + 16 * bh, -1 + 16 * bw
+        s = np.float32(0)
+        for hh in range(max(h0, 0), min(h0 + 18, H)):
+            for ww in range(max(w0, 0), min(w0 + 18, W)):
+                s = np.float32(s + mask[n, hh, ww, 0])
+        tol = float(np.float32(s / np.float32(324)))
+        _sets_equal(cuda_ops, oracle_port, mask, g, tol, True)
+        _sets_equal(cuda_ops, oracle_port, mask, g, float(np.nextafter(np.float32(tol), np.float32(-1e9))), True)
+
+
+def test_zero_threshold_on_binary_mask(cuda_ops, oracle_port):
+    mask = cfg.rect_union_mask(2, 160, 176, seed=1, n_rects=6)
+    g = cfg.halo_geom(160, 176)
+    for avg in (True, False):
+        n = _sets_equal(cuda_ops, oracle_port, mask, g, 0.0, avg)
+        assert 0 < n < 2 * 10 * 11
+
+
+def test_negative_threshold_activates_out_of_range_blocks(cuda_ops, oracle_port):
+    # block rows/cols entirely outside the image: avg of nothing is 0 > tol when tol < 0
+    mask = np.zeros((1, 8, 8, 1), np.float32)
+    g = cfg.BlockGeom((2, 2), (4, 4), (-6, -6), (5, 5))
+    for avg in (True, False):
+        _sets_equal(cuda_ops, oracle_port, mask, g, -0.5, avg)
+
+
+def test_nan_and_inf_pixels(cuda_ops, oracle_port):
+    rng = np.random.default_rng(0)
+    mask = rng.standard_normal((1, 64, 64, 1)).astype(np.float32)
+    mask[0, 5, 5, 0] = np.nan
+    mask[0, 40, 40, 0] = np.inf
+    mask[0, 41, 41, 0] = -np.inf
+    mask[0, 20, 50, 0] = np.inf
+    g = cfg.halo_geom(64, 64)
+    for avg in (True, False):
+        _sets_equal(cuda_ops, oracle_port, mask, g, 0.1, avg)
+
+
+def test_scratch_is_reusable_across_calls_and_empty_results(cuda_ops, oracle_port):
+    g = cfg.halo_geom(64, 64)
+    full = np.ones((3, 64, 64, 1), np.float32)
+    empty = np.zeros((3, 64, 64, 1), np.float32)
+    for mask in (full, empty, full, empty, empty, full):
+        for avg in (False, True):
+            gi, gc = cuda_ops.reduce_mask(mask, *g.as_lists(), tol=0.5, avgpool=avg)
+            oi, oc = oracle_port.reduce_mask(mask, *g.as_lists(), tol=0.5, avgpool=avg)
+            assert int(gc[0]) == int(oc[0])
+            if mask is empty:
+                assert int(gc[0]) == 1 and gi[0].tolist() == [0, 0, 0]
+
+
+def test_many_narrow_blocks_span_several_tiles(cuda_ops, oracle_port):
+    rng = np.random.default_rng(3)
+    mask = (rng.random((1, 6, 9000, 1)) < 0.02).astype(np.float32)
+    g = cfg.geom_for(6, 9000, (3, 3), (2, 1), (-1, -1))        # 9001 block columns, stride 1
+    _sets_equal(cuda_ops, oracle_port, mask, g, 0.5, False)
+    _sets_equal(cuda_ops, oracle_port, mask, g, 0.2, True)
+
+
+def test_window_wider_than_the_staging_area_uses_the_fallback(cuda_ops, oracle_port):
+    rng = np.random.default_rng(4)
+    mask = rng.standard_normal((1, 5, 12000, 1)).astype(np.float32)
+    g = cfg.geom_for(5, 12000, (2, 5000), (2, 3000), (0, -10))
+    _sets_equal(cuda_ops, oracle_port, mask, g, 3.5, False)
+    _sets_equal(cuda_ops, oracle_port, mask, g, 0.001, True)
+
+
+def test_full_size_bev_mask_matches(cuda_ops, oracle_port):
+    c2 = cfg.config2(0)
+    for run in c2["runs"]:
+        _sets_equal(cuda_ops, oracle_port, c2["mask"], c2["geom"], run["tol"], run["avgpool"])
+
+
+def test_misaligned_scratch_is_rejected(cuda_ops):
+    import torch
+    from sbnet_b200 import lib
+    m = torch.zeros((1, 8, 8, 1), device="cuda")
+    idx = torch.zeros((16, 3), dtype=torch.int16, device="cuda")
+    scratch = torch.zeros(8, dtype=torch.int32, device="cuda")
+    rc = lib.load().sbnet_reduce_mask(m.data_ptr(), 1, 8, 8, 0.5, 0, 0, 0, 2, 2, 2, 2, 4, 4, idx.data_ptr(),
+                                      scratch.data_ptr() + 4, None, 0, None)
+    assert rc == -1
+
+
+def test_pageable_count_host(cuda_ops):
+    """count_host in ordinary (unpinned) memory takes the copy path."""
+    import ctypes as C
+    import torch
+    from sbnet_b200 import lib
+    m = torch.ones((2, 16, 16, 1), device="cuda")
+    idx = torch.zeros((2 * 4 * 4, 3), dtype=torch.int16, device="cuda")
+    scratch = torch.zeros(4, dtype=torch.int32, device="cuda")
+    out = C.c_int32(-7)
+    rc = lib.load().sbnet_reduce_mask(m.data_ptr(), 2, 16, 16, 0.5, 0, 0, 0, 4, 4, 4, 4, 4, 4, idx.data_ptr(),
+                                      scratch.data_ptr(), C.addressof(out), 0,
+                                      torch.cuda.current_stream().cuda_stream)
+    assert rc == 0 and out.value == 32
+    assert scratch.cpu().tolist() == [32, 0, 0, 0]
