@@ -147,6 +147,32 @@ int sbnet_cuda_timer_end(int64_t handle, float* elapsed_ms);
  */
 int sbnet_wait_timeouts(unsigned int* count);
 
+/*
+ * ReduceMask without caller-provided scratch.  No counterpart in the reference.
+ *
+ * For hosts that cannot give the library device memory of their own: a plug-in inside a framework
+ * that has already reserved the whole GPU for its memory pool (a plain cudaMalloc fails there), code
+ * in a section where allocation calls are not allowed, or a thin C wrapper with no allocator.  Same
+ * result as sbnet_reduce_mask; the cursor / ticket words live in a fixed SBNET_STATIC_SCRATCH_BYTES
+ * array inside the library's device image (one per GPU that loads the library, held until exit).
+ *
+ *   count_dev   optional DEVICE int32 that receives the published count in stream order (what
+ *               scratch_dev[0] is for sbnet_reduce_mask); count_host as in sbnet_reduce_mask.
+ *
+ * Limits and rules: N*bCntH*bCntW must not exceed SBNET_STATIC_MAX_BLOCKS (rejected with
+ * SBNET_ERR_INVALID_ARGUMENT otherwise).  All calls on one GPU share the array: calls whose kernels
+ * can overlap (different streams or threads without ordering) race; the words that must start at zero
+ * are cleared on `stream` at the start of every call, so a previous call's leftovers never leak.
+ * The first call on each GPU resolves the array's device address (not a stream operation): make it
+ * before any stream capture.  The function and everything it calls allocate nothing.
+ */
+#define SBNET_STATIC_SCRATCH_BYTES 256
+#define SBNET_STATIC_MAX_BLOCKS (1 << 24)
+int sbnet_reduce_mask_static(const float* mask, int N, int H, int W, float tol, int avgpool,
+                             int bOffsH, int bOffsW, int bSzH, int bSzW, int bStrH, int bStrW,
+                             int bCntH, int bCntW, int16_t* active_block_indices, int32_t* count_dev,
+                             int32_t* count_host, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

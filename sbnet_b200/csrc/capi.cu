@@ -96,6 +96,11 @@ int scatter_mode(const char* op, int add, int atomic, int bSzH, int bSzW, int bS
 
 } // namespace
 
+namespace sbnet {
+// Lets other translation units of the library report through sbnet_last_error().
+void set_last_error(const char* text) { snprintf(g_err, sizeof(g_err), "%s", text); }
+} // namespace sbnet
+
 SBNET_EXPORT int sbnet_version(void) { return 100; }
 
 SBNET_EXPORT const char* sbnet_last_error(void) { return g_err; }

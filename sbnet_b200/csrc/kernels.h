@@ -28,4 +28,7 @@ cudaError_t launch_copy(void* dst, const void* src, size_t bytes, cudaStream_t s
 
 int sm_count();
 
+// Sets the calling thread's sbnet_last_error() text.
+void set_last_error(const char* text);
+
 } // namespace sbnet

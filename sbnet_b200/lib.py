@@ -31,6 +31,7 @@ SIGNATURES = {
     "sbnet_cuda_timer_start": (_i, [C.POINTER(C.c_int64)]),
     "sbnet_cuda_timer_end": (_i, [C.c_int64, C.POINTER(_f)]),
     "sbnet_wait_timeouts": (_i, [C.POINTER(C.c_uint)]),
+    "sbnet_reduce_mask_static": (_i, [_p, _i, _i, _i, _f, _i] + _GEOM + [_i, _i, _p, _p, _p, _p]),
 }
 
 _lib = None
