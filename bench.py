@@ -107,16 +107,18 @@ class ClockSampler:
 
 # ---- workload ------------------------------------------------------------------------------------
 
-def pipeline_shapes(args, world):
-    N = args.batch if args.scaling == "weak" else max(args.batch // world, 1)
-    return N, args.height, args.width, args.channels
-
-
 def make_host_inputs(args, rank, world):
-    """Seeded host-side inputs of one rank (numpy)."""
-    N, H, W, C = pipeline_shapes(args, world)
-    seed = 1000 * rank + 7
-    mask = cfg.rect_union_mask(N, H, W, seed=seed, occupancy=args.occupancy)
+    """Seeded host-side inputs of one rank (numpy).  Weak scaling: every rank owns a full batch of its
+    own images; strong scaling: the ranks split ONE batch into contiguous slices."""
+    from sbnet_b200.dist import shard_bounds
+    H, W, C = args.height, args.width, args.channels
+    if args.scaling == "weak":
+        first, N = rank * args.batch, args.batch
+    else:
+        lo, hi = shard_bounds(args.batch, world, rank)
+        first, N = lo, max(hi - lo, 1)
+    # image n of the global batch always gets seed 7 + n, whichever rank owns it
+    mask = cfg.rect_union_mask(N, H, W, seed=7 + first, occupancy=args.occupancy)
     return N, H, W, C, mask
 
 
@@ -181,8 +183,10 @@ def run_ours(args):
     bytes_gather = cfg.algorithmic_bytes("gather", nB=nB, geom=g_in, C=C, itemsize=sz, U=U_in)
     bytes_scatter = cfg.algorithmic_bytes("scatter_add", nB=nB, geom=g_out, C=C, itemsize=sz, U=U_out)
 
-    counts_all = torch.zeros(world, dtype=torch.int32, device=dev)
+    from sbnet_b200 import dist as sbdist
     ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+
+    last_counts = [None]
 
     def step(i, marks=None):
         m = masks[i % len(masks)]
@@ -192,9 +196,9 @@ def run_ours(args):
         if marks is not None:
             marks[1].record()
         work = None
-        if world > 1:  # the only exchange of the path: every rank's block count
-            work = dist.all_gather_into_tensor(counts_all, ops.scratch_for(dev, torch.cuda.current_stream(dev).cuda_stream)[0][:1],
-                                               async_op=True)
+        if world > 1:  # the only exchange of the path: every rank's block count, read on the device
+            count_dev = ops.scratch_for(dev, torch.cuda.current_stream(dev).cuda_stream)[0][:1]
+            counts_all, work = sbdist.all_gather_counts(count_dev, async_op=True)
         nb = int(cnt[0])
         assert nb == nB, (nb, nB)
         if marks is not None:
@@ -207,7 +211,8 @@ def run_ours(args):
         if marks is not None:
             marks[4].record()
         if work is not None:
-            work.wait()
+            work.wait()          # stream-level wait; the host does not block
+            last_counts[0] = counts_all
         return nb
 
     def fence():
@@ -283,6 +288,10 @@ def run_ours(args):
     ms_total, e2e_ms = stats.tolist()
     blocks_all, e2e_blocks_all = sums.tolist()
 
+    global_blocks = None
+    if world > 1 and last_counts[0] is not None:
+        global_blocks = int(last_counts[0].sum().item())   # from the all-gathered device counts
+        assert global_blocks * args.steps == int(blocks_all), (global_blocks, blocks_all)
     if rank == 0:
         peak, peak_kind = measured_peak()
         med = {k: statistics.median(v) for k, v in op_ms.items()}
@@ -306,7 +315,8 @@ def run_ours(args):
                 "bsize": [18, 18], "bstride": [16, 16], "boffset": [-1, -1],
                 "active_blocks_per_rank": nB, "candidate_blocks_per_rank": N * g_in.bcount[0] * g_in.bcount[1],
                 "l2": "x (2.3 GB per rank) exceeds L2; masks rotate through copies and are evicted by the x traffic between uses",
-                "parallelism": f"dp{world}",
+                "parallelism": f"dp{world}", "global_blocks_per_step": global_blocks if world > 1 else nB,
+                "collective": "all-gather of one int32 block count per rank per step (NCCL), off the critical path",
             },
             "ops": {k: {"us": med[k] * 1e3, "algorithmic_bytes": alg[k], "GB/s": gbs[k],
                         "frac_of_" + peak_kind: gbs[k] / peak} for k in med},
@@ -387,8 +397,11 @@ def run_reference(args):
     vals = []
     base = None
     t_all = time.perf_counter()
+    step_ms = []
     for _ in range(args.warmup + args.steps):
+        t_step = time.perf_counter()
         base = cpu_pipeline(args, mask_h, N, H, W, C, budget_s=args.cpu_budget / 2)
+        step_ms.append((time.perf_counter() - t_step) * 1e3)
         vals.append(base["value"])
         if time.perf_counter() - t_all > 150:
             break
@@ -400,7 +413,8 @@ def run_reference(args):
         "impl": "reference",
         "metric": "sparse block pipeline throughput (reduce_mask -> sparse_gather -> sparse_scatter_var)",
         "value": value, "unit": "blocks/s", "n_gpus": world, "steps": len(timed),
-        "warmup": min(args.warmup, len(vals) - 1), "ms_per_step": None, "higher_is_better": True,
+        "warmup": min(args.warmup, len(vals) - 1), "ms_per_step": statistics.median(step_ms),
+        "higher_is_better": True,
         "scaling": args.scaling, "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": "sparse ResNet bottleneck block ops (BASELINE config 5 without the framework's convs), CPU functors on a bounded sample",
                    "x": [N, H, W, C], "mask": f"rectangle union, {args.occupancy:.0%} pixel occupancy",
@@ -432,6 +446,7 @@ def main():
     ap.add_argument("--suite", choices=["ops", "one"], default=None)
     ap.add_argument("--case", default="gather_f16_t1")
     ap.add_argument("--density", type=float, default=0.2)
+    ap.add_argument("--one-channels", type=int, default=None)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.suite in ("ops", "one"):

@@ -83,8 +83,7 @@ def one(args):
         mode = name.split("_")[3] if kind == "scatter" else None
         dtype = torch.float16 if tname == "f16" else torch.float32
         tr = layout == "t1"
-        C = args.channels if args.channels != 256 or kind == "gather" else 64
-        C = 128 if (kind == "gather" and args.channels == 256) else C
+        C = args.one_channels or (128 if kind == "gather" else 64)
         halo = kind == "gather" or mode == "atomic"
         g = cfg.halo_geom(H, W) if halo else cfg.inner_geom(H, W)
         idx_h, cnt_h = cfg.random_block_list(N, g.bcount, dens, seed=11)
