@@ -24,7 +24,8 @@
 
 namespace sbnet {
 
-constexpr int kRmThreads = 256;
+constexpr int kRmThreads = 192;      // 176 threads cover a 704-pixel row with 128-bit loads; 3 CTAs per SM
+                                    // keep the 400 bands of an [8,800,704] mask in a single wave
 constexpr int kRmMaxCols = 4096;   // image columns one CTA stages (x2 floats of shared memory)
 constexpr int kRowBatch = 18;      // loads kept in flight per thread while running down a band
 
@@ -88,7 +89,7 @@ __device__ __forceinline__ void publish(const RmArgs& a, int count)
 }
 
 template <bool AVG, bool VEC4>
-__global__ void __launch_bounds__(kRmThreads) reduce_mask_band(const RmArgs a)
+__global__ void __launch_bounds__(kRmThreads, 3) reduce_mask_band(const RmArgs a)
 {
     // per staged column: sum (or any-flag) and, for AVG, the sum of magnitudes
     __shared__ float colVal[kRmMaxCols];

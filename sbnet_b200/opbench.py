@@ -211,8 +211,37 @@ def main(args):
              {"blocks": nb, "blocks/s": nb / (med * 1e-3)})
         del base, stack
 
-    # ---- plain copy (the non-Var op's base copy) ----
+    # ---- plain copy (the non-Var op's base copy), with torch's own copy beside it as a yardstick ----
     a = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
     b = torch.empty_like(a)
     med, mn = tm.run(lambda: ops.copy_tensor(b, a))
     emit("copy_tensor_1GiB", med, mn, 2 << 30, {})
+    a16, b16 = a.view(torch.bfloat16), b.view(torch.bfloat16)
+    med, mn = tm.run(lambda: b16.copy_(a16))
+    emit("yardstick_torch_copy_1GiB", med, mn, 2 << 30, {})
+
+    # ---- launch floor: the same reduce_mask entry point on a 32x32 mask ----
+    tiny = torch.zeros((1, 32, 32, 1), device=dev)
+    med, mn = tm.run(lambda: ops.reduce_mask_async(tiny, [2, 2], [18, 18], [16, 16], [-1, -1], tol=0.5))
+    emit("floor_reduce_mask_32x32_event_timed", med, mn, 4096, {})
+
+    # ---- reduce_mask replayed from a CUDA graph: 32 launches over 8 rotating masks, no host in the loop ----
+    c2 = cfg.config2(0)
+    g = c2["geom"]
+    masks = [torch.from_numpy(c2["mask"]).to(dev) for _ in range(8)]
+    for run in c2["runs"]:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for m in masks:   # warm-up on the capture stream (also zero-fills that stream's scratch)
+                ops.reduce_mask_async(m, *g.as_lists(), tol=run["tol"], avgpool=run["avgpool"])
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        keep = []
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(32):
+                keep.append(ops.reduce_mask_async(masks[i % 8], *g.as_lists(), tol=run["tol"], avgpool=run["avgpool"]))
+        med, mn = tm.run(graph.replay, flush=False)
+        tag = "avg" if run["avgpool"] else "max"
+        emit(f"reduce_mask_{tag}_graph_replay_per_launch", med / 32, mn / 32, 18022400, {"launches_per_replay": 32})
