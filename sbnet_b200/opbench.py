@@ -106,11 +106,61 @@ def one(args):
     emit(name, med, mn, nbytes, {"density": dens})
 
 
+def resblock(args):
+    """``bench.py --suite resblock``: the full sparse bottleneck (x fp16 [batch,400,352,256], 1x1 256->64,
+    3x3 VALID 64->64, 1x1 64->256 by torch / cuDNN between gather and scatter) with the share of the
+    block ops in the block time.  The convolutions are the host framework's, identical whichever op
+    library is used; they are reported, not optimised here."""
+    import torch
+    from . import build, ops
+    from .resblock import SparseBottleneck
+    build.build_library()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    N, H, W, C = args.batch, args.height, args.width, args.channels
+    m = SparseBottleneck(C, C // 4, dtype=torch.float16).eval()
+    x = torch.randn((N, H, W, C), device=dev, dtype=torch.float32).half() if N * H * W * C < 2 ** 29 else None
+    if x is None:
+        x = torch.empty((N, H, W, C), device=dev, dtype=torch.float16)
+        for n in range(N):
+            x[n] = torch.randn((H, W, C), device=dev).half()
+    mask = torch.from_numpy(cfg.rect_union_mask(N, H, W, seed=7, occupancy=args.occupancy)).to(dev)
+    bp = m.block_params(x.shape)
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+    rows = []
+    with torch.no_grad():
+        for it in range(args.warmup + args.steps):
+            e = [ev() for _ in range(5)]
+            e[0].record()
+            idx, cnt = ops.reduce_mask(mask, bp.bcount, bp.bsize, bp.bstrides, bp.boffset, tol=0.5)
+            e[1].record()
+            p = ops.sparse_gather(x, cnt, idx, bp.bsize, bp.bstrides, bp.boffset, transpose=True)
+            e[2].record()
+            q = m.residual(p).contiguous()
+            e[3].record()
+            ops.sparse_scatter_var(q, cnt, idx, x, bp.bsize_out, bp.bsize_out, [0, 0], add=True, transpose=True)
+            e[4].record()
+            torch.cuda.synchronize()
+            if it >= args.warmup:
+                rows.append([e[i].elapsed_time(e[i + 1]) for i in range(4)])
+            del p, q
+    med = [statistics.median(r[i] for r in rows) for i in range(4)]
+    total = sum(med)
+    nb = int(cnt[0])
+    print(json.dumps({"case": "sparse_bottleneck_block", "x": [N, H, W, C], "occupancy": args.occupancy,
+                      "active_blocks": nb, "ms": {"reduce_mask": med[0], "gather": med[1], "convs_bn_relu": med[2],
+                                                  "scatter": med[3], "total": total},
+                      "block_ops_share_of_block_time": (med[0] + med[1] + med[3]) / total,
+                      "blocks/s": nb / (total * 1e-3)}), flush=True)
+
+
 def main(args):
     import torch
     from . import build, ops
     if getattr(args, "suite", None) == "one":
         return one(args)
+    if getattr(args, "suite", None) == "resblock":
+        return resblock(args)
     build.build_library()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
