@@ -21,6 +21,8 @@
 // The launch is a fixed-size grid of CTAs striding over work items, so the number of active blocks
 // may come from device memory (written by reduce_mask earlier on the same stream) instead of the
 // host.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -400,8 +402,23 @@ cudaError_t launch_blocks(const BlockArgs& a, int dtype, int mode, bool transpos
     if (mode == kScatterAdd && dtype != 0)
         mode = kScatterAtomic;
     const int itemsize = dtype == 0 ? 4 : 2;
-    if (transpose) {   // aligned shapes: the TMA pipeline
+    if (transpose) {
+        // Aligned shapes have two implementations: one short CTA per tile (planes_simt.cu) and the
+        // persistent TMA pipeline (planes_tma.cu, the only one that can read the count on the device).
+        // They are within a few percent of each other; measured on B200 the tile CTAs win for fp32
+        // gather (+3 %) and for add / atomic scatter (+3 %), the pipeline for fp16 gather (+2 %) and
+        // overwrite scatter (+5 %).  SBNET_PLANES=tma|tile forces one of them (A/B measurements).
         bool taken = false;
+        const char* force = getenv("SBNET_PLANES");
+        bool tileFirst = (mode == kGather) ? (dtype == 0) : (mode != kScatterSet);
+        if (force && force[0] == 't')
+            tileFirst = force[1] == 'i';
+        if (tileFirst) {
+            if (cudaError_t e = launch_planes_simt(a, dtype, mode, stream, &taken))
+                return e;
+            if (taken)
+                return cudaSuccess;
+        }
         if (cudaError_t e = launch_planes_tma(a, dtype, mode, stream, &taken))
             return e;
         if (taken)

@@ -21,6 +21,10 @@ cudaError_t launch_blocks(const BlockArgs& a, int dtype, int mode, bool transpos
 // Plane-layout fast path (TMA pipeline); *taken tells whether it accepted the call.
 cudaError_t launch_planes_tma(const BlockArgs& a, int dtype, int mode, cudaStream_t stream, bool* taken);
 
+// Same shapes as launch_planes_tma, one short CTA per tile; host-side block count only.
+cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStream_t stream, bool* taken);
+bool planes_tma_eligible(const BlockArgs& a, int itemsize);
+
 // Bounded device-side waits that gave up since the library was loaded (0 in a healthy process).
 cudaError_t read_wait_timeouts(unsigned int* out);
 

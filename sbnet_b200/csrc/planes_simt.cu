@@ -1,0 +1,266 @@
+// Transposed ([nB,C,R,S]) gather and scatter, one short CTA per tile (sm_100a).
+//
+// Same eligibility and semantics as the TMA pipeline of planes_tma.cu (C*sizeof(T) a multiple of 128
+// bytes, blocks of at most 384 pixels); used when the block count is known on the host, because on
+// B200 a grid of many short CTAs streams measurably faster than a resident grid looping over the
+// same tiles.  A work item is one active block x one 128-byte channel chunk: a tile of P = R*S pixels
+// x 128 bytes, staged ONCE in shared memory and transposed in place through registers:
+//
+//  gather : every thread issues all of its 16-byte image loads (out-of-image pixels become zeros),
+//           stores them to the tile in [pixel][128 B] order with the 16-byte groups XOR-swizzled by
+//           the pixel index; each thread then reads its share back as 16-byte channel groups, the
+//           CTA synchronises, and the same threads write words of one channel (1 fp32 pixel / 2 fp16
+//           pixels, regrouped with prmt) in [channel][pixel] order into the same buffer.  The tile
+//           leaves as ONE bulk store (TMA engine): a chunk's channel planes are contiguous in the
+//           stack.
+//  scatter: the tile (contiguous in the stack) is copied in with 16-byte loads, then words are
+//           regrouped into 16-byte channel groups and written / added / reduced into the image with
+//           a per-pixel in-range test.
+#include "async_ptx.cuh"
+#include "common.cuh"
+#include "kernels.h"
+
+namespace sbnet {
+
+constexpr int kPsThreads = 256;
+constexpr int kPsMaxPixels = 384;
+constexpr int kPsTileBytes = 128 * kPsMaxPixels;          // 48 KB
+constexpr int kPsMaxVecs = (8 * kPsMaxPixels) / kPsThreads;   // 16-byte vectors per thread
+
+struct SimtPlan {
+    FastDiv cChunks;   // 128-byte channel chunks per pixel
+    FastDiv blockW;    // S
+    int pixels;        // P
+    int units;         // words per channel plane: P (fp32) or P/2 (fp16)
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kPsThreads, 3) planes_gather_simt(const BlockArgs a, const SimtPlan p)
+{
+    __shared__ __align__(1024) unsigned char tileRaw[kPsTileBytes];
+    constexpr int EPW = 4 / (int)sizeof(T);
+    constexpr int CPG = 16 / (int)sizeof(T);
+    constexpr int kMaxTasks = ((kPsMaxPixels / EPW + 15) / 16 + 1) / 2;
+    const uint32_t tile = smem_u32(tileRaw);
+
+    uint32_t ib, cc;
+    p.cChunks.divmod(blockIdx.x, ib, cc);
+    const int n = a.idx[ib * 3 + 0];
+    const int h0 = a.bOffsH + a.idx[ib * 3 + 1] * a.bStrH;
+    const int w0 = a.bOffsW + a.idx[ib * 3 + 2] * a.bStrW;
+    const T* imgN = reinterpret_cast<const T*>(a.image) + (long long)n * a.H * a.W * a.C +
+                    (long long)cc * (128 / (int)sizeof(T));
+    const int P = p.pixels, U = p.units;
+
+    // ---- image -> tile: thread owns 16-byte group j of pixels px0, px0+32, ...
+    {
+        const int j = threadIdx.x & 7, px0 = threadIdx.x >> 3;
+        uint4 v[kPsMaxVecs];
+#pragma unroll
+        for (int k = 0; k < kPsMaxVecs; ++k) {
+            const int px = px0 + 32 * k;
+            v[k] = make_uint4(0, 0, 0, 0);
+            if (px < P) {
+                uint32_t r, s;
+                p.blockW.divmod((uint32_t)px, r, s);
+                const int h = h0 + (int)r, w = w0 + (int)s;
+                if (h >= 0 && h < a.H && w >= 0 && w < a.W)
+                    v[k] = ld_stream(reinterpret_cast<const uint4*>(imgN + ((long long)h * a.W + w) * a.C + j * CPG));
+            }
+        }
+        const uint32_t dst = tile + ((uint32_t)(j ^ (px0 & 7)) << 4);   // (px & 7) == (px0 & 7)
+#pragma unroll
+        for (int k = 0; k < kPsMaxVecs; ++k)
+            if (px0 + 32 * k < P)
+                sts128(dst + (uint32_t)(px0 + 32 * k) * 128u, v[k]);
+    }
+    __syncthreads();
+
+    // ---- tile -> registers (16-byte channel groups), then registers -> tile in [channel][pixel] order
+    const int nTasks = ((U + 15) >> 4) * 128;
+    uint4 A[kMaxTasks], B[kMaxTasks];
+#pragma unroll
+    for (int q = 0; q < kMaxTasks; ++q) {
+        const int t = threadIdx.x + q * kPsThreads;
+        const int uLocal = t & 15, grp = t >> 4;
+        const int j = grp & 7, u = ((grp >> 3) << 4) + uLocal;
+        if (t < nTasks && u < U) {
+            if constexpr (EPW == 2) {
+                const int r0 = 2 * u, r1 = 2 * u + 1;
+                A[q] = lds128(tile + r0 * 128 + ((j ^ (r0 & 7)) << 4));
+                B[q] = lds128(tile + r1 * 128 + ((j ^ (r1 & 7)) << 4));
+            } else {
+                A[q] = lds128(tile + u * 128 + ((j ^ (u & 7)) << 4));
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < kMaxTasks; ++q) {
+        const int t = threadIdx.x + q * kPsThreads;
+        const int uLocal = t & 15, grp = t >> 4;
+        const int j = grp & 7, u = ((grp >> 3) << 4) + uLocal;
+        if (t < nTasks && u < U) {
+            const uint32_t base = tile + ((uint32_t)(CPG * j) * U + u) * 4u;
+            const uint32_t pitch = (uint32_t)U * 4u;
+            if constexpr (EPW == 2) {
+                sts32(base + 0u * pitch, __byte_perm(A[q].x, B[q].x, 0x5410));
+                sts32(base + 1u * pitch, __byte_perm(A[q].x, B[q].x, 0x7632));
+                sts32(base + 2u * pitch, __byte_perm(A[q].y, B[q].y, 0x5410));
+                sts32(base + 3u * pitch, __byte_perm(A[q].y, B[q].y, 0x7632));
+                sts32(base + 4u * pitch, __byte_perm(A[q].z, B[q].z, 0x5410));
+                sts32(base + 5u * pitch, __byte_perm(A[q].z, B[q].z, 0x7632));
+                sts32(base + 6u * pitch, __byte_perm(A[q].w, B[q].w, 0x5410));
+                sts32(base + 7u * pitch, __byte_perm(A[q].w, B[q].w, 0x7632));
+            } else {
+                sts32(base + 0u * pitch, A[q].x);
+                sts32(base + 1u * pitch, A[q].y);
+                sts32(base + 2u * pitch, A[q].z);
+                sts32(base + 3u * pitch, A[q].w);
+            }
+        }
+    }
+    fence_async_smem();   // the bulk store reads what the generic proxy just wrote
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        T* dst = reinterpret_cast<T*>(a.stack) + ((long long)ib * a.C + (long long)cc * (128 / (int)sizeof(T))) * P;
+        bulk_store_1d(dst, tile, (uint32_t)(128 * P));
+        bulk_wait_read<0>();   // shared memory must outlive the engine's read of it
+    }
+}
+
+template <int MODE, typename T>
+__global__ void __launch_bounds__(kPsThreads, MODE == kScatterAdd ? 2 : 3)
+planes_scatter_simt(const BlockArgs a, const SimtPlan p)
+{
+    __shared__ __align__(128) unsigned char tileRaw[kPsTileBytes];
+    constexpr int EPW = 4 / (int)sizeof(T);
+    constexpr int CPG = 16 / (int)sizeof(T);
+    constexpr int kMaxTasks = ((kPsMaxPixels / EPW + 15) / 16 + 1) / 2;
+    const uint32_t tile = smem_u32(tileRaw);
+
+    uint32_t ib, cc;
+    p.cChunks.divmod(blockIdx.x, ib, cc);
+    const int n = a.idx[ib * 3 + 0];
+    const int h0 = a.bOffsH + a.idx[ib * 3 + 1] * a.bStrH;
+    const int w0 = a.bOffsW + a.idx[ib * 3 + 2] * a.bStrW;
+    T* imgN = reinterpret_cast<T*>(a.image) + (long long)n * a.H * a.W * a.C + (long long)cc * (128 / (int)sizeof(T));
+    const int P = p.pixels, U = p.units;
+    const int nTasks = ((U + 15) >> 4) * 128;
+
+    auto dest = [&](int pix, int j) -> uint4* {
+        uint32_t r, sx;
+        p.blockW.divmod((uint32_t)pix, r, sx);
+        const int h = h0 + (int)r, w = w0 + (int)sx;
+        if (h < 0 || h >= a.H || w < 0 || w >= a.W)
+            return nullptr;
+        return reinterpret_cast<uint4*>(imgN + ((long long)h * a.W + w) * a.C + j * CPG);
+    };
+
+    // ---- stack -> tile: the chunk's planes are one contiguous run of 8*P vectors
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(
+            reinterpret_cast<const T*>(a.stack) + ((long long)ib * a.C + (long long)cc * (128 / (int)sizeof(T))) * P);
+        const int nVec = 8 * P;
+        uint4 v[kPsMaxVecs];
+#pragma unroll
+        for (int k = 0; k < kPsMaxVecs; ++k)
+            if ((int)threadIdx.x + k * kPsThreads < nVec)
+                v[k] = ld_stream(src + threadIdx.x + k * kPsThreads);
+#pragma unroll
+        for (int k = 0; k < kPsMaxVecs; ++k)
+            if ((int)threadIdx.x + k * kPsThreads < nVec)
+                sts128(tile + (uint32_t)(threadIdx.x + k * kPsThreads) * 16u, v[k]);
+    }
+    // read-add-write: the destination loads go out while the tile settles
+    uint4 old[kMaxTasks][EPW];
+    if constexpr (MODE == kScatterAdd) {
+#pragma unroll
+        for (int q = 0; q < kMaxTasks; ++q) {
+            const int t = threadIdx.x + q * kPsThreads;
+            const int uLocal = t & 15, grp = t >> 4;
+            const int j = grp & 7, u = ((grp >> 3) << 4) + uLocal;
+#pragma unroll
+            for (int e = 0; e < EPW; ++e) {
+                old[q][e] = make_uint4(0, 0, 0, 0);
+                if (t < nTasks && u < U)
+                    if (const uint4* d = dest(u * EPW + e, j))
+                        old[q][e] = *d;
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- tile -> image
+#pragma unroll
+    for (int q = 0; q < kMaxTasks; ++q) {
+        const int t = threadIdx.x + q * kPsThreads;
+        const int uLocal = t & 15, grp = t >> 4;
+        const int j = grp & 7, u = ((grp >> 3) << 4) + uLocal;
+        if (t >= nTasks || u >= U)
+            continue;
+        const uint32_t base = tile + ((uint32_t)(CPG * j) * U + u) * 4u;
+        const uint32_t pitch = (uint32_t)U * 4u;
+        if constexpr (EPW == 2) {
+            uint32_t w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                w[i] = lds32(base + (uint32_t)i * pitch);
+            const uint4 v0 = make_uint4(__byte_perm(w[0], w[1], 0x5410), __byte_perm(w[2], w[3], 0x5410),
+                                        __byte_perm(w[4], w[5], 0x5410), __byte_perm(w[6], w[7], 0x5410));
+            const uint4 v1 = make_uint4(__byte_perm(w[0], w[1], 0x7632), __byte_perm(w[2], w[3], 0x7632),
+                                        __byte_perm(w[4], w[5], 0x7632), __byte_perm(w[6], w[7], 0x7632));
+            if (uint4* d = dest(2 * u, j))
+                image_write<16, MODE, T>(d, v0, old[q][0]);
+            if (uint4* d = dest(2 * u + 1, j))
+                image_write<16, MODE, T>(d, v1, old[q][EPW - 1]);
+        } else {
+            const uint4 v = make_uint4(lds32(base), lds32(base + pitch), lds32(base + 2u * pitch),
+                                       lds32(base + 3u * pitch));
+            if (uint4* d = dest(u, j))
+                image_write<16, MODE, T>(d, v, old[q][0]);
+        }
+    }
+}
+
+cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStream_t stream, bool* taken)
+{
+    *taken = false;
+    const int itemsize = dtype == 0 ? 4 : 2;
+    if (a.num_active_dev != nullptr || !planes_tma_eligible(a, itemsize))
+        return cudaSuccess;
+    SimtPlan p;
+    const int P = a.bSzH * a.bSzW;
+    p.cChunks = FastDiv((uint32_t)((size_t)a.C * itemsize / 128));
+    p.blockW = FastDiv((uint32_t)a.bSzW);
+    p.pixels = P;
+    p.units = itemsize == 4 ? P : P / 2;
+    const long long nItems = (long long)a.numActive * p.cChunks.div;
+    if (nItems > 0x7fffffffll)
+        return cudaSuccess;
+    const unsigned grid = (unsigned)nItems;
+#define SBNET_PS(KERNEL) KERNEL<<<grid, kPsThreads, 0, stream>>>(a, p)
+    if (mode == kGather) {
+        if (dtype == 0)
+            SBNET_PS(planes_gather_simt<float>);
+        else
+            SBNET_PS(planes_gather_simt<__half>);
+    } else if (dtype == 0) {
+        if (mode == kScatterSet)
+            SBNET_PS((planes_scatter_simt<kScatterSet, float>));
+        else if (mode == kScatterAdd)
+            SBNET_PS((planes_scatter_simt<kScatterAdd, float>));
+        else
+            SBNET_PS((planes_scatter_simt<kScatterAtomic, float>));
+    } else {
+        if (mode == kScatterSet)
+            SBNET_PS((planes_scatter_simt<kScatterSet, __half>));
+        else
+            SBNET_PS((planes_scatter_simt<kScatterAtomic, __half>));   // fp16 add arrives as a reduction
+    }
+#undef SBNET_PS
+    *taken = true;
+    return cudaGetLastError();
+}
+
+} // namespace sbnet

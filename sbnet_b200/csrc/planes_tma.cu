@@ -28,6 +28,7 @@
 #include <cudaTypedefs.h>
 #include <stdlib.h>
 
+#include "async_ptx.cuh"
 #include "common.cuh"
 #include "kernels.h"
 
@@ -52,10 +53,6 @@ struct TmaPlan {
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p)
-{
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
 {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -114,24 +111,6 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
         "l"(src), "r"(bytes), "r"(bar)
         : "memory");
 }
-__device__ __forceinline__ void bulk_store_1d(void* dst, uint32_t src, uint32_t bytes)
-{
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes)
-                 : "memory");
-    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-}
-template <int N> __device__ __forceinline__ void bulk_wait_read()
-{
-    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void bulk_wait_all()
-{
-    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-}
-__device__ __forceinline__ void fence_async_smem()
-{
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
 // Barrier among the consumer warps only (the producer warp never joins), with an OR vote.
 __device__ __forceinline__ bool consumers_any(bool pred)
 {
@@ -149,22 +128,6 @@ __device__ __forceinline__ bool consumers_any(bool pred)
 __device__ __forceinline__ void consumers_sync()
 {
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
-}
-__device__ __forceinline__ uint4 lds128(uint32_t addr)
-{
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ uint32_t lds32(uint32_t addr)
-{
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v)
-{
-    asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 
 struct Ring {

@@ -31,16 +31,24 @@ def _ids():
     return [f"{np.dtype(s[0]).name}_C{s[4]}_b{s[5][0]}x{s[5][1]}_s{s[6][0]}x{s[6][1]}" for s in SHAPES]
 
 
-@pytest.fixture(params=[False, True], ids=["tma", "general"])
+@pytest.fixture(params=["tile_ctas", "tma_pipeline", "general"])
 def tma_off(request):
-    old = os.environ.get("SBNET_DISABLE_TMA")
-    if request.param:
+    """Selects which of the three plane-layout implementations takes the call."""
+    saved = {k: os.environ.get(k) for k in ("SBNET_DISABLE_TMA", "SBNET_PLANES")}
+    os.environ.pop("SBNET_DISABLE_TMA", None)
+    os.environ.pop("SBNET_PLANES", None)
+    if request.param == "general":
         os.environ["SBNET_DISABLE_TMA"] = "1"
-    yield request.param
-    if old is None:
-        os.environ.pop("SBNET_DISABLE_TMA", None)
+    elif request.param == "tma_pipeline":
+        os.environ["SBNET_PLANES"] = "tma"
     else:
-        os.environ["SBNET_DISABLE_TMA"] = old
+        os.environ["SBNET_PLANES"] = "tile"
+    yield request.param
+    for k, v in saved.items():
+        if v is None:
+            os.environ.pop(k, None)
+        else:
+            os.environ[k] = v
 
 
 @pytest.mark.parametrize("shape", SHAPES, ids=_ids())
