@@ -49,12 +49,11 @@ int check_geometry(const char* op, int bOffsH, int bOffsW, int bSzH, int bSzW, i
     return SBNET_OK;
 }
 
-int blocks_call(const char* op, int mode, const void* stackOrX, int dtype, int N, int H, int W, int C,
+int blocks_call(const char* op, int mode, int dtype, int N, int H, int W, int C,
                 void* image, void* stack, int bOffsH, int bOffsW, int bSzH, int bSzW, int bStrH,
                 int bStrW, int numActive, const int32_t* numActiveDev, const int16_t* idx,
                 int transpose, void* stream)
 {
-    (void)stackOrX;
     if (dtype != SBNET_F32 && dtype != SBNET_F16)
         return reject(SBNET_ERR_INVALID_ARGUMENT, "%s: unknown dtype %d", op, dtype);
     if (N < 1 || H < 1 || W < 1 || C < 1)
@@ -162,7 +161,7 @@ SBNET_EXPORT int sbnet_sparse_gather(const void* x, int dtype, int N, int H, int
                                      int bStrW, int numActive, const int16_t* active_block_indices,
                                      int transpose, void* stream)
 {
-    return blocks_call("SparseGather", sbnet::kGather, x, dtype, N, H, W, C, const_cast<void*>(x), y,
+    return blocks_call("SparseGather", sbnet::kGather, dtype, N, H, W, C, const_cast<void*>(x), y,
                        bOffsH, bOffsW, bSzH, bSzW, bStrH, bStrW, numActive, nullptr,
                        active_block_indices, transpose, stream);
 }
@@ -176,7 +175,7 @@ SBNET_EXPORT int sbnet_sparse_gather_dyn(const void* x, int dtype, int N, int H,
 {
     if (num_active_dev == nullptr)
         return reject(SBNET_ERR_INVALID_ARGUMENT, "SparseGather: num_active_dev is null");
-    return blocks_call("SparseGather", sbnet::kGather, x, dtype, N, H, W, C, const_cast<void*>(x), y,
+    return blocks_call("SparseGather", sbnet::kGather, dtype, N, H, W, C, const_cast<void*>(x), y,
                        bOffsH, bOffsW, bSzH, bSzW, bStrH, bStrW, maxActive, num_active_dev,
                        active_block_indices, transpose, stream);
 }
@@ -189,7 +188,7 @@ SBNET_EXPORT int sbnet_sparse_scatter(const void* x, int dtype, int N, int H, in
     int mode = 0;
     if (int rc = scatter_mode("SparseScatter", add, atomic, bSzH, bSzW, bStrH, bStrW, &mode))
         return rc;
-    return blocks_call("SparseScatter", mode, x, dtype, N, H, W, C, y, const_cast<void*>(x), bOffsH,
+    return blocks_call("SparseScatter", mode, dtype, N, H, W, C, y, const_cast<void*>(x), bOffsH,
                        bOffsW, bSzH, bSzW, bStrH, bStrW, numActive, nullptr, active_block_indices,
                        transpose, stream);
 }
@@ -206,7 +205,7 @@ SBNET_EXPORT int sbnet_sparse_scatter_dyn(const void* x, int dtype, int N, int H
         return reject(SBNET_ERR_INVALID_ARGUMENT, "SparseScatter: num_active_dev is null");
     if (int rc = scatter_mode("SparseScatter", add, atomic, bSzH, bSzW, bStrH, bStrW, &mode))
         return rc;
-    return blocks_call("SparseScatter", mode, x, dtype, N, H, W, C, y, const_cast<void*>(x), bOffsH,
+    return blocks_call("SparseScatter", mode, dtype, N, H, W, C, y, const_cast<void*>(x), bOffsH,
                        bOffsW, bSzH, bSzW, bStrH, bStrW, maxActive, num_active_dev,
                        active_block_indices, transpose, stream);
 }

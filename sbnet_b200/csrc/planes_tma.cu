@@ -209,7 +209,6 @@ planes_gather_tma(const __grid_constant__ CUtensorMap imageMap, const BlockArgs 
     const int U = p.units;
     const int nTasks = ((U + 15) >> 4) * 128;
     int k = 0;
-    bool failed = false;
     for (long long item = blockIdx.x; item < nItems; item += gridDim.x, ++k) {
         const int s = k % p.inStages, o = k % p.outStages;
         const uint32_t parity = (uint32_t)(k / p.inStages) & 1u;
@@ -217,10 +216,8 @@ planes_gather_tma(const __grid_constant__ CUtensorMap imageMap, const BlockArgs 
         if (lane == 0)
             ok = mbar_wait(ring.full0 + 8u * s, parity, &abortFlag) ? 1 : 0;
         ok = __shfl_sync(0xffffffffu, ok, 0);   // reconverges the warp before the CTA-level vote
-        if (consumers_any(ok == 0)) {   // also orders: thread 0 has drained the store that used out[o]
-            failed = true;
+        if (consumers_any(ok == 0))   // also orders: thread 0 has drained the store that used out[o]
             break;
-        }
         const uint32_t in = ring.in0 + (uint32_t)s * p.inStageBytes;
         const uint32_t out = ring.out0 + (uint32_t)o * p.outStageBytes;
         for (int t = threadIdx.x; t < nTasks; t += kConsumers) {
@@ -265,7 +262,6 @@ planes_gather_tma(const __grid_constant__ CUtensorMap imageMap, const BlockArgs 
         }
         __syncwarp();
     }
-    (void)failed;
     if (threadIdx.x == 0)
         bulk_wait_all();
 }
