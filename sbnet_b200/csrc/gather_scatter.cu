@@ -405,12 +405,13 @@ cudaError_t launch_blocks(const BlockArgs& a, int dtype, int mode, bool transpos
     if (transpose) {
         // Aligned shapes have two implementations: one short CTA per tile (planes_simt.cu) and the
         // persistent TMA pipeline (planes_tma.cu, the only one that can read the count on the device).
-        // They are within a few percent of each other; measured on B200 the tile CTAs win for fp32
-        // gather (+3 %) and for add / atomic scatter (+3 %), the pipeline for fp16 gather (+2 %) and
-        // overwrite scatter (+5 %).  SBNET_PLANES=tma|tile forces one of them (A/B measurements).
+        // Scatter goes to the tile CTAs, whose swizzled tile lets every warp-level store / reduction
+        // cover whole 128-byte image lines (about 20 % faster than the pipeline's dense tile); for
+        // gather the two are within a few percent (tile CTAs +3 % for fp32, pipeline +2 % for fp16).
+        // SBNET_PLANES=tma|tile forces one of them (A/B measurements).
         bool taken = false;
         const char* force = getenv("SBNET_PLANES");
-        bool tileFirst = (mode == kGather) ? (dtype == 0) : (mode != kScatterSet);
+        bool tileFirst = (mode == kGather) ? (dtype == 0) : true;
         if (force && force[0] == 't')
             tileFirst = force[1] == 'i';
         if (tileFirst) {

@@ -30,6 +30,8 @@ constexpr int kPsMaxVecs = (8 * kPsMaxPixels) / kPsThreads;   // 16-byte vectors
 struct SimtPlan {
     FastDiv cChunks;   // 128-byte channel chunks per pixel
     FastDiv blockW;    // S
+    FastDiv unitsPerRow; // copy-in units (GW words each) per channel plane (swizzled scatter only)
+    int pitchWords;    // tile row pitch of the swizzled scatter: units rounded up to 32
     int pixels;        // P
     int units;         // words per channel plane: P (fp32) or P/2 (fp16)
 };
@@ -129,14 +131,23 @@ __global__ void __launch_bounds__(kPsThreads, 3) planes_gather_simt(const BlockA
     }
 }
 
-template <int MODE, typename T>
+// GW > 0 (plane rows of a multiple of GW = 2 or 4 words): the tile is stored with a row pitch rounded
+// up to 32 words and its 16-byte column groups XOR-ed by the channel-group index, which lets eight
+// neighbouring lanes own the eight 16-byte groups of ONE pixel without bank conflicts -- every
+// warp-level store / reduction then covers whole 128-byte lines of the image (four pixels) instead
+// of sixteen scattered sectors (measured: 5.3 -> 6.4 TB/s on the fp16 add scatter).  GW is the
+// copy-in unit in words (a unit must not straddle plane rows).  GW == 0 (odd row length): dense
+// tile, sixteen-pixel lane mapping.
+template <int MODE, typename T, int GW>
 __global__ void __launch_bounds__(kPsThreads, MODE == kScatterAdd ? 2 : 3)
 planes_scatter_simt(const BlockArgs a, const SimtPlan p)
 {
     __shared__ __align__(128) unsigned char tileRaw[kPsTileBytes];
     constexpr int EPW = 4 / (int)sizeof(T);
     constexpr int CPG = 16 / (int)sizeof(T);
-    constexpr int kMaxTasks = ((kPsMaxPixels / EPW + 15) / 16 + 1) / 2;
+    constexpr bool SWZ = GW > 0;
+    constexpr int kMaxTasks = SWZ ? (8 * (kPsMaxPixels / EPW)) / kPsThreads
+                                  : ((kPsMaxPixels / EPW + 15) / 16 + 1) / 2;
     const uint32_t tile = smem_u32(tileRaw);
 
     uint32_t ib, cc;
@@ -146,7 +157,8 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
     const int w0 = a.bOffsW + a.idx[ib * 3 + 2] * a.bStrW;
     T* imgN = reinterpret_cast<T*>(a.image) + (long long)n * a.H * a.W * a.C + (long long)cc * (128 / (int)sizeof(T));
     const int P = p.pixels, U = p.units;
-    const int nTasks = ((U + 15) >> 4) * 128;
+    const int nTasks = SWZ ? 8 * U : ((U + 15) >> 4) * 128;
+    const uint32_t pitchW = SWZ ? (uint32_t)p.pitchWords : (uint32_t)U;   // tile row pitch in words
 
     auto dest = [&](int pix, int j) -> uint4* {
         uint32_t r, sx;
@@ -156,21 +168,65 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
             return nullptr;
         return reinterpret_cast<uint4*>(imgN + ((long long)h * a.W + w) * a.C + j * CPG);
     };
+    // task t of this thread -> (16-byte channel group j, word column u)
+    auto task = [&](int t, int& j, int& u) {
+        if constexpr (SWZ) {
+            j = t & 7;
+            u = t >> 3;
+        } else {
+            const int uLocal = t & 15, grp = t >> 4;
+            j = grp & 7;
+            u = ((grp >> 3) << 4) + uLocal;
+        }
+    };
 
-    // ---- stack -> tile: the chunk's planes are one contiguous run of 8*P vectors
+    // ---- stack -> tile: the chunk's planes are one contiguous run of 32*P words
     {
-        const uint4* src = reinterpret_cast<const uint4*>(
-            reinterpret_cast<const T*>(a.stack) + ((long long)ib * a.C + (long long)cc * (128 / (int)sizeof(T))) * P);
-        const int nVec = 8 * P;
-        uint4 v[kPsMaxVecs];
+        const T* srcT = reinterpret_cast<const T*>(a.stack) + ((long long)ib * a.C + (long long)cc * (128 / (int)sizeof(T))) * P;
+        if constexpr (GW == 2) {
+            const uint2* src = reinterpret_cast<const uint2*>(srcT);
+            const int nUnit = 16 * P;
 #pragma unroll
-        for (int k = 0; k < kPsMaxVecs; ++k)
-            if ((int)threadIdx.x + k * kPsThreads < nVec)
-                v[k] = ld_stream(src + threadIdx.x + k * kPsThreads);
+            for (int half = 0; half < 2; ++half) {   // two batches keep the register count under the launch bound
+                uint2 v[kPsMaxVecs];
 #pragma unroll
-        for (int k = 0; k < kPsMaxVecs; ++k)
-            if ((int)threadIdx.x + k * kPsThreads < nVec)
-                sts128(tile + (uint32_t)(threadIdx.x + k * kPsThreads) * 16u, v[k]);
+                for (int k = 0; k < kPsMaxVecs; ++k)
+                    if ((int)threadIdx.x + (half * kPsMaxVecs + k) * kPsThreads < nUnit)
+                        v[k] = ld_stream(src + threadIdx.x + (half * kPsMaxVecs + k) * kPsThreads);
+#pragma unroll
+                for (int k = 0; k < kPsMaxVecs; ++k) {
+                    const int vi = (int)threadIdx.x + (half * kPsMaxVecs + k) * kPsThreads;
+                    if (vi < nUnit) {
+                        uint32_t c, col;
+                        p.unitsPerRow.divmod((uint32_t)vi, c, col);
+                        const uint32_t w = c * pitchW + ((col * 2u) ^ (4u * ((c / CPG) & 7u)));
+                        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(tile + w * 4u), "r"(v[k].x), "r"(v[k].y)
+                                     : "memory");
+                    }
+                }
+            }
+        } else {
+            const uint4* src = reinterpret_cast<const uint4*>(srcT);
+            const int nVec = 8 * P;
+            uint4 v[kPsMaxVecs];
+#pragma unroll
+            for (int k = 0; k < kPsMaxVecs; ++k)
+                if ((int)threadIdx.x + k * kPsThreads < nVec)
+                    v[k] = ld_stream(src + threadIdx.x + k * kPsThreads);
+#pragma unroll
+            for (int k = 0; k < kPsMaxVecs; ++k) {
+                const int vi = (int)threadIdx.x + k * kPsThreads;
+                if (vi < nVec) {
+                    uint32_t w = (uint32_t)vi * 4u;
+                    if constexpr (GW == 4) {   // row = channel; XOR the 16-byte column group with the channel group
+                        uint32_t c, col;
+                        p.unitsPerRow.divmod((uint32_t)vi, c, col);
+                        w = c * pitchW + ((col * 4u) ^ (4u * ((c / CPG) & 7u)));
+                    }
+                    sts128(tile + w * 4u, v[k]);
+                }
+            }
+        }
     }
     // read-add-write: the destination loads go out while the tile settles
     uint4 old[kMaxTasks][EPW];
@@ -178,8 +234,8 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
 #pragma unroll
         for (int q = 0; q < kMaxTasks; ++q) {
             const int t = threadIdx.x + q * kPsThreads;
-            const int uLocal = t & 15, grp = t >> 4;
-            const int j = grp & 7, u = ((grp >> 3) << 4) + uLocal;
+            int j, u;
+            task(t, j, u);
 #pragma unroll
             for (int e = 0; e < EPW; ++e) {
                 old[q][e] = make_uint4(0, 0, 0, 0);
@@ -195,12 +251,13 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
 #pragma unroll
     for (int q = 0; q < kMaxTasks; ++q) {
         const int t = threadIdx.x + q * kPsThreads;
-        const int uLocal = t & 15, grp = t >> 4;
-        const int j = grp & 7, u = ((grp >> 3) << 4) + uLocal;
+        int j, u;
+        task(t, j, u);
         if (t >= nTasks || u >= U)
             continue;
-        const uint32_t base = tile + ((uint32_t)(CPG * j) * U + u) * 4u;
-        const uint32_t pitch = (uint32_t)U * 4u;
+        const uint32_t col = SWZ ? ((uint32_t)u ^ (4u * ((uint32_t)j & 7u))) : (uint32_t)u;
+        const uint32_t base = tile + ((uint32_t)(CPG * j) * pitchW + col) * 4u;
+        const uint32_t pitch = pitchW * 4u;
         if constexpr (EPW == 2) {
             uint32_t w[8];
 #pragma unroll
@@ -235,6 +292,9 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
     p.blockW = FastDiv((uint32_t)a.bSzW);
     p.pixels = P;
     p.units = itemsize == 4 ? P : P / 2;
+    const int gw = p.units % 4 == 0 ? 4 : (p.units % 2 == 0 ? 2 : 0);
+    p.unitsPerRow = FastDiv((uint32_t)(gw ? p.units / gw : 1));
+    p.pitchWords = (p.units + 31) & ~31;
     const long long nItems = (long long)a.numActive * p.cChunks.div;
     if (nItems > 0x7fffffffll)
         return cudaSuccess;
@@ -246,17 +306,27 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
         else
             SBNET_PS(planes_gather_simt<__half>);
     } else if (dtype == 0) {
+#define SBNET_PS_SC(M, T_)                                    \
+    do {                                                      \
+        if (gw == 4)                                          \
+            SBNET_PS((planes_scatter_simt<M, T_, 4>));        \
+        else if (gw == 2)                                     \
+            SBNET_PS((planes_scatter_simt<M, T_, 2>));        \
+        else                                                  \
+            SBNET_PS((planes_scatter_simt<M, T_, 0>));        \
+    } while (0)
         if (mode == kScatterSet)
-            SBNET_PS((planes_scatter_simt<kScatterSet, float>));
+            SBNET_PS_SC(kScatterSet, float);
         else if (mode == kScatterAdd)
-            SBNET_PS((planes_scatter_simt<kScatterAdd, float>));
+            SBNET_PS_SC(kScatterAdd, float);
         else
-            SBNET_PS((planes_scatter_simt<kScatterAtomic, float>));
+            SBNET_PS_SC(kScatterAtomic, float);
     } else {
         if (mode == kScatterSet)
-            SBNET_PS((planes_scatter_simt<kScatterSet, __half>));
+            SBNET_PS_SC(kScatterSet, __half);
         else
-            SBNET_PS((planes_scatter_simt<kScatterAtomic, __half>));   // fp16 add arrives as a reduction
+            SBNET_PS_SC(kScatterAtomic, __half);   // fp16 add arrives as a reduction
+#undef SBNET_PS_SC
     }
 #undef SBNET_PS
     *taken = true;

@@ -8,7 +8,8 @@ import ctypes as C
 import os
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG, "libsbnet_b200.so")
+# SBNET_B200_LIB selects another build of the same library (e.g. an instrumented one)
+LIB_PATH = os.environ.get("SBNET_B200_LIB") or os.path.join(PKG, "libsbnet_b200.so")
 
 SBNET_F32, SBNET_F16 = 0, 1
 SBNET_SCRATCH_CLEAN = 1

@@ -24,6 +24,12 @@ SHAPES = [
     (np.float32, 1, 37, 41, 64, (7, 3), (5, 3), (-3, -1)),      # 21 pixels (odd is fine for fp32)
     (np.float32, 1, 50, 50, 32, (19, 20), (19, 20), (-9, -9)),
     (np.float32, 1, 20, 20, 32, (1, 1), (1, 1), (0, 0)),
+    # plane rows a multiple of 32 words: the swizzled scatter tile
+    (np.float32, 2, 40, 56, 64, (16, 16), (16, 16), (0, 0)),
+    (np.float32, 1, 30, 30, 32, (8, 8), (5, 6), (-3, -2)),
+    (np.float16, 1, 30, 30, 128, (8, 8), (8, 8), (-3, -2)),
+    (np.float16, 2, 64, 48, 256, (16, 16), (16, 16), (0, 0)),
+    (np.float16, 1, 50, 70, 64, (16, 24), (11, 13), (-7, -9)),   # 384 pixels, overlapping
 ]
 
 
