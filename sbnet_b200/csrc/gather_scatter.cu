@@ -407,11 +407,12 @@ cudaError_t launch_blocks(const BlockArgs& a, int dtype, int mode, bool transpos
         // persistent TMA pipeline (planes_tma.cu, the only one that can read the count on the device).
         // Scatter goes to the tile CTAs, whose swizzled tile lets every warp-level store / reduction
         // cover whole 128-byte image lines (about 20 % faster than the pipeline's dense tile); for
-        // gather the two are within a few percent (tile CTAs +3 % for fp32, pipeline +2 % for fp16).
+        // gather the two are within a few percent (tile CTAs +3 % at the largest sizes), so the
+        // pipeline only serves calls whose block count lives on the device.
         // SBNET_PLANES=tma|tile forces one of them (A/B measurements).
         bool taken = false;
         const char* force = getenv("SBNET_PLANES");
-        bool tileFirst = (mode == kGather) ? (dtype == 0) : true;
+        bool tileFirst = true;
         if (force && force[0] == 't')
             tileFirst = force[1] == 'i';
         if (tileFirst) {

@@ -37,7 +37,7 @@ struct SimtPlan {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(kPsThreads, 3) planes_gather_simt(const BlockArgs a, const SimtPlan p)
+__global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gather_simt(const BlockArgs a, const SimtPlan p)
 {
     __shared__ __align__(1024) unsigned char tileRaw[kPsTileBytes];
     constexpr int EPW = 4 / (int)sizeof(T);
