@@ -400,12 +400,12 @@ def run_ours(args):
         alg = {"reduce_mask": bytes_mask, "gather": bytes_gather, "scatter": bytes_scatter}
         gbs = {k: alg[k] / (med[k] * 1e-3) / 1e9 for k in med}
         dom = max(("gather", "scatter"), key=lambda k: med[k])
-        kernel_name = {"gather": "planes_gather_tma<__half> (sparse_gather transpose=True)",
-                       "scatter": "planes_scatter_tma<atomic,__half> (sparse_scatter_var add=True transpose=True)"}[dom]
+        kernel_name = {"gather": "planes_gather_simt<__half> (sparse_gather transpose=True)",
+                       "scatter": "planes_scatter_simt<atomic,__half,4> (sparse_scatter_var add=True transpose=True)"}[dom]
         # DRAM bytes per active block from one ncu capture of each kernel on a smaller case of the same
         # shape (1,641 blocks; profiles/planes_*_c256_d20.txt), scaled by the blocks of this launch
         # (traffic is proportional to the block count: every block moves the same tile)
-        traffic = {"gather": 295898, "scatter": 362527}[dom] * nB
+        traffic = {"gather": 295860, "scatter": 357910}[dom] * nB
         line = {
             "metric": "sparse block pipeline throughput (reduce_mask -> sparse_gather -> sparse_scatter_var)",
             "value": blocks_all / (ms_total * 1e-3),
