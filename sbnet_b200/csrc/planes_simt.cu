@@ -150,8 +150,15 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
                                   : ((kPsMaxPixels / EPW + 15) / 16 + 1) / 2;
     const uint32_t tile = smem_u32(tileRaw);
 
+    // One item per CTA when the grid was sized from a host-side count; with a device-side count the
+    // grid is one resident wave and every CTA strides over the items.
+    int nActive = a.numActive;
+    if (a.num_active_dev != nullptr)
+        nActive = min(__ldg(a.num_active_dev), a.numActive);
+    const long long nItems = (long long)nActive * p.cChunks.div;
+    for (long long item = blockIdx.x; item < nItems; item += gridDim.x) {
     uint32_t ib, cc;
-    p.cChunks.divmod(blockIdx.x, ib, cc);
+    p.cChunks.divmod((uint32_t)item, ib, cc);
     const int n = a.idx[ib * 3 + 0];
     const int h0 = a.bOffsH + a.idx[ib * 3 + 1] * a.bStrH;
     const int w0 = a.bOffsW + a.idx[ib * 3 + 2] * a.bStrW;
@@ -278,14 +285,18 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
                 image_write<16, MODE, T>(d, v, old[q][0]);
         }
     }
+    __syncthreads();   // the tile is reused by the next item
+    }
 }
 
 cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStream_t stream, bool* taken)
 {
     *taken = false;
     const int itemsize = dtype == 0 ? 4 : 2;
-    if (a.num_active_dev != nullptr || !planes_tma_eligible(a, itemsize))
+    if (!planes_tma_eligible(a, itemsize))
         return cudaSuccess;
+    if (a.num_active_dev != nullptr && mode == kGather)
+        return cudaSuccess;   // device-side count: the gather goes through the TMA pipeline
     SimtPlan p;
     const int P = a.bSzH * a.bSzW;
     p.cChunks = FastDiv((uint32_t)((size_t)a.C * itemsize / 128));
@@ -298,7 +309,11 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
     const long long nItems = (long long)a.numActive * p.cChunks.div;
     if (nItems > 0x7fffffffll)
         return cudaSuccess;
-    const unsigned grid = (unsigned)nItems;
+    unsigned grid = (unsigned)nItems;
+    if (a.num_active_dev != nullptr) {   // count on the device: one resident wave strides over the items
+        const long long wave = (long long)sm_count() * 3;
+        grid = (unsigned)(nItems < wave ? nItems : wave);
+    }
 #define SBNET_PS(KERNEL) KERNEL<<<grid, kPsThreads, 0, stream>>>(a, p)
     if (mode == kGather) {
         if (dtype == 0)
