@@ -16,6 +16,8 @@
 //  scatter: the tile (contiguous in the stack) is copied in with 16-byte loads, then words are
 //           regrouped into 16-byte channel groups and written / added / reduced into the image with
 //           a per-pixel in-range test.
+#include <stdlib.h>
+
 #include "async_ptx.cuh"
 #include "common.cuh"
 #include "kernels.h"
@@ -32,6 +34,7 @@ struct SimtPlan {
     FastDiv blockW;    // S
     FastDiv unitsPerRow; // copy-in units (GW words each) per channel plane (swizzled scatter only)
     int pitchWords;    // tile row pitch of the swizzled scatter: units rounded up to 32
+    int groups;        // 16-byte channel groups per pixel (C*sizeof(T)/16); the last chunk may hold fewer than 8
     int pixels;        // P
     int units;         // words per channel plane: P (fp32) or P/2 (fp16)
 };
@@ -53,6 +56,7 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
     const T* imgN = reinterpret_cast<const T*>(a.image) + (long long)n * a.H * a.W * a.C +
                     (long long)cc * (128 / (int)sizeof(T));
     const int P = p.pixels, U = p.units;
+    const int nG = min(8, p.groups - 8 * (int)cc);   // 16-byte groups in this chunk
 
     // ---- image -> tile: thread owns 16-byte group j of pixels px0, px0+32, ...
     {
@@ -62,7 +66,7 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
         for (int k = 0; k < kPsMaxVecs; ++k) {
             const int px = px0 + 32 * k;
             v[k] = make_uint4(0, 0, 0, 0);
-            if (px < P) {
+            if (px < P && j < nG) {
                 uint32_t r, s;
                 p.blockW.divmod((uint32_t)px, r, s);
                 const int h = h0 + (int)r, w = w0 + (int)s;
@@ -86,7 +90,7 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
         const int t = threadIdx.x + q * kPsThreads;
         const int uLocal = t & 15, grp = t >> 4;
         const int j = grp & 7, u = ((grp >> 3) << 4) + uLocal;
-        if (t < nTasks && u < U) {
+        if (t < nTasks && u < U && j < nG) {
             if constexpr (EPW == 2) {
                 const int r0 = 2 * u, r1 = 2 * u + 1;
                 A[q] = lds128(tile + r0 * 128 + ((j ^ (r0 & 7)) << 4));
@@ -102,7 +106,7 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
         const int t = threadIdx.x + q * kPsThreads;
         const int uLocal = t & 15, grp = t >> 4;
         const int j = grp & 7, u = ((grp >> 3) << 4) + uLocal;
-        if (t < nTasks && u < U) {
+        if (t < nTasks && u < U && j < nG) {
             const uint32_t base = tile + ((uint32_t)(CPG * j) * U + u) * 4u;
             const uint32_t pitch = (uint32_t)U * 4u;
             if constexpr (EPW == 2) {
@@ -126,7 +130,7 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
     __syncthreads();
     if (threadIdx.x == 0) {
         T* dst = reinterpret_cast<T*>(a.stack) + ((long long)ib * a.C + (long long)cc * (128 / (int)sizeof(T))) * P;
-        bulk_store_1d(dst, tile, (uint32_t)(128 * P));
+        bulk_store_1d(dst, tile, (uint32_t)(16 * nG * P));
         bulk_wait_read<0>();   // shared memory must outlive the engine's read of it
     }
 }
@@ -164,6 +168,7 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
     const int w0 = a.bOffsW + a.idx[ib * 3 + 2] * a.bStrW;
     T* imgN = reinterpret_cast<T*>(a.image) + (long long)n * a.H * a.W * a.C + (long long)cc * (128 / (int)sizeof(T));
     const int P = p.pixels, U = p.units;
+    const int nG = min(8, p.groups - 8 * (int)cc);   // 16-byte groups in this chunk
     const int nTasks = SWZ ? 8 * U : ((U + 15) >> 4) * 128;
     const uint32_t pitchW = SWZ ? (uint32_t)p.pitchWords : (uint32_t)U;   // tile row pitch in words
 
@@ -192,7 +197,7 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
         const T* srcT = reinterpret_cast<const T*>(a.stack) + ((long long)ib * a.C + (long long)cc * (128 / (int)sizeof(T))) * P;
         if constexpr (GW == 2) {
             const uint2* src = reinterpret_cast<const uint2*>(srcT);
-            const int nUnit = 16 * P;
+            const int nUnit = 2 * nG * P;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {   // two batches keep the register count under the launch bound
                 uint2 v[kPsMaxVecs];
@@ -214,7 +219,7 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
             }
         } else {
             const uint4* src = reinterpret_cast<const uint4*>(srcT);
-            const int nVec = 8 * P;
+            const int nVec = nG * P;
             uint4 v[kPsMaxVecs];
 #pragma unroll
             for (int k = 0; k < kPsMaxVecs; ++k)
@@ -246,7 +251,7 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
 #pragma unroll
             for (int e = 0; e < EPW; ++e) {
                 old[q][e] = make_uint4(0, 0, 0, 0);
-                if (t < nTasks && u < U)
+                if (t < nTasks && u < U && j < nG)
                     if (const uint4* d = dest(u * EPW + e, j))
                         old[q][e] = *d;
             }
@@ -260,7 +265,7 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
         const int t = threadIdx.x + q * kPsThreads;
         int j, u;
         task(t, j, u);
-        if (t >= nTasks || u >= U)
+        if (t >= nTasks || u >= U || j >= nG)
             continue;
         const uint32_t col = SWZ ? ((uint32_t)u ^ (4u * ((uint32_t)j & 7u))) : (uint32_t)u;
         const uint32_t base = tile + ((uint32_t)(CPG * j) * pitchW + col) * 4u;
@@ -289,17 +294,31 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
     }
 }
 
+// Pixels of a multiple of 16 bytes (the last 128-byte chunk may be partial), blocks of at most 384
+// pixels (an even number for fp16), 16-byte aligned buffers.
+static bool planes_simt_eligible(const BlockArgs& a, int itemsize)
+{
+    const char* off = getenv("SBNET_DISABLE_TMA");
+    if (off && off[0] == '1')
+        return false;
+    const long long P = (long long)a.bSzH * a.bSzW;
+    if (((size_t)a.C * itemsize) % 16 != 0 || P > kPsMaxPixels || (itemsize == 2 && (P & 1)))
+        return false;
+    return ((reinterpret_cast<uintptr_t>(a.image) | reinterpret_cast<uintptr_t>(a.stack)) & 15) == 0;
+}
+
 cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStream_t stream, bool* taken)
 {
     *taken = false;
     const int itemsize = dtype == 0 ? 4 : 2;
-    if (!planes_tma_eligible(a, itemsize))
+    if (!planes_simt_eligible(a, itemsize))
         return cudaSuccess;
     if (a.num_active_dev != nullptr && mode == kGather)
         return cudaSuccess;   // device-side count: the gather goes through the TMA pipeline
     SimtPlan p;
     const int P = a.bSzH * a.bSzW;
-    p.cChunks = FastDiv((uint32_t)((size_t)a.C * itemsize / 128));
+    p.groups = (int)((size_t)a.C * itemsize / 16);
+    p.cChunks = FastDiv((uint32_t)((p.groups + 7) / 8));
     p.blockW = FastDiv((uint32_t)a.bSzW);
     p.pixels = P;
     p.units = itemsize == 4 ? P : P / 2;

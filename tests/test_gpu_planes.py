@@ -30,6 +30,12 @@ SHAPES = [
     (np.float16, 1, 30, 30, 128, (8, 8), (8, 8), (-3, -2)),
     (np.float16, 2, 64, 48, 256, (16, 16), (16, 16), (0, 0)),
     (np.float16, 1, 50, 70, 64, (16, 24), (11, 13), (-7, -9)),   # 384 pixels, overlapping
+    # pixels that are not a multiple of 128 bytes: the last channel chunk is partial (tile CTAs only)
+    (np.float32, 2, 40, 56, 48, (18, 18), (16, 16), (-1, -1)),
+    (np.float32, 1, 30, 30, 12, (8, 8), (8, 8), (0, 0)),
+    (np.float16, 1, 30, 30, 24, (6, 6), (5, 5), (-1, -1)),
+    (np.float16, 2, 64, 48, 200, (16, 16), (16, 16), (0, 0)),
+    (np.float16, 1, 40, 40, 40, (18, 18), (16, 16), (-1, -1)),
 ]
 
 
