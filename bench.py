@@ -53,7 +53,9 @@ def measured_peak():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi.  The sampler is started
+    well before the timed region (nvidia-smi takes a moment to come up); `summary(t0, t1)` keeps the
+    samples that arrived inside the wall-clock window of the load."""
 
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -62,11 +64,11 @@ class ClockSampler:
     def __init__(self, index: int):
         self.index, self.rows, self.proc = index, [], None
 
-    def __enter__(self):
+    def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
@@ -76,21 +78,22 @@ class ClockSampler:
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
 
-    def __exit__(self, *exc):
+    def stop(self):
         if self.proc is not None:
-            time.sleep(0.15)
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
             except Exception:
                 self.proc.kill()
 
-    def summary(self):
+    def summary(self, t0, t1):
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for t, r in self.rows:
+            if not (t0 <= t <= t1 + 0.06):
+                continue
             try:
                 sm.append(float(r[0]))
                 mx.append(float(r[1]))
@@ -200,18 +203,19 @@ def run_ours(args):
     ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
 
     last_counts = [None]
+    pending = [None]
+    side = torch.cuda.Stream() if world > 1 else None
 
-    def step(i, marks=None):
+    def step(i, marks=None, exchange=True):
         m = masks[i % len(masks)]
+        if pending[0] is not None:   # the previous step's all-gather has read the device count by now
+            pending[0].wait()
+            pending[0] = None
         if marks is not None:
             marks[0].record()
         idx, cnt = ops.reduce_mask(m, *g_in.as_lists(), tol=0.5, avgpool=False)
         if marks is not None:
             marks[1].record()
-        work = None
-        if world > 1:  # the only exchange of the path: every rank's block count, read on the device
-            count_dev = ops.scratch_for(dev, torch.cuda.current_stream(dev).cuda_stream)[0][:1]
-            counts_all, work = sbdist.all_gather_counts(count_dev, async_op=True)
         nb = int(cnt[0])
         assert nb == nB, (nb, nB)
         if marks is not None:
@@ -223,8 +227,14 @@ def run_ours(args):
                                transpose=True)
         if marks is not None:
             marks[4].record()
-        if work is not None:
-            work.wait()          # stream-level wait; the host does not block
+        if world > 1 and exchange:
+            # The only exchange of the path: every rank's block count, read from device memory.  It is
+            # issued after gather and scatter are queued, on a side stream (the count is final: the op
+            # interface already synchronised for it), so it overlaps them and nothing waits for it
+            # until the next reduce_mask is about to overwrite the count.
+            count_dev = ops.scratch_for(dev, torch.cuda.current_stream(dev).cuda_stream)[0][:1]
+            with torch.cuda.stream(side):
+                counts_all, pending[0] = sbdist.all_gather_counts(count_dev, async_op=True)
             last_counts[0] = counts_all
         return nb
 
@@ -234,20 +244,37 @@ def run_ours(args):
             dist.barrier()
             torch.cuda.synchronize()
 
+    clocks = ClockSampler(local).start()
     for i in range(args.warmup):
         step(i)
     fence()
     marks = [[ev() for _ in range(5)] for _ in range(args.steps)]
     t0, t1 = ev(), ev()
-    with ClockSampler(local) as clocks:
-        fence()
-        t0.record()
-        blocks = 0
-        for i in range(args.steps):
-            blocks += step(args.warmup + i, marks[i])
-        t1.record()
-        fence()
+    fence()
+    wall0 = time.time()
+    t0.record()
+    blocks = 0
+    for i in range(args.steps):
+        blocks += step(args.warmup + i, marks[i])
+    t1.record()
+    if pending[0] is not None:
+        pending[0].wait()
+        pending[0] = None
+    fence()
     ms_total = t0.elapsed_time(t1)
+    # a short timed region may fall between two clock samples: keep the same load running (untimed)
+    # until at least half a second of it has been sampled
+    extra = 0
+    while time.time() - wall0 < 0.5:
+        step(extra, exchange=False)   # ranks may run different numbers of these: no collective here
+        extra += 1
+    torch.cuda.synchronize()
+    wall1 = time.time()
+    if pending[0] is not None:
+        pending[0].wait()
+        pending[0] = None
+    fence()
+    clocks.stop()
     op_ms = {"reduce_mask": [], "gather": [], "scatter": []}
     for mk in marks:
         op_ms["reduce_mask"].append(mk[0].elapsed_time(mk[1]))
@@ -430,7 +457,7 @@ def run_ours(args):
                          "peak_source": peak_kind, "unit": "GB/s", "frac": gbs[dom] / peak,
                          "traffic": traffic, "algorithmic_bytes": alg[dom]},
             "gpu_launches": 3 * args.steps,
-            "clocks": clocks.summary(),
+            "clocks": clocks.summary(wall0, wall1),
         }
         if sync_free:
             line["sync_free"] = sync_free
