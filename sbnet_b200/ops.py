@@ -23,7 +23,27 @@ _DTYPES = {torch.float32: _lib.SBNET_F32, torch.float16: _lib.SBNET_F16}
 _scratch: dict = {}
 
 
+class _on:
+    """Makes a tensor's device current for the call; free when it already is (the usual case)."""
+
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, device):
+        self.idx = device.index if device.index is not None else torch.cuda.current_device()
+
+    def __enter__(self):
+        self.prev = torch.cuda.current_device()
+        if self.prev != self.idx:
+            torch.cuda.set_device(self.idx)
+
+    def __exit__(self, *exc):
+        if self.prev != self.idx:
+            torch.cuda.set_device(self.prev)
+
+
 def _pair(v, name) -> tuple:
+    if type(v) in (tuple, list) and len(v) == 2 and type(v[0]) is int and type(v[1]) is int:
+        return v[0], v[1]
     if isinstance(v, torch.Tensor):
         v = v.detach().cpu().tolist()
     v = list(v)
@@ -79,7 +99,7 @@ def reduce_mask(mask: torch.Tensor, dynamic_bcount: Sequence[int], dynamic_bsize
     bsh, bsw = _pair(dynamic_bsize, "dynamic_bsize")
     bth, btw = _pair(dynamic_bstride, "dynamic_bstride")
     boh, bow = _pair(dynamic_boffset, "dynamic_boffset")
-    with torch.cuda.device(mask.device):
+    with _on(mask.device):
         stream = _stream(mask.device)
         idx = torch.empty((max(N * bch * bcw, 0), 3), dtype=torch.int16, device=mask.device)
         counts = torch.empty(1, dtype=torch.int32, pin_memory=True)
@@ -101,7 +121,7 @@ def reduce_mask_async(mask, dynamic_bcount, dynamic_bsize, dynamic_bstride, dyna
     bsh, bsw = _pair(dynamic_bsize, "dynamic_bsize")
     bth, btw = _pair(dynamic_bstride, "dynamic_bstride")
     boh, bow = _pair(dynamic_boffset, "dynamic_boffset")
-    with torch.cuda.device(mask.device):
+    with _on(mask.device):
         stream = _stream(mask.device)
         idx = torch.empty((N * bch * bcw, 3), dtype=torch.int16, device=mask.device)
         scratch, flags = scratch_for(mask.device, stream)
@@ -132,7 +152,7 @@ def sparse_gather(x: torch.Tensor, bin_counts, active_block_indices: torch.Tenso
     g = _geom(dynamic_bsize, dynamic_bstride, dynamic_boffset)
     nb = _count(bin_counts)
     shape = (nb, Cc, g[2], g[3]) if transpose else (nb, g[2], g[3], Cc)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         y = out if out is not None else torch.empty(shape, dtype=x.dtype, device=x.device)
         _lib.check(_lib.load().sbnet_sparse_gather(
             x.data_ptr(), _DTYPES[x.dtype], N, H, W, Cc, y.data_ptr(), *g, nb,
@@ -157,7 +177,7 @@ def sparse_scatter_var(x: torch.Tensor, bin_counts, active_block_indices: torch.
     nb = _count(bin_counts)
     if x.numel() != nb * g[2] * g[3] * Cc:
         raise ValueError("x must hold bin_counts[0]*bsize[0]*bsize[1]*C elements")
-    with torch.cuda.device(ybase.device):
+    with _on(ybase.device):
         _lib.check(_lib.load().sbnet_sparse_scatter(
             x.data_ptr(), _DTYPES[ybase.dtype], N, H, W, Cc, ybase.data_ptr(), *g, nb,
             active_block_indices.data_ptr(), int(bool(add)), int(bool(transpose)),
@@ -171,7 +191,7 @@ def copy_tensor(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
     nbytes = src.numel() * src.element_size()
     if dst.numel() * dst.element_size() != nbytes:
         raise ValueError("size mismatch")
-    with torch.cuda.device(dst.device):
+    with _on(dst.device):
         _lib.check(_lib.load().sbnet_copy_tensor(dst.data_ptr(), src.data_ptr(), nbytes,
                                                  _stream(dst.device)))
     return dst
@@ -200,7 +220,7 @@ def sparse_gather_dyn(x, count_dev: torch.Tensor, max_blocks: int, active_block_
     N, H, W, Cc = x.shape
     g = _geom(dynamic_bsize, dynamic_bstride, dynamic_boffset)
     shape = (max_blocks, Cc, g[2], g[3]) if transpose else (max_blocks, g[2], g[3], Cc)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         y = out if out is not None else torch.empty(shape, dtype=x.dtype, device=x.device)
         _lib.check(_lib.load().sbnet_sparse_gather_dyn(
             x.data_ptr(), _DTYPES[x.dtype], N, H, W, Cc, y.data_ptr(), *g, int(max_blocks),
@@ -215,7 +235,7 @@ def sparse_scatter_var_dyn(x, count_dev: torch.Tensor, max_blocks: int, active_b
     _require_cuda(ybase, "ybase")
     N, H, W, Cc = ybase.shape
     g = _geom(dynamic_bsize, dynamic_bstride, dynamic_boffset)
-    with torch.cuda.device(ybase.device):
+    with _on(ybase.device):
         _lib.check(_lib.load().sbnet_sparse_scatter_dyn(
             x.data_ptr(), _DTYPES[ybase.dtype], N, H, W, Cc, ybase.data_ptr(), *g, int(max_blocks),
             count_dev.data_ptr(), active_block_indices.data_ptr(), int(bool(add)),

@@ -33,7 +33,7 @@ def test_gather_and_scatter_gradients_are_the_adjoints(cuda_ops, oracle_port, tr
                                          bsize, bstride, boffset, add=True, atomic=True, transpose=transpose)
     np.testing.assert_allclose(gx.cpu().numpy(), exp, rtol=1e-5, atol=1e-5)
     # <gather(x), gy> == <x, gx>
-    assert abs(float((y * gy).sum()) - float((x * gx).sum())) < 1e-2
+    assert abs(float((y.detach() * gy).sum()) - float((x.detach() * gx).sum())) < 1e-2
 
     disjoint = bstride[0] >= bsize[0] and bstride[1] >= bsize[1]
     shape = (nb, C, *bsize) if transpose else (nb, *bsize, C)

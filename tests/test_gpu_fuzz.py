@@ -1,0 +1,68 @@
+"""Seeded random geometries through all ops on the GPU against the CPU checker (through the C ABI).
+
+Each case draws image size, channel count, block size / stride / offset (overlaps, gaps, blocks
+hanging over every border), dtype, layout and a block list from a seed, then checks reduce_mask
+(both pooling modes), gather (bit-exact), overwrite scatter of gathered values (bit-exact), atomic
+add (tolerance per addend) and, where blocks are disjoint, non-atomic add (bit-exact)."""
+import numpy as np
+import pytest
+
+from sbnet_b200 import configs as cfg
+
+pytestmark = pytest.mark.gpu
+
+CHANNELS = [1, 2, 3, 4, 5, 8, 12, 16, 20, 32, 33, 48, 64, 96, 128, 130]
+
+
+def _draw(seed):
+    rng = np.random.default_rng(1000 + seed)
+    N = int(rng.integers(1, 4))
+    H, W = int(rng.integers(1, 40)), int(rng.integers(1, 40))
+    C = int(rng.choice(CHANNELS))
+    bsize = (int(rng.integers(1, min(H, 20) + 1)), int(rng.integers(1, min(W, 20) + 1)))
+    bstride = (int(rng.integers(1, bsize[0] + 3)), int(rng.integers(1, bsize[1] + 3)))
+    boffset = (int(rng.integers(-bsize[0] + 1, 1)), int(rng.integers(-bsize[1] + 1, 1)))
+    dtype = np.float16 if rng.random() < 0.5 else np.float32
+    return N, H, W, C, bsize, bstride, boffset, dtype, rng
+
+
+@pytest.mark.parametrize("seed", range(120))
+def test_random_geometry(cuda_ops, oracle_port, seed):
+    N, H, W, C, bsize, bstride, boffset, dtype, rng = _draw(seed)
+    g = cfg.geom_for(H, W, bsize, bstride, boffset)
+    # reduce_mask on a real-valued mask, both modes
+    mask = rng.standard_normal((N, H, W, 1)).astype(np.float32)
+    for avg, tol in ((False, 0.8), (True, 0.05)):
+        gi, gc = cuda_ops.reduce_mask(mask, *g.as_lists(), tol=tol, avgpool=avg)
+        oi, oc = oracle_port.reduce_mask(mask, *g.as_lists(), tol=tol, avgpool=avg)
+        n = int(oc[0])
+        assert int(gc[0]) == n
+        assert sorted(map(tuple, gi[:n].tolist())) == sorted(map(tuple, oi[:n].tolist()))
+    idx, cnt = cfg.random_block_list(N, g.bcount, 0.6, seed=seed)
+    nb = int(cnt[0])
+    x = cfg.normal((N, H, W, C), seed, dtype)
+    base = cfg.normal((N, H, W, C), seed + 1, dtype)
+    disjoint = bstride[0] >= bsize[0] and bstride[1] >= bsize[1]
+    cover = -(-bsize[0] // bstride[0]) * -(-bsize[1] // bstride[1])
+    rtol = (1e-6 if dtype == np.float32 else 1e-3) * (1 + cover)
+    for transpose in (False, True):
+        exp = oracle_port.sparse_gather(x, cnt, idx, bsize, bstride, boffset, transpose=transpose)
+        got = cuda_ops.sparse_gather(x, cnt, idx, bsize, bstride, boffset, transpose=transpose)
+        np.testing.assert_array_equal(got, exp)
+        e = oracle_port.sparse_scatter(exp, cnt, idx, base, bsize, bstride, boffset, add=False, transpose=transpose)
+        o = cuda_ops.sparse_scatter(exp, cnt, idx, base, bsize, bstride, boffset, add=False, transpose=transpose)
+        np.testing.assert_array_equal(o, e)
+        shape = (nb, C, *bsize) if transpose else (nb, *bsize, C)
+        stack = cfg.normal(shape, seed + 2, dtype)
+        e = oracle_port.sparse_scatter_var(stack, cnt, idx, base.copy(), bsize, bstride, boffset, add=True,
+                                           atomic=True, transpose=transpose)
+        o = cuda_ops.sparse_scatter_var(stack, cnt, idx, base.copy(), bsize, bstride, boffset, add=True,
+                                        atomic=True, transpose=transpose)
+        err = np.abs(o.astype(np.float64) - e.astype(np.float64)) / np.maximum(np.abs(e.astype(np.float64)), 1.0)
+        assert err.max() <= rtol, (err.max(), rtol)
+        if disjoint:
+            e = oracle_port.sparse_scatter_var(stack, cnt, idx, base.copy(), bsize, bstride, boffset, add=True,
+                                               transpose=transpose)
+            o = cuda_ops.sparse_scatter_var(stack, cnt, idx, base.copy(), bsize, bstride, boffset, add=True,
+                                            transpose=transpose)
+            np.testing.assert_array_equal(o, e)
