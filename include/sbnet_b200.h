@@ -39,6 +39,7 @@ extern "C" {
 
 /* sbnet_reduce_mask flags */
 #define SBNET_SCRATCH_CLEAN 1 /* scratch[2..3] are already zero (see below): skip the memset */
+#define SBNET_COUNT_POLL 2    /* pinned count_host: return as soon as the count has arrived (see below) */
 
 /* int32 words of device scratch sbnet_reduce_mask needs */
 #define SBNET_REDUCE_MASK_SCRATCH_INTS 4
@@ -68,7 +69,11 @@ const char* sbnet_last_error(void);
  *   count_host            host int32 (the op's bin_counts output, reduce_mask.cc:198-220) or NULL.
  *                         When given, the call synchronises `stream` and stores the count.  Pinned
  *                         host memory is written directly by the kernel; pageable memory costs an
- *                         extra copy.  An empty result is reported as ONE block with index (0,0,0),
+ *                         extra copy.  With SBNET_COUNT_POLL (pinned memory only) the call watches that
+ *                         word instead of synchronising the stream and returns as soon as the count is
+ *                         there: the kernel's last index writes may still be in flight, but they are
+ *                         ordered before anything enqueued on `stream` afterwards (use an event or a
+ *                         stream synchronisation before reading the indices from another stream).  An empty result is reported as ONE block with index (0,0,0),
  *                         as the reference does.
  */
 int sbnet_reduce_mask(const float* mask, int N, int H, int W, float tol, int avgpool,

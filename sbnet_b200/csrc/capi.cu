@@ -3,6 +3,7 @@
 #include <limits.h>
 #include <stdarg.h>
 #include <stdio.h>
+#include <time.h>
 
 #include "../../include/sbnet_b200.h"
 #include "common.cuh"
@@ -13,6 +14,7 @@
 namespace {
 
 thread_local char g_err[320] = "";
+constexpr int32_t kCountSentinel = INT32_MIN;
 
 int reject(int code, const char* fmt, ...)
 {
@@ -138,6 +140,8 @@ SBNET_EXPORT int sbnet_reduce_mask(const float* mask, int N, int H, int W, float
         else
             (void)cudaGetLastError();
     }
+    if (hostDev != nullptr && (flags & SBNET_COUNT_POLL))
+        *count_host = kCountSentinel;
     if (!(flags & SBNET_SCRATCH_CLEAN))
         if (cudaError_t e = cudaMemsetAsync(scratch_dev, 0, sizeof(int32_t) * SBNET_REDUCE_MASK_SCRATCH_INTS, s))
             return cuda_status(e);
@@ -146,6 +150,24 @@ SBNET_EXPORT int sbnet_reduce_mask(const float* mask, int N, int H, int W, float
                                                   active_block_indices, scratch_dev, hostDev, s))
         return cuda_status(e);
     if (count_host != nullptr) {
+        if (hostDev != nullptr && (flags & SBNET_COUNT_POLL)) {
+            // The kernel stores the count straight into pinned memory: watching that word is several
+            // times quicker than putting the thread to sleep in a stream synchronisation.  A count is
+            // never negative, so the sentinel written before the launch cannot be mistaken for one.
+            volatile int32_t* word = count_host;
+            timespec t0;
+            clock_gettime(CLOCK_MONOTONIC, &t0);
+            for (unsigned spins = 0; *word == kCountSentinel; ++spins) {
+                if ((spins & 1023u) == 1023u) {
+                    timespec t1;
+                    clock_gettime(CLOCK_MONOTONIC, &t1);
+                    if ((t1.tv_sec - t0.tv_sec) * 1000000000ll + (t1.tv_nsec - t0.tv_nsec) > 200000000ll)
+                        break;   // 0.2 s: let the runtime wait (and report a failed launch, if any)
+                }
+            }
+            if (*word != kCountSentinel)
+                return SBNET_OK;
+        }
         if (hostDev == nullptr)
             if (cudaError_t e = cudaMemcpyAsync(count_host, scratch_dev, sizeof(int32_t),
                                                 cudaMemcpyDeviceToHost, s))

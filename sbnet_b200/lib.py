@@ -13,6 +13,7 @@ LIB_PATH = os.environ.get("SBNET_B200_LIB") or os.path.join(PKG, "libsbnet_b200.
 
 SBNET_F32, SBNET_F16 = 0, 1
 SBNET_SCRATCH_CLEAN = 1
+SBNET_COUNT_POLL = 2
 SBNET_REDUCE_MASK_SCRATCH_INTS = 4
 
 _i, _f, _p, _sz = C.c_int, C.c_float, C.c_void_p, C.c_size_t

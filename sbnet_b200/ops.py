@@ -106,7 +106,7 @@ def reduce_mask(mask: torch.Tensor, dynamic_bcount: Sequence[int], dynamic_bsize
         scratch, flags = scratch_for(mask.device, stream)
         _lib.check(_lib.load().sbnet_reduce_mask(
             mask.data_ptr(), N, H, W, float(tol), int(bool(avgpool)), boh, bow, bsh, bsw, bth, btw,
-            bch, bcw, idx.data_ptr(), scratch.data_ptr(), counts.data_ptr(), flags, stream))
+            bch, bcw, idx.data_ptr(), scratch.data_ptr(), counts.data_ptr(), flags | _lib.SBNET_COUNT_POLL, stream))
     return ReduceMaskResult(idx, counts)
 
 
