@@ -1,0 +1,2 @@
+// Stand-in for the TensorFlow header of the same name (test infrastructure only).
+#include "tf_stub.h"
