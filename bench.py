@@ -581,13 +581,13 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-sync-free", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=12.0)
-    ap.add_argument("--suite", choices=["ops", "one", "resblock"], default=None)
+    ap.add_argument("--suite", choices=["ops", "one", "resblock", "cpu"], default=None)
     ap.add_argument("--case", default="gather_f16_t1")
     ap.add_argument("--density", type=float, default=0.2)
     ap.add_argument("--one-channels", type=int, default=None)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.suite in ("ops", "one", "resblock"):
+    if args.suite in ("ops", "one", "resblock", "cpu"):
         from sbnet_b200 import opbench
         opbench.main(args)
     elif args.impl == "reference":
