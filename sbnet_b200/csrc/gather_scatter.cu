@@ -352,8 +352,11 @@ static void launch_planes(const BlockArgs& a, cudaStream_t stream)
     p.pixFull = FastDiv((uint32_t)p.pixPerChunk);
     p.pixLast = FastDiv((uint32_t)lastPix);
     const long long nItems = (long long)a.numActive * nC * nP;
+    // host-side count: one CTA per item (short CTAs stream faster than a resident grid); device-side
+    // count: one resident wave striding over the items
     static const int wave = resident_ctas(planes_kernel<VB, MODE, T>, kThreads);
-    const int grid = (int)(nItems < wave ? nItems : wave);
+    const bool perItem = a.num_active_dev == nullptr && nItems <= 0x7fffffffll;
+    const unsigned grid = (unsigned)(perItem ? nItems : (nItems < wave ? nItems : wave));
     planes_kernel<VB, MODE, T><<<grid, kThreads, 0, stream>>>(a, p);
 }
 
