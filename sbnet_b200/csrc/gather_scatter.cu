@@ -1,5 +1,6 @@
-// sparse_gather / sparse_scatter for sm_100a -- general kernels (any block size, stride, offset,
-// channel count, fp32 or fp16).
+// sparse_gather / sparse_scatter for sm_100a: the row-layout kernels, the general plane-layout
+// kernel (any block size, stride, offset, channel count, fp32 or fp16), the flat copy, and the
+// dispatch between these and the aligned plane-layout kernels of planes_simt.cu / planes_tma.cu.
 //
 // Replaces the reference's blockGatherTiled0/1 and blockScatterTiled0/1 families and their launcher
 // (sbnet_ops/sparse_blocks.cu.h:68-366, sbnet_ops/sparse_gather.cu:41-266).  Semantics follow the
@@ -11,16 +12,17 @@
 //    the NHWC image and in the stack, so the op is a clipped copy of contiguous runs.  Threads move
 //    the widest vector (16/8/4/2 bytes) that divides C*sizeof(T), several per thread in flight, no
 //    shared memory.
-//  * [nB, C, R, S] ("planes", transpose=true): a CTA stages a tile of pixels x channels (128 bytes of
-//    channels per pixel) in shared memory with an odd word pitch, so that the image side moves
-//    128-byte channel runs and the stack side moves runs of consecutive pixels of one channel plane,
-//    both conflict-free.
+//  * [nB, C, R, S] ("planes", transpose=true): pixels of a multiple of 16 bytes go to the kernels of
+//    planes_simt.cu / planes_tma.cu.  The kernel here takes every other shape: a CTA stages a tile
+//    of pixels x channels (128 bytes of channels per pixel) in shared memory with an odd word pitch,
+//    so that the image side moves channel runs and the stack side moves runs of consecutive pixels
+//    of one channel plane, both conflict-free.
 // Scatter has three write modes: overwrite, read-add-write (legal only for disjoint blocks) and
 // vector reductions (red.global.add .v4.f32 / .v4.f16x2 and narrower) for overlapping halos.
 //
-// The launch is a fixed-size grid of CTAs striding over work items, so the number of active blocks
-// may come from device memory (written by reduce_mask earlier on the same stream) instead of the
-// host.
+// With the block count on the host every work item gets its own short CTA (measured faster on B200
+// than a resident grid); when the count lives in device memory (written by reduce_mask earlier on
+// the same stream) a fixed-size grid strides over the items instead.
 #include <stdlib.h>
 
 #include "common.cuh"

@@ -1,21 +1,25 @@
 // Transposed ([nB,C,R,S]) gather and scatter, one short CTA per tile (sm_100a).
 //
-// Same eligibility and semantics as the TMA pipeline of planes_tma.cu (C*sizeof(T) a multiple of 128
-// bytes, blocks of at most 384 pixels); used when the block count is known on the host, because on
-// B200 a grid of many short CTAs streams measurably faster than a resident grid looping over the
-// same tiles.  A work item is one active block x one 128-byte channel chunk: a tile of P = R*S pixels
-// x 128 bytes, staged ONCE in shared memory and transposed in place through registers:
+// Default implementation of the plane-layout ops for pixels of a multiple of 16 bytes and blocks of
+// at most 384 pixels (an even number for fp16); other shapes run the general kernel of
+// gather_scatter.cu.  Semantics follow the reference CPU functors (sbnet_ops/sparse_gather.cc:61-132,
+// transposed branches).  On B200 a grid of many short CTAs streams measurably faster than a resident
+// grid looping over the same tiles, so with a host-side block count every work item gets its own
+// CTA.  A work item is one active block x one 128-byte channel chunk (the last chunk of a pixel may
+// be narrower): a tile of P = R*S pixels x up to 128 bytes, staged ONCE in shared memory.
 //
 //  gather : every thread issues all of its 16-byte image loads (out-of-image pixels become zeros),
 //           stores them to the tile in [pixel][128 B] order with the 16-byte groups XOR-swizzled by
 //           the pixel index; each thread then reads its share back as 16-byte channel groups, the
 //           CTA synchronises, and the same threads write words of one channel (1 fp32 pixel / 2 fp16
-//           pixels, regrouped with prmt) in [channel][pixel] order into the same buffer.  The tile
-//           leaves as ONE bulk store (TMA engine): a chunk's channel planes are contiguous in the
-//           stack.
-//  scatter: the tile (contiguous in the stack) is copied in with 16-byte loads, then words are
-//           regrouped into 16-byte channel groups and written / added / reduced into the image with
-//           a per-pixel in-range test.
+//           pixels, regrouped with prmt) in [channel][pixel] order into the same buffer (in-place
+//           transpose through registers).  The tile leaves as ONE bulk store (TMA engine): a
+//           chunk's channel planes are contiguous in the stack.
+//  scatter: the tile (contiguous in the stack) is copied in, swizzled so that eight neighbouring
+//           lanes can own the eight 16-byte groups of one pixel; words are regrouped into 16-byte
+//           channel groups and written / added / reduced into the image, whole 128-byte lines per
+//           warp instruction, with a per-pixel in-range test.  With a device-side block count the
+//           same kernel runs as one resident wave striding over the items.
 #include <stdlib.h>
 
 #include "async_ptx.cuh"

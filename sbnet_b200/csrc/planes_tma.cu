@@ -1,8 +1,10 @@
 // Transposed ([nB,C,R,S]) gather and scatter as TMA pipelines (sm_100a).
 //
-// Fast path of the plane-layout ops for the shapes that matter at scale: C*sizeof(T) a multiple of
-// 128 bytes and blocks of at most 384 pixels.  Everything else runs the general kernels of
-// gather_scatter.cu.  Semantics are identical (reference: sbnet_ops/sparse_gather.cc:61-132,
+// Persistent-pipeline implementation of the plane-layout ops for C*sizeof(T) a multiple of 128 bytes
+// and blocks of at most 384 pixels.  It serves gather calls whose block count lives in device memory
+// (a resident grid does not need the count at launch) and is the A/B partner of the one-CTA-per-tile
+// kernels of planes_simt.cu, which take the host-count calls.  Semantics are identical (reference:
+// sbnet_ops/sparse_gather.cc:61-132,
 // transposed branches of sbnet_ops/sparse_blocks.cu.h:135-171 and :217-251).
 //
 // One persistent CTA per SM: a producer warp keeps a ring of shared-memory stages filled through
