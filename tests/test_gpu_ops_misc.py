@@ -162,3 +162,56 @@ def test_cuda_timers(cuda_ops):
     (a * 2).sum().item()
     ms = ops.cuda_timer_end(h)
     assert 0.0 < ms < 5000.0
+
+
+def test_device_count_pipeline_replays_from_a_cuda_graph(cuda_ops, oracle_port):
+    """mask -> gather -> scatter captured once, replayed on two different masks written into the same
+    buffers: the block count never visits the host, so the graph adapts to each mask by itself."""
+    import torch
+    from sbnet_b200 import ops
+    dev = "cuda"
+    N, H, W, C = 2, 64, 48, 64
+    g, go = cfg.halo_geom(H, W), cfg.inner_geom(H, W)
+    max_blocks = N * g.bcount[0] * g.bcount[1]
+    x_h = cfg.normal((N, H, W, C), 1, np.float16)
+    masks = [cfg.rect_union_mask(N, H, W, seed=s, occupancy=occ, side=(4, 12)) for s, occ in ((1, 0.1), (2, 0.35))]
+    mask = torch.from_numpy(masks[0]).to(dev)
+    x = torch.from_numpy(x_h).to(dev)
+    y = torch.zeros_like(x)
+    stack = torch.zeros((max_blocks, C, 18, 18), dtype=torch.float16, device=dev)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+
+    def enqueue():
+        idx, cnt_dev = ops.reduce_mask_async(mask, *g.as_lists(), tol=0.5)
+        ops.sparse_gather_dyn(x, cnt_dev, max_blocks, idx, g.bsize, g.bstride, g.boffset, transpose=True, out=stack)
+        inner = stack[:, :, 1:17, 1:17].contiguous()
+        ops.sparse_scatter_var_dyn(inner, cnt_dev, max_blocks, idx, y, go.bsize, go.bstride, go.boffset, add=True,
+                                   transpose=True)
+        return idx, cnt_dev
+
+    with torch.cuda.stream(side):
+        enqueue()                                   # warm-up: scratch allocation, lazy loading
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        idx, cnt_dev = enqueue()
+    counts = []
+    for m_h in masks:
+        mask.copy_(torch.from_numpy(m_h))
+        y.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        oi, oc = oracle_port.reduce_mask(m_h, *g.as_lists(), tol=0.5)
+        n = int(oc[0])
+        counts.append(n)
+        assert int(cnt_dev[0]) == n
+        got_idx = idx[:n].cpu().numpy()
+        assert sorted(map(tuple, got_idx.tolist())) == sorted(map(tuple, oi[:n].tolist()))
+        # reference result: gather interiors of the active blocks added onto zeros == x on those pixels
+        st = oracle_port.sparse_gather(x_h, oc, oi, g.bsize, g.bstride, g.boffset, transpose=True)
+        exp = oracle_port.sparse_scatter_var(np.ascontiguousarray(st[:, :, 1:17, 1:17]), oc, oi, np.zeros_like(x_h),
+                                             go.bsize, go.bstride, go.boffset, add=True, transpose=True)
+        np.testing.assert_array_equal(y.cpu().numpy(), exp)
+    assert counts[0] != counts[1]
