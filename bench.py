@@ -524,6 +524,65 @@ def cpu_pipeline(args, mask_h, N, H, W, C, budget_s=12.0, steps=1):
             "us_per_block": {"gather": t_g / M * 1e6, "scatter_add": t_s / M * 1e6}}
 
 
+def cpu_suite(args):
+    """``bench.py --suite cpu``: the reference's CPU functors (compiled from the reference tree when
+    available, else the C restatement) on bounded samples of the op-level configurations, all host
+    threads.  One JSON line per case; reported beside the GPU numbers, not a target."""
+    from oracle import oracle   # the checker, timed here as the CPU baseline (never used by the product)
+    kind = "ref" if oracle.have_ref() else "port"
+    if kind == "port":
+        oracle.build(ref=False)
+    o = oracle.get(kind)
+    cores = o.max_threads()
+    o.set_threads(cores)
+
+    def line(case, seconds, units, unit_name, nbytes, sample):
+        print(json.dumps({"case": "cpu_" + case, "kind": "reference" if kind == "ref" else "port", "cores": cores,
+                          "seconds": seconds, unit_name + "/s": units / seconds, "GB/s": nbytes / seconds / 1e9,
+                          "sample": sample}), flush=True)
+
+    def best(fn, reps=3):
+        out = []
+        for _ in range(reps):
+            t = time.perf_counter()
+            fn()
+            out.append(time.perf_counter() - t)
+        return min(out)
+
+    c2 = cfg.config2(0)
+    g = c2["geom"]
+    for run in c2["runs"]:
+        dt = best(lambda: o.reduce_mask(c2["mask"], *g.as_lists(), tol=run["tol"], avgpool=run["avgpool"]))
+        line("reduce_mask_" + ("avg" if run["avgpool"] else "max"), dt, 1, "masks", c2["mask"].nbytes,
+             "full [8,800,704] mask, single thread (the functor is not threaded)")
+    N, H, W = 8, 512, 512
+    g = cfg.halo_geom(H, W)
+    idx, cnt = cfg.random_block_list(N, g.bcount, 0.2, seed=20)
+    for dtype, tname, C in ((np.float32, "f32", 128), (np.float16, "f16", 128)):
+        x = cfg.normal((N, H, W, C), 1, dtype)
+        nb = min(int(cnt[0]), 1600)
+        m = np.array([nb], np.int32)
+        for tr in (False, True):
+            dt = best(lambda: o.sparse_gather(x, m, idx, g.bsize, g.bstride, g.boffset, transpose=tr))
+            line(f"gather_{tname}_t{int(tr)}", dt, nb, "blocks", 2 * nb * 324 * C * x.itemsize,
+                 f"first {nb} blocks of the 20 % list on x [8,512,512,128]")
+    C = 64
+    base = cfg.normal((N, H, W, C), 2)
+    m = np.array([64], np.int32)
+    stack = cfg.normal((64, 18, 18, C), 3)
+    dt = best(lambda: o.sparse_scatter_var(stack, m, idx, base, g.bsize, g.bstride, g.boffset, add=True, atomic=True), 2)
+    line("scatter_f32_add", dt, 64, "blocks", 3 * 64 * 324 * C * 4,
+         "first 64 blocks, add=True (one global lock per added element in the reference)")
+    gi = cfg.inner_geom(H, W)
+    base16 = cfg.normal((N, H, W, C), 4, np.float16)
+    nb = min(int(cnt[0]), 1600)
+    m = np.array([nb], np.int32)
+    stack16 = cfg.normal((nb, C, 16, 16), 5, np.float16)
+    dt = best(lambda: o.sparse_scatter_var(stack16, m, idx, base16, gi.bsize, gi.bstride, gi.boffset, add=False,
+                                           transpose=True))
+    line("scatter_f16_t1_set", dt, nb, "blocks", 2 * nb * 256 * C * 2, f"first {nb} blocks, overwrite, transposed stack")
+
+
 def run_reference(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -587,7 +646,9 @@ def main():
     ap.add_argument("--one-channels", type=int, default=None)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.suite in ("ops", "one", "resblock", "cpu"):
+    if args.suite == "cpu":
+        cpu_suite(args)
+    elif args.suite in ("ops", "one", "resblock"):
         from sbnet_b200 import opbench
         opbench.main(args)
     elif args.impl == "reference":

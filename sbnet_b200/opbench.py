@@ -162,8 +162,6 @@ def main(args):
         return one(args)
     if getattr(args, "suite", None) == "resblock":
         return resblock(args)
-    if getattr(args, "suite", None) == "cpu":
-        return cpu_reference(args)
     build.build_library()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -326,67 +324,3 @@ def main(args):
         tag = "avg" if run["avgpool"] else "max"
         emit(f"reduce_mask_{tag}_graph_replay_per_launch", med / 32, mn / 32, 18022400, {"launches_per_replay": 32})
 
-
-def cpu_reference(args):
-    """``bench.py --suite cpu``: the reference's CPU functors (compiled from the reference tree when
-    available, else the C restatement) on bounded samples of the op-level configurations, all host
-    threads.  One JSON line per case; reported beside the GPU numbers, not a target."""
-    import time
-    import os
-    import sys
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    if root not in sys.path:
-        sys.path.insert(0, root)
-    from oracle import oracle   # test/benchmark infrastructure: the checker, timed as the CPU baseline
-    kind = "ref" if oracle.have_ref() else "port"
-    if kind == "port":
-        oracle.build(ref=False)
-    o = oracle.get(kind)
-    cores = o.max_threads()
-    o.set_threads(cores)
-
-    def line(case, seconds, units, unit_name, nbytes, sample):
-        print(json.dumps({"case": "cpu_" + case, "kind": "reference" if kind == "ref" else "port", "cores": cores,
-                          "seconds": seconds, unit_name + "/s": units / seconds, "GB/s": nbytes / seconds / 1e9,
-                          "sample": sample}), flush=True)
-
-    def best(fn, reps=3):
-        out = []
-        for _ in range(reps):
-            t = time.perf_counter()
-            fn()
-            out.append(time.perf_counter() - t)
-        return min(out)
-
-    c2 = cfg.config2(0)
-    g = c2["geom"]
-    for run in c2["runs"]:
-        dt = best(lambda: o.reduce_mask(c2["mask"], *g.as_lists(), tol=run["tol"], avgpool=run["avgpool"]))
-        line("reduce_mask_" + ("avg" if run["avgpool"] else "max"), dt, 1, "masks", c2["mask"].nbytes,
-             "full [8,800,704] mask, single thread (the functor is not threaded)")
-    N, H, W = 8, 512, 512
-    g = cfg.halo_geom(H, W)
-    idx, cnt = cfg.random_block_list(N, g.bcount, 0.2, seed=20)
-    for dtype, tname, C in ((np.float32, "f32", 128), (np.float16, "f16", 128)):
-        x = cfg.normal((N, H, W, C), 1, dtype)
-        nb = min(int(cnt[0]), 1600)
-        m = np.array([nb], np.int32)
-        for tr in (False, True):
-            dt = best(lambda: o.sparse_gather(x, m, idx, g.bsize, g.bstride, g.boffset, transpose=tr))
-            line(f"gather_{tname}_t{int(tr)}", dt, nb, "blocks", 2 * nb * 324 * C * x.itemsize,
-                 f"first {nb} blocks of the 20 % list on x [8,512,512,128]")
-    C = 64
-    base = cfg.normal((N, H, W, C), 2)
-    m = np.array([64], np.int32)
-    stack = cfg.normal((64, 18, 18, C), 3)
-    dt = best(lambda: o.sparse_scatter_var(stack, m, idx, base, g.bsize, g.bstride, g.boffset, add=True, atomic=True), 2)
-    line("scatter_f32_add", dt, 64, "blocks", 3 * 64 * 324 * C * 4,
-         "first 64 blocks, add=True (one global lock per added element in the reference)")
-    gi = cfg.inner_geom(H, W)
-    base16 = cfg.normal((N, H, W, C), 4, np.float16)
-    nb = min(int(cnt[0]), 1600)
-    m = np.array([nb], np.int32)
-    stack16 = cfg.normal((nb, C, 16, 16), 5, np.float16)
-    dt = best(lambda: o.sparse_scatter_var(stack16, m, idx, base16, gi.bsize, gi.bstride, gi.boffset, add=False,
-                                           transpose=True))
-    line("scatter_f16_t1_set", dt, nb, "blocks", 2 * nb * 256 * C * 2, f"first {nb} blocks, overwrite, transposed stack")

@@ -82,3 +82,13 @@ def test_ops_refuse_cpu_tensors():
     with pytest.raises(ValueError, match="CUDA tensor"):
         ops.sparse_gather(torch.zeros(1, 4, 4, 1), [1], torch.zeros(1, 3, dtype=torch.int16), [2, 2],
                           [2, 2], [0, 0])
+
+
+def test_product_package_never_touches_the_checker():
+    """The CPU checker is test infrastructure: nothing under sbnet_b200/ may import, load or run it."""
+    pkg = os.path.join(ROOT, "sbnet_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for name in files:
+            if name.endswith((".py", ".cu", ".cuh", ".h", ".cc")):
+                text = open(os.path.join(dirpath, name), errors="replace").read()
+                assert "oracle" not in text.lower(), os.path.join(dirpath, name)
