@@ -52,7 +52,14 @@ def _pair(v, name) -> tuple:
     return int(v[0]), int(v[1])
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream(device) -> int:
+    """Handle of torch's current stream on ``device`` (the raw getter skips building a Stream object)."""
+    if _raw_stream is not None:
+        idx = device.index
+        return _raw_stream(torch.cuda.current_device() if idx is None else idx)
     return torch.cuda.current_stream(device).cuda_stream
 
 
@@ -73,7 +80,7 @@ def _count(bin_counts) -> int:
 
 def scratch_for(device, stream: int) -> tuple:
     """Per (device, stream) reduce_mask scratch, zero-filled once; later calls pass SCRATCH_CLEAN."""
-    key = (torch.device(device).index, stream)
+    key = (device.index if isinstance(device, torch.device) else torch.device(device).index, stream)
     hit = _scratch.get(key)
     if hit is None:
         buf = torch.zeros(_lib.SBNET_REDUCE_MASK_SCRATCH_INTS, dtype=torch.int32, device=device)
