@@ -126,3 +126,49 @@ def test_pageable_count_host(cuda_ops):
                                       torch.cuda.current_stream().cuda_stream)
     assert rc == 0 and out.value == 32
     assert scratch.cpu().tolist() == [32, 0, 0, 0]
+
+
+def test_two_thousand_calls_on_one_self_resetting_scratch(cuda_ops):
+    """The scratch word is zero-filled once and then only reset by the kernel itself; alternate
+    masks of different counts for many calls (polled and device-side counts) and check each one."""
+    import torch
+    from sbnet_b200 import ops
+    g = cfg.halo_geom(160, 176)
+    masks_h = [cfg.rect_union_mask(2, 160, 176, seed=s, n_rects=k) for s, k in ((1, 3), (2, 12), (3, 0), (4, 30))]
+    masks = [torch.from_numpy(m).cuda() for m in masks_h]
+    expect = []
+    for m in masks:
+        idx, cnt = ops.reduce_mask(m, *g.as_lists(), tol=0.5)
+        expect.append(int(cnt[0]))
+    assert expect[2] == 1 and len(set(expect)) == 4
+    for i in range(2000):
+        k = (i * 7 + i // 3) % 4
+        if i % 5 == 0:
+            idx, cnt_dev = ops.reduce_mask_async(masks[k], *g.as_lists(), tol=0.5)
+            got = int(cnt_dev.cpu()[0])
+        else:
+            idx, cnt = ops.reduce_mask(masks[k], *g.as_lists(), tol=0.5)
+            got = int(cnt[0])
+        assert got == expect[k], (i, k, got, expect[k])
+    torch.cuda.synchronize()
+    stream = torch.cuda.current_stream().cuda_stream
+    assert ops.scratch_for(masks[0].device, stream)[0].cpu().tolist()[2:] == [0, 0]
+
+
+def test_two_streams_with_their_own_scratch_do_not_interfere(cuda_ops):
+    import torch
+    from sbnet_b200 import ops
+    g = cfg.halo_geom(160, 176)
+    a = torch.from_numpy(cfg.rect_union_mask(2, 160, 176, seed=5, n_rects=5)).cuda()
+    b = torch.from_numpy(cfg.rect_union_mask(2, 160, 176, seed=6, n_rects=25)).cuda()
+    na = int(ops.reduce_mask(a, *g.as_lists(), tol=0.5)[1][0])
+    nb = int(ops.reduce_mask(b, *g.as_lists(), tol=0.5)[1][0])
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    outs = []
+    for i in range(200):
+        with torch.cuda.stream(s1):
+            outs.append((ops.reduce_mask_async(a, *g.as_lists(), tol=0.5)[1].clone(), na))
+        with torch.cuda.stream(s2):
+            outs.append((ops.reduce_mask_async(b, *g.as_lists(), tol=0.5)[1].clone(), nb))
+    torch.cuda.synchronize()
+    assert all(int(c[0]) == n for c, n in outs)
