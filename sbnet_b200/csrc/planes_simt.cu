@@ -1,8 +1,8 @@
 // Transposed ([nB,C,R,S]) gather and scatter, one short CTA per tile (sm_100a).
 //
-// Default implementation of the plane-layout ops for pixels of a multiple of 16 bytes and blocks of
-// at most 384 pixels (an even number for fp16); other shapes run the general kernel of
-// gather_scatter.cu.  Semantics follow the reference CPU functors (sbnet_ops/sparse_gather.cc:61-132,
+// Default implementation of the plane-layout ops for pixels of a multiple of 16 bytes (an even
+// number of pixels per block for fp16; blocks of more than 384 pixels are cut into pixel chunks);
+// other shapes run the general kernel of gather_scatter.cu.  Semantics follow the reference CPU functors (sbnet_ops/sparse_gather.cc:61-132,
 // transposed branches).  On B200 a grid of many short CTAs streams measurably faster than a resident
 // grid looping over the same tiles, so with a host-side block count every work item gets its own
 // CTA.  A work item is one active block x one 128-byte channel chunk (the last chunk of a pixel may
@@ -35,6 +35,10 @@ constexpr int kPsMaxVecs = (8 * kPsMaxPixels) / kPsThreads;   // 16-byte vectors
 
 struct SimtPlan {
     FastDiv cChunks;   // 128-byte channel chunks per pixel
+    FastDiv pChunks;   // pixel chunks per block (1 unless the block has more than 384 pixels)
+    FastDiv unitsPerRowLast; // unitsPerRow of a block's last (shorter) pixel chunk
+    int chunkPixels;   // pixels per pixel chunk (a multiple of 8); the last chunk of a block may hold fewer
+    int rowsAligned;   // every plane row of every pixel chunk starts and ends on a 16-byte boundary
     FastDiv blockW;    // S
     FastDiv unitsPerRow; // copy-in units (GW words each) per channel plane (swizzled scatter only)
     int pitchWords;    // tile row pitch of the swizzled scatter: units rounded up to 32
@@ -43,7 +47,9 @@ struct SimtPlan {
     int units;         // words per channel plane: P (fp32) or P/2 (fp16)
 };
 
-template <typename T>
+// PCH: blocks of more than 384 pixels are cut into pixel chunks; a work item is then (block, pixel
+// chunk, channel chunk) and its transposed tile leaves as one run per channel plane.
+template <typename T, bool PCH>
 __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gather_simt(const BlockArgs a, const SimtPlan p)
 {
     __shared__ __align__(1024) unsigned char tileRaw[kPsTileBytes];
@@ -53,13 +59,22 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
     const uint32_t tile = smem_u32(tileRaw);
 
     uint32_t ib, cc;
-    p.cChunks.divmod(blockIdx.x, ib, cc);
+    int p0 = 0, P = p.pixels, U = p.units;   // first pixel, pixels and words per plane row of this item
+    if constexpr (PCH) {
+        uint32_t rest, pc;
+        p.cChunks.divmod(blockIdx.x, rest, cc);
+        p.pChunks.divmod(rest, ib, pc);
+        p0 = (int)pc * p.chunkPixels;
+        P = min(p.chunkPixels, p.pixels - p0);
+        U = P / EPW;
+    } else {
+        p.cChunks.divmod(blockIdx.x, ib, cc);
+    }
     const int n = a.idx[ib * 3 + 0];
     const int h0 = a.bOffsH + a.idx[ib * 3 + 1] * a.bStrH;
     const int w0 = a.bOffsW + a.idx[ib * 3 + 2] * a.bStrW;
     const T* imgN = reinterpret_cast<const T*>(a.image) + (long long)n * a.H * a.W * a.C +
                     (long long)cc * (128 / (int)sizeof(T));
-    const int P = p.pixels, U = p.units;
     const int nG = min(8, p.groups - 8 * (int)cc);   // 16-byte groups in this chunk
 
     // ---- image -> tile: thread owns 16-byte group j of pixels px0, px0+32, ...
@@ -72,7 +87,7 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
             v[k] = make_uint4(0, 0, 0, 0);
             if (px < P && j < nG) {
                 uint32_t r, s;
-                p.blockW.divmod((uint32_t)px, r, s);
+                p.blockW.divmod((uint32_t)(px + p0), r, s);
                 const int h = h0 + (int)r, w = w0 + (int)s;
                 if (h >= 0 && h < a.H && w >= 0 && w < a.W)
                     v[k] = ld_stream(reinterpret_cast<const uint4*>(imgN + ((long long)h * a.W + w) * a.C + j * CPG));
@@ -132,8 +147,34 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
     }
     fence_async_smem();   // the bulk store reads what the generic proxy just wrote
     __syncthreads();
-    if (threadIdx.x == 0) {
-        T* dst = reinterpret_cast<T*>(a.stack) + ((long long)ib * a.C + (long long)cc * (128 / (int)sizeof(T))) * P;
+    T* dst = reinterpret_cast<T*>(a.stack) +
+             ((long long)ib * a.C + (long long)cc * (128 / (int)sizeof(T))) * p.pixels + p0;
+    if constexpr (PCH) {
+        // one run of U words per channel plane, p.pixels elements apart
+        const int rows = nG * CPG;
+        if (p.rowsAligned) {
+            if ((int)threadIdx.x < rows) {
+                bulk_store_1d(dst + (long long)threadIdx.x * p.pixels, tile + threadIdx.x * (uint32_t)U * 4u, (uint32_t)U * 4u);
+                bulk_wait_read<0>();
+            }
+        } else if ((p.pixels / EPW) % 2 == 0) {   // rows of an even number of words: 8-byte stores
+            uint2* dst2 = reinterpret_cast<uint2*>(dst);
+            const long long row2 = p.pixels / EPW / 2;
+            const int U2 = U / 2;
+            for (int c = threadIdx.x >> 5; c < rows; c += kPsThreads / 32)
+                for (int u = threadIdx.x & 31; u < U2; u += 32) {
+                    uint2 v;
+                    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(tile + (uint32_t)(c * U2 + u) * 8u));
+                    dst2[c * row2 + u] = v;
+                }
+        } else {
+            uint32_t* dstW = reinterpret_cast<uint32_t*>(dst);   // rows start on word boundaries (fp16: P even)
+            const long long rowW = p.pixels / EPW;
+            for (int c = threadIdx.x >> 5; c < rows; c += kPsThreads / 32)
+                for (int u = threadIdx.x & 31; u < U; u += 32)
+                    dstW[c * rowW + u] = lds32(tile + (uint32_t)(c * U + u) * 4u);
+        }
+    } else if (threadIdx.x == 0) {
         bulk_store_1d(dst, tile, (uint32_t)(16 * nG * P));
         bulk_wait_read<0>();   // shared memory must outlive the engine's read of it
     }
@@ -146,10 +187,12 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
 // of sixteen scattered sectors (measured: 5.3 -> 6.4 TB/s on the fp16 add scatter).  GW is the
 // copy-in unit in words (a unit must not straddle plane rows).  GW == 0 (odd row length): dense
 // tile, sixteen-pixel lane mapping.
-template <int MODE, typename T, int GW>
+// PCH (GW > 0 only): blocks of more than 384 pixels, cut into pixel chunks as in the gather.
+template <int MODE, typename T, int GW, bool PCH>
 __global__ void __launch_bounds__(kPsThreads, MODE == kScatterAdd ? 2 : 3)
 planes_scatter_simt(const BlockArgs a, const SimtPlan p)
 {
+    static_assert(!PCH || GW > 0, "pixel chunks need the swizzled tile");
     __shared__ __align__(128) unsigned char tileRaw[kPsTileBytes];
     constexpr int EPW = 4 / (int)sizeof(T);
     constexpr int CPG = 16 / (int)sizeof(T);
@@ -163,22 +206,34 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
     int nActive = a.numActive;
     if (a.num_active_dev != nullptr)
         nActive = min(__ldg(a.num_active_dev), a.numActive);
-    const long long nItems = (long long)nActive * p.cChunks.div;
+    const long long nItems = (long long)nActive * p.cChunks.div * (PCH ? p.pChunks.div : 1u);
     for (long long item = blockIdx.x; item < nItems; item += gridDim.x) {
     uint32_t ib, cc;
-    p.cChunks.divmod((uint32_t)item, ib, cc);
+    int p0 = 0, P = p.pixels, U = p.units;   // first pixel, pixels and words per plane row of this item
+    FastDiv unitsPerRow = p.unitsPerRow;
+    if constexpr (PCH) {
+        uint32_t rest, pc;
+        p.cChunks.divmod((uint32_t)item, rest, cc);
+        p.pChunks.divmod(rest, ib, pc);
+        p0 = (int)pc * p.chunkPixels;
+        P = min(p.chunkPixels, p.pixels - p0);
+        U = P / EPW;
+        if (pc + 1 == p.pChunks.div)
+            unitsPerRow = p.unitsPerRowLast;
+    } else {
+        p.cChunks.divmod((uint32_t)item, ib, cc);
+    }
     const int n = a.idx[ib * 3 + 0];
     const int h0 = a.bOffsH + a.idx[ib * 3 + 1] * a.bStrH;
     const int w0 = a.bOffsW + a.idx[ib * 3 + 2] * a.bStrW;
     T* imgN = reinterpret_cast<T*>(a.image) + (long long)n * a.H * a.W * a.C + (long long)cc * (128 / (int)sizeof(T));
-    const int P = p.pixels, U = p.units;
     const int nG = min(8, p.groups - 8 * (int)cc);   // 16-byte groups in this chunk
     const int nTasks = SWZ ? 8 * U : ((U + 15) >> 4) * 128;
     const uint32_t pitchW = SWZ ? (uint32_t)p.pitchWords : (uint32_t)U;   // tile row pitch in words
 
     auto dest = [&](int pix, int j) -> uint4* {
         uint32_t r, sx;
-        p.blockW.divmod((uint32_t)pix, r, sx);
+        p.blockW.divmod((uint32_t)(pix + p0), r, sx);
         const int h = h0 + (int)r, w = w0 + (int)sx;
         if (h < 0 || h >= a.H || w < 0 || w >= a.W)
             return nullptr;
@@ -196,9 +251,19 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
         }
     };
 
-    // ---- stack -> tile: the chunk's planes are one contiguous run of 32*P words
+    // ---- stack -> tile: the chunk's planes are one contiguous run of 32*P words (pixel chunks: one
+    // run of U words per plane, p.pixels elements apart)
     {
-        const T* srcT = reinterpret_cast<const T*>(a.stack) + ((long long)ib * a.C + (long long)cc * (128 / (int)sizeof(T))) * P;
+        const T* srcT = reinterpret_cast<const T*>(a.stack) +
+                        ((long long)ib * a.C + (long long)cc * (128 / (int)sizeof(T))) * p.pixels + p0;
+        // unit vi = (plane c, column col) -> offset from srcT in copy-in units
+        const uint32_t rowUnits = PCH ? (uint32_t)(p.pixels / EPW / (GW > 0 ? GW : 1)) : 0u;
+        auto srcOff = [&](uint32_t vi, uint32_t c, uint32_t col) -> uint32_t {
+            if constexpr (PCH)
+                return c * rowUnits + col;
+            else
+                return vi;
+        };
         if constexpr (GW == 2) {
             const uint2* src = reinterpret_cast<const uint2*>(srcT);
             const int nUnit = 2 * nG * P;
@@ -206,15 +271,21 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
             for (int half = 0; half < 2; ++half) {   // two batches keep the register count under the launch bound
                 uint2 v[kPsMaxVecs];
 #pragma unroll
-                for (int k = 0; k < kPsMaxVecs; ++k)
-                    if ((int)threadIdx.x + (half * kPsMaxVecs + k) * kPsThreads < nUnit)
-                        v[k] = ld_stream(src + threadIdx.x + (half * kPsMaxVecs + k) * kPsThreads);
+                for (int k = 0; k < kPsMaxVecs; ++k) {
+                    const int vi = (int)threadIdx.x + (half * kPsMaxVecs + k) * kPsThreads;
+                    if (vi < nUnit) {
+                        uint32_t c = 0, col = 0;
+                        if constexpr (PCH)
+                            unitsPerRow.divmod((uint32_t)vi, c, col);
+                        v[k] = ld_stream(src + srcOff((uint32_t)vi, c, col));
+                    }
+                }
 #pragma unroll
                 for (int k = 0; k < kPsMaxVecs; ++k) {
                     const int vi = (int)threadIdx.x + (half * kPsMaxVecs + k) * kPsThreads;
                     if (vi < nUnit) {
                         uint32_t c, col;
-                        p.unitsPerRow.divmod((uint32_t)vi, c, col);
+                        unitsPerRow.divmod((uint32_t)vi, c, col);
                         const uint32_t w = c * pitchW + ((col * 2u) ^ (4u * ((c / CPG) & 7u)));
                         asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(tile + w * 4u), "r"(v[k].x), "r"(v[k].y)
                                      : "memory");
@@ -224,22 +295,33 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
         } else {
             const uint4* src = reinterpret_cast<const uint4*>(srcT);
             const int nVec = nG * P;
-            uint4 v[kPsMaxVecs];
+            // pixel chunks: the per-unit row arithmetic costs registers, so two batches as above
+            constexpr int kBatches = PCH ? 2 : 1, kPer = kPsMaxVecs / kBatches;
 #pragma unroll
-            for (int k = 0; k < kPsMaxVecs; ++k)
-                if ((int)threadIdx.x + k * kPsThreads < nVec)
-                    v[k] = ld_stream(src + threadIdx.x + k * kPsThreads);
+            for (int b = 0; b < kBatches; ++b) {
+                uint4 v[kPer];
 #pragma unroll
-            for (int k = 0; k < kPsMaxVecs; ++k) {
-                const int vi = (int)threadIdx.x + k * kPsThreads;
-                if (vi < nVec) {
-                    uint32_t w = (uint32_t)vi * 4u;
-                    if constexpr (GW == 4) {   // row = channel; XOR the 16-byte column group with the channel group
-                        uint32_t c, col;
-                        p.unitsPerRow.divmod((uint32_t)vi, c, col);
-                        w = c * pitchW + ((col * 4u) ^ (4u * ((c / CPG) & 7u)));
+                for (int k = 0; k < kPer; ++k) {
+                    const int vi = (int)threadIdx.x + (b * kPer + k) * kPsThreads;
+                    if (vi < nVec) {
+                        uint32_t c = 0, col = 0;
+                        if constexpr (PCH)
+                            unitsPerRow.divmod((uint32_t)vi, c, col);
+                        v[k] = ld_stream(src + srcOff((uint32_t)vi, c, col));
                     }
-                    sts128(tile + w * 4u, v[k]);
+                }
+#pragma unroll
+                for (int k = 0; k < kPer; ++k) {
+                    const int vi = (int)threadIdx.x + (b * kPer + k) * kPsThreads;
+                    if (vi < nVec) {
+                        uint32_t w = (uint32_t)vi * 4u;
+                        if constexpr (GW == 4) {   // row = channel; XOR the 16-byte column group with the channel group
+                            uint32_t c, col;
+                            unitsPerRow.divmod((uint32_t)vi, c, col);
+                            w = c * pitchW + ((col * 4u) ^ (4u * ((c / CPG) & 7u)));
+                        }
+                        sts128(tile + w * 4u, v[k]);
+                    }
                 }
             }
         }
@@ -298,15 +380,16 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
     }
 }
 
-// Pixels of a multiple of 16 bytes (the last 128-byte chunk may be partial), blocks of at most 384
-// pixels (an even number for fp16), 16-byte aligned buffers.
+// Pixels of a multiple of 16 bytes (the last 128-byte chunk may be partial), an even number of
+// pixels per block for fp16, 16-byte aligned buffers.  Blocks of more than 384 pixels run as pixel
+// chunks (the scatter then needs plane rows of an even number of words).
 static bool planes_simt_eligible(const BlockArgs& a, int itemsize)
 {
     const char* off = getenv("SBNET_DISABLE_TMA");
     if (off && off[0] == '1')
         return false;
     const long long P = (long long)a.bSzH * a.bSzW;
-    if (((size_t)a.C * itemsize) % 16 != 0 || P > kPsMaxPixels || (itemsize == 2 && (P & 1)))
+    if (((size_t)a.C * itemsize) % 16 != 0 || P > (1 << 24) || (itemsize == 2 && (P & 1)))
         return false;
     return ((reinterpret_cast<uintptr_t>(a.image) | reinterpret_cast<uintptr_t>(a.stack)) & 15) == 0;
 }
@@ -327,9 +410,21 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
     p.pixels = P;
     p.units = itemsize == 4 ? P : P / 2;
     const int gw = p.units % 4 == 0 ? 4 : (p.units % 2 == 0 ? 2 : 0);
-    p.unitsPerRow = FastDiv((uint32_t)(gw ? p.units / gw : 1));
-    p.pitchWords = (p.units + 31) & ~31;
-    const long long nItems = (long long)a.numActive * p.cChunks.div;
+    // Blocks of more than 384 pixels: the fewest equal pixel chunks, each a multiple of 8 pixels.
+    const int nPc = (P + kPsMaxPixels - 1) / kPsMaxPixels;
+    const bool pch = nPc > 1;
+    if (pch && mode != kGather && gw == 0)
+        return cudaSuccess;
+    const int epw = 4 / itemsize;
+    p.chunkPixels = pch ? (((P + nPc - 1) / nPc + 7) & ~7) : P;
+    p.pChunks = FastDiv((uint32_t)((P + p.chunkPixels - 1) / p.chunkPixels));
+    const int chunkUnits = p.chunkPixels / epw;
+    const int lastUnits = (P - ((int)p.pChunks.div - 1) * p.chunkPixels) / epw;
+    p.rowsAligned = ((size_t)P * itemsize) % 16 == 0;
+    p.unitsPerRow = FastDiv((uint32_t)(gw ? (pch ? chunkUnits : p.units) / gw : 1));
+    p.unitsPerRowLast = FastDiv((uint32_t)(gw ? (pch ? lastUnits : p.units) / gw : 1));
+    p.pitchWords = ((pch ? chunkUnits : p.units) + 31) & ~31;
+    const long long nItems = (long long)a.numActive * p.cChunks.div * p.pChunks.div;
     if (nItems > 0x7fffffffll)
         return cudaSuccess;
     unsigned grid = (unsigned)nItems;
@@ -339,19 +434,30 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
     }
 #define SBNET_PS(KERNEL) KERNEL<<<grid, kPsThreads, 0, stream>>>(a, p)
     if (mode == kGather) {
-        if (dtype == 0)
-            SBNET_PS(planes_gather_simt<float>);
-        else
-            SBNET_PS(planes_gather_simt<__half>);
+        if (dtype == 0) {
+            if (pch)
+                SBNET_PS((planes_gather_simt<float, true>));
+            else
+                SBNET_PS((planes_gather_simt<float, false>));
+        } else {
+            if (pch)
+                SBNET_PS((planes_gather_simt<__half, true>));
+            else
+                SBNET_PS((planes_gather_simt<__half, false>));
+        }
     } else if (dtype == 0) {
-#define SBNET_PS_SC(M, T_)                                    \
-    do {                                                      \
-        if (gw == 4)                                          \
-            SBNET_PS((planes_scatter_simt<M, T_, 4>));        \
-        else if (gw == 2)                                     \
-            SBNET_PS((planes_scatter_simt<M, T_, 2>));        \
-        else                                                  \
-            SBNET_PS((planes_scatter_simt<M, T_, 0>));        \
+#define SBNET_PS_SC(M, T_)                                           \
+    do {                                                             \
+        if (gw == 4 && pch)                                          \
+            SBNET_PS((planes_scatter_simt<M, T_, 4, true>));         \
+        else if (gw == 4)                                            \
+            SBNET_PS((planes_scatter_simt<M, T_, 4, false>));        \
+        else if (gw == 2 && pch)                                     \
+            SBNET_PS((planes_scatter_simt<M, T_, 2, true>));         \
+        else if (gw == 2)                                            \
+            SBNET_PS((planes_scatter_simt<M, T_, 2, false>));        \
+        else                                                         \
+            SBNET_PS((planes_scatter_simt<M, T_, 0, false>));        \
     } while (0)
         if (mode == kScatterSet)
             SBNET_PS_SC(kScatterSet, float);

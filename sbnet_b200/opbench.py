@@ -289,6 +289,27 @@ def main(args):
              {"blocks": nb, "blocks/s": nb / (med * 1e-3)})
         del base, stack
 
+    # ---- blocks of more than 384 pixels in the plane layout: 34x34 over stride 32 on [8,512,512,128] ----
+    C = 128
+    gl = cfg.geom_for(H, W, (34, 34), (32, 32), (-1, -1))
+    idx_h, cnt_h = cfg.random_block_list(N, gl.bcount, 0.20, seed=34)
+    nb = int(cnt_h[0])
+    idx, cnt = torch.from_numpy(idx_h).to(dev), torch.from_numpy(cnt_h)
+    U = cfg.union_pixels(idx_h, nb, gl, N, H, W)
+    for dtype, tname in ((torch.float32, "f32"), (torch.float16, "f16")):
+        x = torch.randn((N, H, W, C), device=dev, dtype=torch.float32).to(dtype)
+        out = torch.empty((nb, C, 34, 34), dtype=dtype, device=dev)
+        nbytes = cfg.algorithmic_bytes("gather", nB=nb, geom=gl, C=C, itemsize=x.element_size(), U=U)
+        med, mn = tm.run(lambda: ops.sparse_gather(x, cnt, idx, gl.bsize, gl.bstride, gl.boffset,
+                                                   transpose=True, out=out))
+        emit(f"gather_{tname}_t1_b34_d20", med, mn, nbytes, {"blocks": nb, "blocks/s": nb / (med * 1e-3)})
+        nbytes = cfg.algorithmic_bytes("scatter_add", nB=nb, geom=gl, C=C, itemsize=x.element_size(), U=U)
+        med, mn = tm.run(lambda: ops.sparse_scatter_var(out, cnt, idx, x, gl.bsize, gl.bstride, gl.boffset,
+                                                        add=True, atomic=True, transpose=True))
+        emit(f"scatter_var_{tname}_t1_atomic_b34_d20", med, mn, nbytes,
+             {"blocks": nb, "blocks/s": nb / (med * 1e-3)})
+        del x, out
+
     # ---- plain copy (the non-Var op's base copy), with torch's own copy beside it as a yardstick ----
     a = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
     b = torch.empty_like(a)

@@ -1,6 +1,7 @@
 """Plane-layout ([nB,C,R,S]) gather / scatter on the shapes the TMA pipeline takes (C*sizeof(T) a
-multiple of 128 bytes, blocks of at most 384 pixels) and on shapes just outside it, against the CPU
-checker; the general kernels are run on the same inputs by switching the pipeline off."""
+multiple of 128 bytes, blocks of at most 384 pixels), the wider set the tile CTAs take (partial
+channel chunks, blocks of any size cut into pixel chunks) and shapes outside both, against the CPU
+checker; the general kernels are run on the same inputs by switching the others off."""
 import os
 
 import numpy as np
@@ -18,7 +19,7 @@ SHAPES = [
     (np.float16, 3, 33, 29, 64, (6, 5), (4, 3), (-2, -3)),      # 30 pixels, all four borders
     (np.float16, 1, 50, 50, 64, (19, 20), (7, 9), (-5, -4)),    # 380 pixels
     (np.float16, 1, 50, 50, 64, (5, 5), (5, 5), (0, 0)),        # odd pixel count: general kernel
-    (np.float16, 1, 64, 64, 64, (20, 20), (16, 16), (-2, -2)),  # 400 pixels: general kernel
+    (np.float16, 1, 64, 64, 64, (20, 20), (16, 16), (-2, -2)),  # 400 pixels: two pixel chunks
     (np.float32, 2, 64, 48, 32, (18, 18), (16, 16), (-1, -1)),
     (np.float32, 2, 64, 48, 128, (18, 18), (16, 16), (-1, -1)),
     (np.float32, 1, 37, 41, 64, (7, 3), (5, 3), (-3, -1)),      # 21 pixels (odd is fine for fp32)
@@ -36,6 +37,15 @@ SHAPES = [
     (np.float16, 1, 30, 30, 24, (6, 6), (5, 5), (-1, -1)),
     (np.float16, 2, 64, 48, 200, (16, 16), (16, 16), (0, 0)),
     (np.float16, 1, 40, 40, 40, (18, 18), (16, 16), (-1, -1)),
+    # blocks of more than 384 pixels: pixel chunks in the tile CTAs
+    (np.float16, 1, 100, 90, 64, (34, 34), (32, 32), (-1, -1)),   # rows of 578 words: 8-byte copy-in, word stores
+    (np.float32, 1, 100, 90, 32, (34, 34), (32, 32), (-1, -1)),   # rows of 1156 words: 16-byte aligned
+    (np.float32, 1, 70, 70, 32, (21, 21), (21, 21), (-3, -3)),    # 441 pixels (odd): gather chunks, general scatter
+    (np.float32, 2, 80, 70, 48, (27, 22), (20, 17), (-5, -4)),    # 594 pixels, overlapping, partial channel chunk
+    (np.float16, 1, 130, 150, 128, (41, 48), (41, 48), (0, 0)),   # 1968 pixels: six chunks of 328
+    (np.float16, 2, 140, 130, 40, (64, 64), (61, 59), (-9, -7)),  # 4096 pixels, partial channel chunk
+    (np.float16, 1, 170, 170, 64, (81, 81), (81, 81), (-4, -4)),  # odd pixel count: general kernel
+    (np.float32, 1, 170, 170, 16, (81, 81), (70, 70), (-4, -4)),  # 6561 pixels (odd), fp32 gather chunks
 ]
 
 
