@@ -583,6 +583,133 @@ def cpu_suite(args):
     line("scatter_f16_t1_set", dt, nb, "blocks", 2 * nb * 256 * C * 2, f"first {nb} blocks, overwrite, transposed stack")
 
 
+def refgpu_suite(args):
+    """``bench.py --suite refgpu``: the reference's own CUDA kernels recompiled for sm_100a
+    (``make -C oracle refgpu``) timed beside this library's kernels on the same device, inputs and
+    timing protocol (CUDA events, L2 flushed between launches, median).  fp32, as the reference is
+    fp32-only; the last cases add this library's fp16 path on the same shapes.  Informational: the
+    parity authority stays the CPU functors."""
+    import torch
+    from oracle import refgpu   # test / benchmark infrastructure, never used by the product
+    from sbnet_b200 import build, ops
+    from sbnet_b200.opbench import Timer, _peak
+    if not refgpu.available():
+        try:
+            refgpu.build()
+        except Exception:
+            pass
+    if not refgpu.available():
+        print(json.dumps({"suite": "refgpu", "unavailable": "reference CUDA kernels not built (no reference tree, no prebuilt library)"}))
+        return
+    build.build_library()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    tm = Timer(torch, dev, max(args.steps if args.steps != 100 else 20, 5), max(args.warmup, 3))
+    peak, kind = _peak()
+
+    def line(case, nbytes, ref_ms, ours_ms, extra=None):
+        extra = extra or {}
+        rbytes = extra.get("ref_algorithmic_bytes", nbytes)   # differs when this library runs fp16
+        d = {"case": case, "algorithmic_bytes": int(nbytes), "ref_us": ref_ms * 1e3, "ours_us": ours_ms * 1e3,
+             "speedup": ref_ms / ours_ms, "ref_GB/s": rbytes / ref_ms / 1e6, "ours_GB/s": nbytes / ours_ms / 1e6,
+             "ref_frac_of_" + kind: rbytes / ref_ms / 1e6 / peak, "ours_frac_of_" + kind: nbytes / ours_ms / 1e6 / peak}
+        d.update(extra)
+        print(json.dumps(d), flush=True)
+
+    # ---- reduce_mask at bird's-eye-view scale (two reference launches: zero the counter, reduce) ----
+    c2 = cfg.config2(0)
+    g = c2["geom"]
+    mask = torch.from_numpy(c2["mask"]).to(dev)
+    ridx = torch.zeros((8 * g.bcount[0] * g.bcount[1], 3), dtype=torch.int16, device=dev)
+    rcnt = torch.zeros(1, dtype=torch.int32, device=dev)
+    for run in c2["runs"]:
+        idx, cnt = ops.reduce_mask(mask, *g.as_lists(), tol=run["tol"], avgpool=run["avgpool"])
+        nb = int(cnt[0])
+        nbytes = cfg.algorithmic_bytes("reduce_mask", nB=nb, geom=g, C=1, itemsize=4, U=0, N=8, H=800, W=704, count=nb)
+        r, _ = tm.run(lambda: refgpu.reduce_mask_launch(mask, g.bcount, g.bsize, g.bstride, g.boffset, run["tol"],
+                                                        run["avgpool"], ridx, rcnt))
+        o, _ = tm.run(lambda: ops.reduce_mask_async(mask, *g.as_lists(), tol=run["tol"], avgpool=run["avgpool"]))
+        line("reduce_mask_" + ("avg" if run["avgpool"] else "max"), nbytes, r, o, {"active": nb, "ref_active": int(rcnt.item())})
+    del mask
+
+    # ---- sparse_gather on [8,512,512,128] fp32 ----
+    N, H, W, C = 8, 512, 512, 128
+    g = cfg.halo_geom(H, W)
+    x = torch.randn((N, H, W, C), device=dev)
+    for dens in (0.05, 0.20, 0.50):
+        idx_h, cnt_h = cfg.random_block_list(N, g.bcount, dens, seed=int(dens * 100))
+        nb = int(cnt_h[0])
+        U = cfg.union_pixels(idx_h, nb, g, N, H, W)
+        idx, cnt = torch.from_numpy(idx_h).to(dev), torch.from_numpy(cnt_h)
+        nbytes = cfg.algorithmic_bytes("gather", nB=nb, geom=g, C=C, itemsize=4, U=U)
+        for tr in (False, True):
+            out = torch.empty((nb, C, 18, 18) if tr else (nb, 18, 18, C), device=dev)
+            r, _ = tm.run(lambda: refgpu.sparse_gather(x, nb, idx, g.bsize, g.bstride, g.boffset, tr, out))
+            o, _ = tm.run(lambda: ops.sparse_gather(x, cnt, idx, g.bsize, g.bstride, g.boffset, transpose=tr, out=out))
+            line(f"gather_f32_t{int(tr)}_d{int(dens * 100)}", nbytes, r, o, {"blocks": nb})
+            del out
+    del x
+
+    # ---- sparse_scatter_var on [8,512,512,64] fp32: atomic add with halos; transposed overwrite ----
+    C = 64
+    gi = cfg.inner_geom(H, W)
+    base = torch.randn((N, H, W, C), device=dev)
+    for dens in (0.05, 0.20, 0.50):
+        idx_h, cnt_h = cfg.random_block_list(N, g.bcount, dens, seed=int(dens * 100) + 1)
+        nb = int(cnt_h[0])
+        idx, cnt = torch.from_numpy(idx_h).to(dev), torch.from_numpy(cnt_h)
+        stack = torch.randn((nb, 18, 18, C), device=dev)
+        nbytes = cfg.algorithmic_bytes("scatter_add", nB=nb, geom=g, C=C, itemsize=4,
+                                       U=cfg.union_pixels(idx_h, nb, g, N, H, W))
+        r, _ = tm.run(lambda: refgpu.sparse_scatter_var(stack, nb, idx, base, g.bsize, g.bstride, g.boffset,
+                                                        add=True, atomic=True))
+        o, _ = tm.run(lambda: ops.sparse_scatter_var(stack, cnt, idx, base, g.bsize, g.bstride, g.boffset,
+                                                     add=True, atomic=True))
+        line(f"scatter_var_f32_atomic_d{int(dens * 100)}", nbytes, r, o, {"blocks": nb})
+        stack = torch.randn((nb, C, 16, 16), device=dev)
+        nbytes = cfg.algorithmic_bytes("scatter", nB=nb, geom=gi, C=C, itemsize=4,
+                                       U=cfg.union_pixels(idx_h, nb, gi, N, H, W))
+        r, _ = tm.run(lambda: refgpu.sparse_scatter_var(stack, nb, idx, base, gi.bsize, gi.bstride, gi.boffset,
+                                                        add=False, transpose=True))
+        o, _ = tm.run(lambda: ops.sparse_scatter_var(stack, cnt, idx, base, gi.bsize, gi.bstride, gi.boffset,
+                                                     add=False, transpose=True))
+        line(f"scatter_var_f32_t1_set_d{int(dens * 100)}", nbytes, r, o, {"blocks": nb})
+        del stack
+    del base
+
+    # ---- the sparse bottleneck's block ops, 8 of the 32 images: [8,400,352,256] ----
+    # reference fp32 (its only type) against this library's fp32 and fp16 paths on the same block list
+    N, H, W, C = 8, 400, 352, 256
+    g, gi = cfg.halo_geom(H, W), cfg.inner_geom(H, W)
+    mask = torch.from_numpy(cfg.rect_union_mask(N, H, W, 7, n_rects=None, occupancy=0.10)).to(dev)
+    idx, cnt = ops.reduce_mask(mask, *g.as_lists(), tol=0.5, avgpool=False)
+    nb = int(cnt[0])
+    idx_h = idx.cpu().numpy()
+    x32 = torch.randn((N, H, W, C), device=dev)
+    x16 = x32.half()
+    for t, tname, sz in ((x32, "f32", 4), (x16, "f16", 2)):
+        out = torch.empty((nb, C, 18, 18), dtype=t.dtype, device=dev)
+        nbytes = cfg.algorithmic_bytes("gather", nB=nb, geom=g, C=C, itemsize=sz, U=cfg.union_pixels(idx_h, nb, g, N, H, W))
+        if sz == 4:
+            r_g, _ = tm.run(lambda: refgpu.sparse_gather(t, nb, idx, g.bsize, g.bstride, g.boffset, True, out))
+            nbytes32 = nbytes
+        o, _ = tm.run(lambda: ops.sparse_gather(t, cnt, idx, g.bsize, g.bstride, g.boffset, transpose=True, out=out))
+        line(f"bottleneck_gather_t1_ours_{tname}_vs_ref_f32", nbytes, r_g, o,
+             {"blocks": nb, "ref_algorithmic_bytes": int(nbytes32)})
+        stack = torch.randn((nb, C, 16, 16), device=dev).to(t.dtype)
+        nbytes = cfg.algorithmic_bytes("scatter_add", nB=nb, geom=gi, C=C, itemsize=sz,
+                                       U=cfg.union_pixels(idx_h, nb, gi, N, H, W))
+        if sz == 4:
+            r_s, _ = tm.run(lambda: refgpu.sparse_scatter_var(stack, nb, idx, t, gi.bsize, gi.bstride, gi.boffset,
+                                                              add=True, transpose=True))
+            nbytes32s = nbytes
+        o, _ = tm.run(lambda: ops.sparse_scatter_var(stack, cnt, idx, t, gi.bsize, gi.bstride, gi.boffset, add=True,
+                                                     transpose=True))
+        line(f"bottleneck_scatter_add_t1_ours_{tname}_vs_ref_f32", nbytes, r_s, o,
+             {"blocks": nb, "ref_algorithmic_bytes": int(nbytes32s)})
+        del out, stack
+
+
 def run_reference(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -640,13 +767,15 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-sync-free", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=12.0)
-    ap.add_argument("--suite", choices=["ops", "one", "resblock", "cpu"], default=None)
+    ap.add_argument("--suite", choices=["ops", "one", "resblock", "cpu", "refgpu"], default=None)
     ap.add_argument("--case", default="gather_f16_t1")
     ap.add_argument("--density", type=float, default=0.2)
     ap.add_argument("--one-channels", type=int, default=None)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.suite == "cpu":
+    if args.suite == "refgpu":
+        refgpu_suite(args)
+    elif args.suite == "cpu":
         cpu_suite(args)
     elif args.suite in ("ops", "one", "resblock"):
         from sbnet_b200 import opbench
