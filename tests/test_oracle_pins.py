@@ -170,3 +170,19 @@ def test_threaded_port_is_deterministic_where_disjoint(oracle_port):
     finally:
         oracle_port.set_threads(1)
     assert a == b
+
+
+def test_reference_cuda_kernel_library_exports_its_entry_points():
+    """The second checker (the reference's CUDA kernels for sm_100a) loads without a GPU and exports
+    the three launchers; no launch is made here."""
+    from oracle import refgpu
+    if not refgpu.available():
+        try:
+            refgpu.build()
+        except Exception:
+            pass
+    if not refgpu.available():
+        pytest.skip("reference CUDA kernels not built (no reference tree and no prebuilt library)")
+    lib = refgpu._load()
+    for name in ("refgpu_sparse_gather", "refgpu_sparse_scatter", "refgpu_reduce_mask"):
+        assert getattr(lib, name) is not None
