@@ -264,7 +264,35 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
             else
                 return vi;
         };
-        if constexpr (GW == 2) {
+        if constexpr (GW == 2 && !PCH) {
+            // The chunk is one contiguous 16-byte aligned run: 16-byte loads even though plane rows
+            // are only 8-byte multiples; a vector that straddles two rows is split when it is stored.
+            const uint4* src = reinterpret_cast<const uint4*>(srcT);
+            const int nVec = nG * P;
+            uint4 v[kPsMaxVecs];
+#pragma unroll
+            for (int k = 0; k < kPsMaxVecs; ++k)
+                if ((int)threadIdx.x + k * kPsThreads < nVec)
+                    v[k] = ld_stream(src + threadIdx.x + k * kPsThreads);
+#pragma unroll
+            for (int k = 0; k < kPsMaxVecs; ++k) {
+                const int vi = (int)threadIdx.x + k * kPsThreads;
+                if (vi < nVec) {
+                    uint32_t c, col;
+                    unitsPerRow.divmod(2u * (uint32_t)vi, c, col);
+                    uint32_t w = c * pitchW + ((col * 2u) ^ (4u * ((c / CPG) & 7u)));
+                    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(tile + w * 4u), "r"(v[k].x), "r"(v[k].y)
+                                 : "memory");
+                    if (++col == unitsPerRow.div) {
+                        col = 0;
+                        ++c;
+                    }
+                    w = c * pitchW + ((col * 2u) ^ (4u * ((c / CPG) & 7u)));
+                    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(tile + w * 4u), "r"(v[k].z), "r"(v[k].w)
+                                 : "memory");
+                }
+            }
+        } else if constexpr (GW == 2) {
             const uint2* src = reinterpret_cast<const uint2*>(srcT);
             const int nUnit = 2 * nG * P;
 #pragma unroll

@@ -121,3 +121,41 @@ def test_no_bounded_wait_gave_up(cuda_ops):
     n = C.c_uint(99)
     lib.check(lib.load().sbnet_wait_timeouts(C.byref(n)))
     assert n.value == 0
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+def test_device_count_calls_on_blocks_above_384_pixels(cuda_ops, dtype):
+    """The ``*_dyn`` entry points (block count read on the device) against the host-count calls on
+    34x34 blocks: the scatter runs the pixel-chunked tile kernel as one resident wave, the gather the
+    general kernel."""
+    import torch
+    from sbnet_b200 import ops
+    N, H, W, C = 2, 100, 90, 64
+    bsize, bstride, boffset = (34, 34), (32, 32), (-1, -1)
+    g = cfg.geom_for(H, W, bsize, bstride, boffset)
+    idx_h, cnt_h = cfg.random_block_list(N, g.bcount, 0.7, seed=5)
+    nb, max_blocks = int(cnt_h[0]), idx_h.shape[0]
+    dev = torch.device("cuda:0")
+    idx, cnt = torch.from_numpy(idx_h).to(dev), torch.from_numpy(cnt_h)
+    cnt_dev = cnt.to(dev)
+    x = torch.from_numpy(cfg.normal((N, H, W, C), 21, dtype)).to(dev)
+    ref = ops.sparse_gather(x, cnt, idx, bsize, bstride, boffset, transpose=True)
+    out = torch.full((max_blocks, C, 34, 34), -3.0, dtype=x.dtype, device=dev)
+    ops.sparse_gather_dyn(x, cnt_dev, max_blocks, idx, bsize, bstride, boffset, transpose=True, out=out)
+    torch.cuda.synchronize()
+    assert torch.equal(out[:nb], ref) and bool((out[nb:] == -3.0).all())
+    base = torch.from_numpy(cfg.normal((N, H, W, C), 22, dtype)).to(dev)
+    for add, atomic in ((False, False), (True, True)):
+        src = ref if not add else torch.from_numpy(cfg.normal(tuple(ref.shape), 23, dtype)).to(dev)
+        full = torch.cat([src, torch.full((max_blocks - nb, C, 34, 34), float("nan"), dtype=x.dtype, device=dev)])
+        y1 = ops.sparse_scatter_var_dyn(full, cnt_dev, max_blocks, idx, base.clone(), bsize, bstride, boffset,
+                                        add=add, atomic=atomic, transpose=True)
+        y2 = ops.sparse_scatter_var(src, cnt, idx, base.clone(), bsize, bstride, boffset, add=add, atomic=atomic,
+                                    transpose=True)
+        torch.cuda.synchronize()
+        if add:   # overlapping halos: arrival order differs between the two runs
+            tol = (1e-6 if dtype == np.float32 else 1e-3) * 5
+            err = ((y1.double() - y2.double()).abs() / y2.double().abs().clamp(min=1.0)).max().item()
+            assert err <= tol, err
+        else:
+            assert torch.equal(y1, y2)
