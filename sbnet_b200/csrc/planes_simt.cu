@@ -22,6 +22,8 @@
 //           same kernel runs as one resident wave striding over the items.
 #include <stdlib.h>
 
+#include <algorithm>
+
 #include "async_ptx.cuh"
 #include "common.cuh"
 #include "kernels.h"
@@ -45,21 +47,35 @@ struct SimtPlan {
     int groups;        // 16-byte channel groups per pixel (C*sizeof(T)/16); the last chunk may hold fewer than 8
     int pixels;        // P
     int units;         // words per channel plane: P (fp32) or P/2 (fp16)
+    // several small blocks per work item (kTileMulti)
+    int blocksPerItem; // blocks sharing one tile
+    FastDiv pixelsDiv; // P
+    FastDiv unitsDiv;  // units
+    FastDiv runUnits, runUnitsLast; // copy-in units of one block's chunk (full / last channel chunk)
 };
 
-// PCH: blocks of more than 384 pixels are cut into pixel chunks; a work item is then (block, pixel
-// chunk, channel chunk) and its transposed tile leaves as one run per channel plane.
-template <typename T, bool PCH>
+// How a work item maps onto the 384-pixel tile.
+constexpr int kTileSingle = 0;   // one block (at most 384 pixels) x one channel chunk
+constexpr int kTileChunked = 1;  // blocks of more than 384 pixels, cut into pixel chunks
+constexpr int kTileMulti = 2;    // blocks of at most 192 pixels: as many whole blocks as fit share the tile
+
+// kTileChunked: a work item is (block, pixel chunk, channel chunk) and its transposed tile leaves as
+// one run per channel plane.
+// kTileMulti: the tile holds the pixels of several consecutive blocks of the list back to back; each
+// block's region is transposed in place on its own and leaves as its own bulk store.
+template <typename T, int SHAPE>
 __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gather_simt(const BlockArgs a, const SimtPlan p)
 {
+    constexpr bool PCH = SHAPE == kTileChunked, MB = SHAPE == kTileMulti;
     __shared__ __align__(1024) unsigned char tileRaw[kPsTileBytes];
     constexpr int EPW = 4 / (int)sizeof(T);
     constexpr int CPG = 16 / (int)sizeof(T);
     constexpr int kMaxTasks = ((kPsMaxPixels / EPW + 15) / 16 + 1) / 2;
     const uint32_t tile = smem_u32(tileRaw);
 
-    uint32_t ib, cc;
+    uint32_t ib, cc;                          // (first) block of the item, channel chunk
     int p0 = 0, P = p.pixels, U = p.units;   // first pixel, pixels and words per plane row of this item
+    int nBlk = 1;                            // blocks sharing the tile
     if constexpr (PCH) {
         uint32_t rest, pc;
         p.cChunks.divmod(blockIdx.x, rest, cc);
@@ -67,14 +83,27 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
         p0 = (int)pc * p.chunkPixels;
         P = min(p.chunkPixels, p.pixels - p0);
         U = P / EPW;
+    } else if constexpr (MB) {
+        uint32_t grp;
+        p.cChunks.divmod(blockIdx.x, grp, cc);
+        ib = grp * (uint32_t)p.blocksPerItem;
+        nBlk = min(p.blocksPerItem, a.numActive - (int)ib);
+        P = nBlk * p.pixels;   // the tile's pixel slots: block b owns slots [b*pixels, (b+1)*pixels)
+        U = nBlk * p.units;
     } else {
         p.cChunks.divmod(blockIdx.x, ib, cc);
     }
-    const int n = a.idx[ib * 3 + 0];
-    const int h0 = a.bOffsH + a.idx[ib * 3 + 1] * a.bStrH;
-    const int w0 = a.bOffsW + a.idx[ib * 3 + 2] * a.bStrW;
-    const T* imgN = reinterpret_cast<const T*>(a.image) + (long long)n * a.H * a.W * a.C +
-                    (long long)cc * (128 / (int)sizeof(T));
+    // image plane of a block's batch index, at this item's channel chunk, and the block's window origin
+    auto locate = [&](uint32_t blk, int& h0, int& w0) -> const T* {
+        const int n = a.idx[blk * 3 + 0];
+        h0 = a.bOffsH + a.idx[blk * 3 + 1] * a.bStrH;
+        w0 = a.bOffsW + a.idx[blk * 3 + 2] * a.bStrW;
+        return reinterpret_cast<const T*>(a.image) + (long long)n * a.H * a.W * a.C + (long long)cc * (128 / (int)sizeof(T));
+    };
+    int h0 = 0, w0 = 0;
+    const T* imgN = nullptr;
+    if constexpr (!MB)
+        imgN = locate(ib, h0, w0);
     const int nG = min(8, p.groups - 8 * (int)cc);   // 16-byte groups in this chunk
 
     // ---- image -> tile: thread owns 16-byte group j of pixels px0, px0+32, ...
@@ -86,8 +115,13 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
             const int px = px0 + 32 * k;
             v[k] = make_uint4(0, 0, 0, 0);
             if (px < P && j < nG) {
-                uint32_t r, s;
-                p.blockW.divmod((uint32_t)(px + p0), r, s);
+                uint32_t r, s, inBlock = (uint32_t)(px + p0);
+                if constexpr (MB) {
+                    uint32_t b;
+                    p.pixelsDiv.divmod((uint32_t)px, b, inBlock);
+                    imgN = locate(ib + b, h0, w0);
+                }
+                p.blockW.divmod(inBlock, r, s);
                 const int h = h0 + (int)r, w = w0 + (int)s;
                 if (h >= 0 && h < a.H && w >= 0 && w < a.W)
                     v[k] = ld_stream(reinterpret_cast<const uint4*>(imgN + ((long long)h * a.W + w) * a.C + j * CPG));
@@ -126,8 +160,14 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
         const int uLocal = t & 15, grp = t >> 4;
         const int j = grp & 7, u = ((grp >> 3) << 4) + uLocal;
         if (t < nTasks && u < U && j < nG) {
-            const uint32_t base = tile + ((uint32_t)(CPG * j) * U + u) * 4u;
-            const uint32_t pitch = (uint32_t)U * 4u;
+            uint32_t base = tile + ((uint32_t)(CPG * j) * U + u) * 4u;
+            uint32_t pitch = (uint32_t)U * 4u;
+            if constexpr (MB) {   // word u of the tile = word uIn of block b's region
+                uint32_t b, uIn;
+                p.unitsDiv.divmod((uint32_t)u, b, uIn);
+                base = tile + b * (uint32_t)p.pixels * 128u + ((uint32_t)(CPG * j) * p.units + uIn) * 4u;
+                pitch = (uint32_t)p.units * 4u;
+            }
             if constexpr (EPW == 2) {
                 sts32(base + 0u * pitch, __byte_perm(A[q].x, B[q].x, 0x5410));
                 sts32(base + 1u * pitch, __byte_perm(A[q].x, B[q].x, 0x7632));
@@ -174,6 +214,12 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
                 for (int u = threadIdx.x & 31; u < U; u += 32)
                     dstW[c * rowW + u] = lds32(tile + (uint32_t)(c * U + u) * 4u);
         }
+    } else if constexpr (MB) {
+        if ((int)threadIdx.x < nBlk) {   // block b's planes of this chunk: one contiguous run of the stack
+            bulk_store_1d(dst + (long long)threadIdx.x * a.C * p.pixels, tile + threadIdx.x * (uint32_t)p.pixels * 128u,
+                          (uint32_t)(16 * nG * p.pixels));
+            bulk_wait_read<0>();
+        }
     } else if (threadIdx.x == 0) {
         bulk_store_1d(dst, tile, (uint32_t)(16 * nG * P));
         bulk_wait_read<0>();   // shared memory must outlive the engine's read of it
@@ -187,12 +233,14 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
 // of sixteen scattered sectors (measured: 5.3 -> 6.4 TB/s on the fp16 add scatter).  GW is the
 // copy-in unit in words (a unit must not straddle plane rows).  GW == 0 (odd row length): dense
 // tile, sixteen-pixel lane mapping.
-// PCH (GW > 0 only): blocks of more than 384 pixels, cut into pixel chunks as in the gather.
-template <int MODE, typename T, int GW, bool PCH>
+// kTileChunked / kTileMulti (GW > 0 only): as in the gather.  kTileMulti keeps block b's words in
+// columns [b*units, (b+1)*units) of every tile row.
+template <int MODE, typename T, int GW, int SHAPE>
 __global__ void __launch_bounds__(kPsThreads, MODE == kScatterAdd ? 2 : 3)
 planes_scatter_simt(const BlockArgs a, const SimtPlan p)
 {
-    static_assert(!PCH || GW > 0, "pixel chunks need the swizzled tile");
+    constexpr bool PCH = SHAPE == kTileChunked, MB = SHAPE == kTileMulti;
+    static_assert(SHAPE == kTileSingle || GW > 0, "pixel chunks and shared tiles need the swizzled tile");
     __shared__ __align__(128) unsigned char tileRaw[kPsTileBytes];
     constexpr int EPW = 4 / (int)sizeof(T);
     constexpr int CPG = 16 / (int)sizeof(T);
@@ -206,10 +254,13 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
     int nActive = a.numActive;
     if (a.num_active_dev != nullptr)
         nActive = min(__ldg(a.num_active_dev), a.numActive);
-    const long long nItems = (long long)nActive * p.cChunks.div * (PCH ? p.pChunks.div : 1u);
+    long long nItems = (long long)nActive * p.cChunks.div * (PCH ? p.pChunks.div : 1u);
+    if constexpr (MB)
+        nItems = (long long)((nActive + p.blocksPerItem - 1) / p.blocksPerItem) * p.cChunks.div;
     for (long long item = blockIdx.x; item < nItems; item += gridDim.x) {
-    uint32_t ib, cc;
+    uint32_t ib, cc;                          // (first) block of the item, channel chunk
     int p0 = 0, P = p.pixels, U = p.units;   // first pixel, pixels and words per plane row of this item
+    int nBlk = 1;                            // blocks sharing the tile
     FastDiv unitsPerRow = p.unitsPerRow;
     if constexpr (PCH) {
         uint32_t rest, pc;
@@ -220,24 +271,55 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
         U = P / EPW;
         if (pc + 1 == p.pChunks.div)
             unitsPerRow = p.unitsPerRowLast;
+    } else if constexpr (MB) {
+        uint32_t grp;
+        p.cChunks.divmod((uint32_t)item, grp, cc);
+        ib = grp * (uint32_t)p.blocksPerItem;
+        nBlk = min(p.blocksPerItem, nActive - (int)ib);
+        P = nBlk * p.pixels;   // the tile's pixel slots: block b owns slots [b*pixels, (b+1)*pixels)
+        U = nBlk * p.units;
     } else {
         p.cChunks.divmod((uint32_t)item, ib, cc);
     }
-    const int n = a.idx[ib * 3 + 0];
-    const int h0 = a.bOffsH + a.idx[ib * 3 + 1] * a.bStrH;
-    const int w0 = a.bOffsW + a.idx[ib * 3 + 2] * a.bStrW;
-    T* imgN = reinterpret_cast<T*>(a.image) + (long long)n * a.H * a.W * a.C + (long long)cc * (128 / (int)sizeof(T));
     const int nG = min(8, p.groups - 8 * (int)cc);   // 16-byte groups in this chunk
     const int nTasks = SWZ ? 8 * U : ((U + 15) >> 4) * 128;
     const uint32_t pitchW = SWZ ? (uint32_t)p.pitchWords : (uint32_t)U;   // tile row pitch in words
 
-    auto dest = [&](int pix, int j) -> uint4* {
+    // A block's window: image plane of its batch index at this item's channel chunk + window origin.
+    struct Window {
+        T* img;
+        int h0, w0;
+    };
+    auto window = [&](uint32_t blk) -> Window {
+        Window wn;
+        const int n = a.idx[blk * 3 + 0];
+        wn.h0 = a.bOffsH + a.idx[blk * 3 + 1] * a.bStrH;
+        wn.w0 = a.bOffsW + a.idx[blk * 3 + 2] * a.bStrW;
+        wn.img = reinterpret_cast<T*>(a.image) + (long long)n * a.H * a.W * a.C + (long long)cc * (128 / (int)sizeof(T));
+        return wn;
+    };
+    Window own = {nullptr, 0, 0};
+    if constexpr (!MB)
+        own = window(ib);
+    // tile pixel slot -> its block's window and the pixel index inside that block
+    auto locate = [&](int slot, int& pix) -> Window {
+        if constexpr (MB) {
+            uint32_t b, q;
+            p.pixelsDiv.divmod((uint32_t)slot, b, q);
+            pix = (int)q;
+            return window(ib + b);
+        } else {
+            pix = slot + p0;
+            return own;
+        }
+    };
+    auto dest = [&](const Window& wn, int pix, int j) -> uint4* {
         uint32_t r, sx;
-        p.blockW.divmod((uint32_t)(pix + p0), r, sx);
-        const int h = h0 + (int)r, w = w0 + (int)sx;
+        p.blockW.divmod((uint32_t)pix, r, sx);
+        const int h = wn.h0 + (int)r, w = wn.w0 + (int)sx;
         if (h < 0 || h >= a.H || w < 0 || w >= a.W)
             return nullptr;
-        return reinterpret_cast<uint4*>(imgN + ((long long)h * a.W + w) * a.C + j * CPG);
+        return reinterpret_cast<uint4*>(wn.img + ((long long)h * a.W + w) * a.C + j * CPG);
     };
     // task t of this thread -> (16-byte channel group j, word column u)
     auto task = [&](int t, int& j, int& u) {
@@ -252,19 +334,31 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
     };
 
     // ---- stack -> tile: the chunk's planes are one contiguous run of 32*P words (pixel chunks: one
-    // run of U words per plane, p.pixels elements apart)
+    // run of U words per plane, p.pixels elements apart; shared tile: one run per block)
     {
         const T* srcT = reinterpret_cast<const T*>(a.stack) +
                         ((long long)ib * a.C + (long long)cc * (128 / (int)sizeof(T))) * p.pixels + p0;
-        // unit vi = (plane c, column col) -> offset from srcT in copy-in units
-        const uint32_t rowUnits = PCH ? (uint32_t)(p.pixels / EPW / (GW > 0 ? GW : 1)) : 0u;
-        auto srcOff = [&](uint32_t vi, uint32_t c, uint32_t col) -> uint32_t {
-            if constexpr (PCH)
-                return c * rowUnits + col;
-            else
-                return vi;
+        constexpr uint32_t G = GW > 0 ? GW : 1;
+        const uint32_t rowUnits = (uint32_t)(p.pixels / EPW) / G;               // one whole plane row
+        const uint32_t blockUnits = (uint32_t)((long long)a.C * p.pixels / EPW) / G;   // one whole block
+        const FastDiv runDiv = (int)cc + 1 == (int)p.cChunks.div ? p.runUnitsLast : p.runUnits;
+        // copy-in unit vi -> its offset from srcT (in units) and its word in the tile
+        auto place = [&](uint32_t vi, uint32_t& srcUnit, uint32_t& tileW) {
+            uint32_t c, col, colW;
+            if constexpr (MB) {
+                uint32_t b, rest;
+                runDiv.divmod(vi, b, rest);
+                p.unitsPerRow.divmod(rest, c, col);
+                srcUnit = b * blockUnits + rest;
+                colW = b * (uint32_t)p.units + col * G;
+            } else {
+                unitsPerRow.divmod(vi, c, col);
+                srcUnit = PCH ? c * rowUnits + col : vi;
+                colW = col * G;
+            }
+            tileW = c * pitchW + (colW ^ (4u * ((c / CPG) & 7u)));
         };
-        if constexpr (GW == 2 && !PCH) {
+        if constexpr (GW == 2 && SHAPE == kTileSingle) {
             // The chunk is one contiguous 16-byte aligned run: 16-byte loads even though plane rows
             // are only 8-byte multiples; a vector that straddles two rows is split when it is stored.
             const uint4* src = reinterpret_cast<const uint4*>(srcT);
@@ -302,19 +396,17 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
                 for (int k = 0; k < kPsMaxVecs; ++k) {
                     const int vi = (int)threadIdx.x + (half * kPsMaxVecs + k) * kPsThreads;
                     if (vi < nUnit) {
-                        uint32_t c = 0, col = 0;
-                        if constexpr (PCH)
-                            unitsPerRow.divmod((uint32_t)vi, c, col);
-                        v[k] = ld_stream(src + srcOff((uint32_t)vi, c, col));
+                        uint32_t srcUnit, w;
+                        place((uint32_t)vi, srcUnit, w);
+                        v[k] = ld_stream(src + srcUnit);
                     }
                 }
 #pragma unroll
                 for (int k = 0; k < kPsMaxVecs; ++k) {
                     const int vi = (int)threadIdx.x + (half * kPsMaxVecs + k) * kPsThreads;
                     if (vi < nUnit) {
-                        uint32_t c, col;
-                        unitsPerRow.divmod((uint32_t)vi, c, col);
-                        const uint32_t w = c * pitchW + ((col * 2u) ^ (4u * ((c / CPG) & 7u)));
+                        uint32_t srcUnit, w;
+                        place((uint32_t)vi, srcUnit, w);
                         asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(tile + w * 4u), "r"(v[k].x), "r"(v[k].y)
                                      : "memory");
                     }
@@ -323,8 +415,8 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
         } else {
             const uint4* src = reinterpret_cast<const uint4*>(srcT);
             const int nVec = nG * P;
-            // pixel chunks: the per-unit row arithmetic costs registers, so two batches as above
-            constexpr int kBatches = PCH ? 2 : 1, kPer = kPsMaxVecs / kBatches;
+            // pixel chunks / shared tiles: the per-unit arithmetic costs registers, so two batches as above
+            constexpr int kBatches = SHAPE == kTileSingle ? 1 : 2, kPer = kPsMaxVecs / kBatches;
 #pragma unroll
             for (int b = 0; b < kBatches; ++b) {
                 uint4 v[kPer];
@@ -332,22 +424,19 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
                 for (int k = 0; k < kPer; ++k) {
                     const int vi = (int)threadIdx.x + (b * kPer + k) * kPsThreads;
                     if (vi < nVec) {
-                        uint32_t c = 0, col = 0;
-                        if constexpr (PCH)
-                            unitsPerRow.divmod((uint32_t)vi, c, col);
-                        v[k] = ld_stream(src + srcOff((uint32_t)vi, c, col));
+                        uint32_t srcUnit = (uint32_t)vi, w;
+                        if constexpr (SHAPE != kTileSingle)
+                            place((uint32_t)vi, srcUnit, w);
+                        v[k] = ld_stream(src + srcUnit);
                     }
                 }
 #pragma unroll
                 for (int k = 0; k < kPer; ++k) {
                     const int vi = (int)threadIdx.x + (b * kPer + k) * kPsThreads;
                     if (vi < nVec) {
-                        uint32_t w = (uint32_t)vi * 4u;
-                        if constexpr (GW == 4) {   // row = channel; XOR the 16-byte column group with the channel group
-                            uint32_t c, col;
-                            unitsPerRow.divmod((uint32_t)vi, c, col);
-                            w = c * pitchW + ((col * 4u) ^ (4u * ((c / CPG) & 7u)));
-                        }
+                        uint32_t srcUnit, w = (uint32_t)vi * 4u;
+                        if constexpr (GW == 4)   // row = channel; XOR the 16-byte column group with the channel group
+                            place((uint32_t)vi, srcUnit, w);
                         sts128(tile + w * 4u, v[k]);
                     }
                 }
@@ -363,10 +452,14 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
             int j, u;
             task(t, j, u);
 #pragma unroll
-            for (int e = 0; e < EPW; ++e) {
+            for (int e = 0; e < EPW; ++e)
                 old[q][e] = make_uint4(0, 0, 0, 0);
-                if (t < nTasks && u < U && j < nG)
-                    if (const uint4* d = dest(u * EPW + e, j))
+            if (t < nTasks && u < U && j < nG) {
+                int pix;
+                const Window wn = locate(u * EPW, pix);
+#pragma unroll
+                for (int e = 0; e < EPW; ++e)
+                    if (const uint4* d = dest(wn, pix + e, j))
                         old[q][e] = *d;
             }
         }
@@ -384,6 +477,8 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
         const uint32_t col = SWZ ? ((uint32_t)u ^ (4u * ((uint32_t)j & 7u))) : (uint32_t)u;
         const uint32_t base = tile + ((uint32_t)(CPG * j) * pitchW + col) * 4u;
         const uint32_t pitch = pitchW * 4u;
+        int pix;
+        const Window wn = locate(u * EPW, pix);   // fp16: both pixels of a word lie in one block (P is even)
         if constexpr (EPW == 2) {
             uint32_t w[8];
 #pragma unroll
@@ -393,14 +488,14 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
                                         __byte_perm(w[4], w[5], 0x5410), __byte_perm(w[6], w[7], 0x5410));
             const uint4 v1 = make_uint4(__byte_perm(w[0], w[1], 0x7632), __byte_perm(w[2], w[3], 0x7632),
                                         __byte_perm(w[4], w[5], 0x7632), __byte_perm(w[6], w[7], 0x7632));
-            if (uint4* d = dest(2 * u, j))
+            if (uint4* d = dest(wn, pix, j))
                 image_write<16, MODE, T>(d, v0, old[q][0]);
-            if (uint4* d = dest(2 * u + 1, j))
+            if (uint4* d = dest(wn, pix + 1, j))
                 image_write<16, MODE, T>(d, v1, old[q][EPW - 1]);
         } else {
             const uint4 v = make_uint4(lds32(base), lds32(base + pitch), lds32(base + 2u * pitch),
                                        lds32(base + 3u * pitch));
-            if (uint4* d = dest(u, j))
+            if (uint4* d = dest(wn, pix, j))
                 image_write<16, MODE, T>(d, v, old[q][0]);
         }
     }
@@ -452,7 +547,30 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
     p.unitsPerRow = FastDiv((uint32_t)(gw ? (pch ? chunkUnits : p.units) / gw : 1));
     p.unitsPerRowLast = FastDiv((uint32_t)(gw ? (pch ? lastUnits : p.units) / gw : 1));
     p.pitchWords = ((pch ? chunkUnits : p.units) + 31) & ~31;
-    const long long nItems = (long long)a.numActive * p.cChunks.div * p.pChunks.div;
+    // Blocks of at most 192 pixels: pack as many whole blocks into the tile as fit, but never so many
+    // that fewer than four items per SM remain (small launches keep one block per item).
+    // The gather gains at every size (more bytes in flight per SM); the scatter only up to about 80
+    // pixels (measured: 8x8 0.62 -> 0.70 of copy bandwidth, but 12x12 0.88 -> 0.69: its copy-in then
+    // needs two load batches), so larger blocks keep one block per scatter item.
+    p.blocksPerItem = 1;
+    if (!pch && (mode == kGather || (gw > 0 && P <= 80))) {
+        long long perSm = (long long)a.numActive * p.cChunks.div / ((long long)sm_count() * 4);
+        if (const char* force = getenv("SBNET_TILE_BLOCKS"))   // tests: pack up to this many blocks regardless of the launch size
+            perSm = atoi(force);
+        const long long k = std::min<long long>(std::min<long long>(kPsMaxPixels / P, kPsThreads), perSm);
+        if (k >= 2)
+            p.blocksPerItem = (int)k;
+    }
+    const bool multi = p.blocksPerItem > 1;
+    p.pixelsDiv = FastDiv((uint32_t)P);
+    p.unitsDiv = FastDiv((uint32_t)std::max(p.units, 1));
+    const int cpg = 16 / itemsize, lastGroups = p.groups - 8 * ((int)p.cChunks.div - 1);
+    p.runUnits = FastDiv((uint32_t)std::max(8 * cpg * (int)p.unitsPerRow.div, 1));
+    p.runUnitsLast = FastDiv((uint32_t)std::max(lastGroups * cpg * (int)p.unitsPerRow.div, 1));
+    if (multi)
+        p.pitchWords = (p.blocksPerItem * p.units + 31) & ~31;
+    const long long nItems = multi ? (long long)((a.numActive + p.blocksPerItem - 1) / p.blocksPerItem) * p.cChunks.div
+                                   : (long long)a.numActive * p.cChunks.div * p.pChunks.div;
     if (nItems > 0x7fffffffll)
         return cudaSuccess;
     unsigned grid = (unsigned)nItems;
@@ -461,32 +579,40 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
         grid = (unsigned)(nItems < wave ? nItems : wave);
     }
 #define SBNET_PS(KERNEL) KERNEL<<<grid, kPsThreads, 0, stream>>>(a, p)
-    if (mode == kGather) {
-        if (dtype == 0) {
-            if (pch)
-                SBNET_PS((planes_gather_simt<float, true>));
-            else
-                SBNET_PS((planes_gather_simt<float, false>));
-        } else {
-            if (pch)
-                SBNET_PS((planes_gather_simt<__half, true>));
-            else
-                SBNET_PS((planes_gather_simt<__half, false>));
-        }
-    } else if (dtype == 0) {
-#define SBNET_PS_SC(M, T_)                                           \
-    do {                                                             \
-        if (gw == 4 && pch)                                          \
-            SBNET_PS((planes_scatter_simt<M, T_, 4, true>));         \
-        else if (gw == 4)                                            \
-            SBNET_PS((planes_scatter_simt<M, T_, 4, false>));        \
-        else if (gw == 2 && pch)                                     \
-            SBNET_PS((planes_scatter_simt<M, T_, 2, true>));         \
-        else if (gw == 2)                                            \
-            SBNET_PS((planes_scatter_simt<M, T_, 2, false>));        \
-        else                                                         \
-            SBNET_PS((planes_scatter_simt<M, T_, 0, false>));        \
+    const int shape = pch ? kTileChunked : (multi ? kTileMulti : kTileSingle);
+#define SBNET_PS_G(T_)                                                \
+    do {                                                              \
+        if (shape == kTileChunked)                                    \
+            SBNET_PS((planes_gather_simt<T_, kTileChunked>));         \
+        else if (shape == kTileMulti)                                 \
+            SBNET_PS((planes_gather_simt<T_, kTileMulti>));           \
+        else                                                          \
+            SBNET_PS((planes_gather_simt<T_, kTileSingle>));          \
     } while (0)
+#define SBNET_PS_SG(M, T_, GW_)                                       \
+    do {                                                              \
+        if (shape == kTileChunked)                                    \
+            SBNET_PS((planes_scatter_simt<M, T_, GW_, kTileChunked>)); \
+        else if (shape == kTileMulti)                                 \
+            SBNET_PS((planes_scatter_simt<M, T_, GW_, kTileMulti>));  \
+        else                                                          \
+            SBNET_PS((planes_scatter_simt<M, T_, GW_, kTileSingle>)); \
+    } while (0)
+#define SBNET_PS_SC(M, T_)                                            \
+    do {                                                              \
+        if (gw == 4)                                                  \
+            SBNET_PS_SG(M, T_, 4);                                    \
+        else if (gw == 2)                                             \
+            SBNET_PS_SG(M, T_, 2);                                    \
+        else                                                          \
+            SBNET_PS((planes_scatter_simt<M, T_, 0, kTileSingle>));   \
+    } while (0)
+    if (mode == kGather) {
+        if (dtype == 0)
+            SBNET_PS_G(float);
+        else
+            SBNET_PS_G(__half);
+    } else if (dtype == 0) {
         if (mode == kScatterSet)
             SBNET_PS_SC(kScatterSet, float);
         else if (mode == kScatterAdd)
@@ -498,8 +624,10 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
             SBNET_PS_SC(kScatterSet, __half);
         else
             SBNET_PS_SC(kScatterAtomic, __half);   // fp16 add arrives as a reduction
-#undef SBNET_PS_SC
     }
+#undef SBNET_PS_SC
+#undef SBNET_PS_SG
+#undef SBNET_PS_G
 #undef SBNET_PS
     *taken = true;
     return cudaGetLastError();

@@ -75,6 +75,10 @@ def tma_off(request):
 
 @pytest.mark.parametrize("shape", SHAPES, ids=_ids())
 def test_planes_gather_and_scatter(cuda_ops, oracle_port, tma_off, shape):
+    _run_shape(cuda_ops, oracle_port, shape)
+
+
+def _run_shape(cuda_ops, oracle_port, shape):
     dtype, N, H, W, C, bsize, bstride, boffset = shape
     g = cfg.geom_for(H, W, bsize, bstride, boffset)
     idx, cnt = cfg.random_block_list(N, g.bcount, 0.6, seed=C + bsize[0])
@@ -159,3 +163,60 @@ def test_device_count_calls_on_blocks_above_384_pixels(cuda_ops, dtype):
             assert err <= tol, err
         else:
             assert torch.equal(y1, y2)
+
+
+# Small blocks: several whole blocks share one tile of the tile CTAs.
+SMALL_BLOCKS = [
+    (np.float16, 2, 40, 40, 64, (6, 6), (4, 4), (-1, -1)),      # 36 pixels, overlapping
+    (np.float16, 1, 33, 29, 200, (4, 6), (4, 6), (0, 0)),       # 24 pixels, partial last channel chunk
+    (np.float32, 2, 40, 40, 32, (5, 5), (3, 3), (-1, -1)),      # 25 pixels (odd rows): gather only, scatter keeps one block per tile
+    (np.float32, 1, 50, 50, 48, (8, 8), (8, 8), (0, 0)),        # 64 pixels, partial last channel chunk
+    (np.float16, 1, 50, 50, 128, (10, 10), (8, 8), (-1, -1)),   # rows of 50 words: 8-byte copy-in
+    (np.float32, 1, 30, 30, 32, (1, 1), (1, 1), (0, 0)),        # one pixel per block
+    (np.float32, 1, 64, 64, 32, (12, 16), (12, 16), (0, 0)),    # 192 pixels: two blocks per tile
+    (np.float16, 1, 64, 64, 64, (2, 1), (2, 1), (0, 0)),        # two pixels per block
+]
+
+
+@pytest.mark.parametrize("blocks_per_tile", ["2", "7", "1000"])
+@pytest.mark.parametrize("shape", SMALL_BLOCKS,
+                         ids=[f"{np.dtype(s[0]).name}_C{s[4]}_b{s[5][0]}x{s[5][1]}" for s in SMALL_BLOCKS])
+def test_several_blocks_per_tile(cuda_ops, oracle_port, shape, blocks_per_tile):
+    saved = {k: os.environ.get(k) for k in ("SBNET_TILE_BLOCKS", "SBNET_PLANES", "SBNET_DISABLE_TMA")}
+    os.environ["SBNET_TILE_BLOCKS"] = blocks_per_tile
+    os.environ["SBNET_PLANES"] = "tile"
+    os.environ.pop("SBNET_DISABLE_TMA", None)
+    try:
+        _run_shape(cuda_ops, oracle_port, shape)
+    finally:
+        for k, v in saved.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+
+
+def test_several_blocks_per_tile_chosen_by_launch_size(cuda_ops, oracle_port):
+    """Enough 8x8 blocks that the dispatcher packs several per tile on its own; also through the
+    device-count scatter."""
+    import torch
+    from sbnet_b200 import ops
+    _run_shape(cuda_ops, oracle_port, (np.float16, 2, 256, 256, 64, (8, 8), (6, 6), (-1, -1)))
+    N, H, W, C = 2, 256, 256, 64
+    bsize, bstride, boffset = (8, 8), (8, 8), (0, 0)
+    g = cfg.geom_for(H, W, bsize, bstride, boffset)
+    idx_h, cnt_h = cfg.random_block_list(N, g.bcount, 0.8, seed=9)
+    nb, max_blocks = int(cnt_h[0]), idx_h.shape[0]
+    dev = torch.device("cuda:0")
+    idx, cnt = torch.from_numpy(idx_h).to(dev), torch.from_numpy(cnt_h)
+    stack = torch.from_numpy(cfg.normal((max_blocks, C, 8, 8), 31, np.float32)).to(dev)
+    base = torch.from_numpy(cfg.normal((N, H, W, C), 32, np.float32)).to(dev)
+    y1 = ops.sparse_scatter_var_dyn(stack, cnt.to(dev), max_blocks, idx, base.clone(), bsize, bstride, boffset,
+                                    add=True, transpose=True)
+    y2 = ops.sparse_scatter_var(stack[:nb].contiguous(), cnt, idx, base.clone(), bsize, bstride, boffset, add=True,
+                                transpose=True)
+    torch.cuda.synchronize()
+    assert torch.equal(y1, y2)
+    exp = oracle_port.sparse_scatter_var(stack[:nb].cpu().numpy(), cnt_h, idx_h, base.cpu().numpy(), bsize, bstride,
+                                         boffset, add=True, transpose=True)
+    np.testing.assert_array_equal(y2.cpu().numpy(), exp)
