@@ -51,6 +51,19 @@ __device__ __forceinline__ void sts32(uint32_t addr, uint32_t v)
     asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 
+// 16-bit accesses (plane rows of an odd number of halves start on odd half boundaries)
+__device__ __forceinline__ uint32_t lds16(uint32_t addr)
+{
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ void sts16(uint32_t addr, uint32_t v)
+{
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((unsigned short)v) : "memory");
+}
+
 __device__ __forceinline__ void sts128(uint32_t addr, uint4 v)
 {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)

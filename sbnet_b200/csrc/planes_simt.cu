@@ -1,8 +1,8 @@
 // Transposed ([nB,C,R,S]) gather and scatter, one short CTA per tile (sm_100a).
 //
-// Default implementation of the plane-layout ops for pixels of a multiple of 16 bytes (an even
-// number of pixels per block for fp16; blocks of more than 384 pixels are cut into pixel chunks);
-// other shapes run the general kernel of gather_scatter.cu.  Semantics follow the reference CPU functors (sbnet_ops/sparse_gather.cc:61-132,
+// Default implementation of the plane-layout ops for pixels of a multiple of 16 bytes (blocks of
+// more than 384 pixels are cut into pixel chunks, which for fp16 needs an even pixel count; small
+// blocks share a tile); other shapes run the general kernel of gather_scatter.cu.  Semantics follow the reference CPU functors (sbnet_ops/sparse_gather.cc:61-132,
 // transposed branches).  On B200 a grid of many short CTAs streams measurably faster than a resident
 // grid looping over the same tiles, so with a host-side block count every work item gets its own
 // CTA.  A work item is one active block x one 128-byte channel chunk (the last chunk of a pixel may
@@ -63,10 +63,14 @@ constexpr int kTileMulti = 2;    // blocks of at most 192 pixels: as many whole 
 // one run per channel plane.
 // kTileMulti: the tile holds the pixels of several consecutive blocks of the list back to back; each
 // block's region is transposed in place on its own and leaves as its own bulk store.
-template <typename T, int SHAPE>
+// ODD (fp16 blocks of an odd pixel count): plane rows are an odd number of halves, so a channel's
+// row starts on a word boundary only for even channels; words of odd channels are written as two
+// halves, and p.units counts a row's words rounded up.
+template <typename T, int SHAPE, bool ODD = false>
 __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gather_simt(const BlockArgs a, const SimtPlan p)
 {
     constexpr bool PCH = SHAPE == kTileChunked, MB = SHAPE == kTileMulti;
+    static_assert(!ODD || (sizeof(T) == 2 && !PCH), "odd rows: fp16, whole blocks only");
     __shared__ __align__(1024) unsigned char tileRaw[kPsTileBytes];
     constexpr int EPW = 4 / (int)sizeof(T);
     constexpr int CPG = 16 / (int)sizeof(T);
@@ -144,7 +148,16 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
         const int uLocal = t & 15, grp = t >> 4;
         const int j = grp & 7, u = ((grp >> 3) << 4) + uLocal;
         if (t < nTasks && u < U && j < nG) {
-            if constexpr (EPW == 2) {
+            if constexpr (ODD) {   // word u = word uIn of block b: pixels 2*uIn and (if it exists) 2*uIn+1
+                uint32_t b = 0, uIn = (uint32_t)u;
+                if constexpr (MB)
+                    p.unitsDiv.divmod((uint32_t)u, b, uIn);
+                const int r0 = (int)(b * (uint32_t)p.pixels + 2u * uIn), r1 = r0 + 1;
+                A[q] = lds128(tile + r0 * 128 + ((j ^ (r0 & 7)) << 4));
+                B[q] = make_uint4(0, 0, 0, 0);
+                if ((int)(2u * uIn) + 1 < p.pixels)
+                    B[q] = lds128(tile + r1 * 128 + ((j ^ (r1 & 7)) << 4));
+            } else if constexpr (EPW == 2) {
                 const int r0 = 2 * u, r1 = 2 * u + 1;
                 A[q] = lds128(tile + r0 * 128 + ((j ^ (r0 & 7)) << 4));
                 B[q] = lds128(tile + r1 * 128 + ((j ^ (r1 & 7)) << 4));
@@ -168,7 +181,29 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
                 base = tile + b * (uint32_t)p.pixels * 128u + ((uint32_t)(CPG * j) * p.units + uIn) * 4u;
                 pitch = (uint32_t)p.units * 4u;
             }
-            if constexpr (EPW == 2) {
+            if constexpr (ODD) {
+                uint32_t b = 0, uIn = (uint32_t)u;
+                if constexpr (MB)
+                    p.unitsDiv.divmod((uint32_t)u, b, uIn);
+                const uint32_t region = tile + b * (uint32_t)p.pixels * 128u;
+                const bool second = (int)(2u * uIn) + 1 < p.pixels;
+                const uint32_t wd[8] = {__byte_perm(A[q].x, B[q].x, 0x5410), __byte_perm(A[q].x, B[q].x, 0x7632),
+                                        __byte_perm(A[q].y, B[q].y, 0x5410), __byte_perm(A[q].y, B[q].y, 0x7632),
+                                        __byte_perm(A[q].z, B[q].z, 0x5410), __byte_perm(A[q].z, B[q].z, 0x7632),
+                                        __byte_perm(A[q].w, B[q].w, 0x5410), __byte_perm(A[q].w, B[q].w, 0x7632)};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    // half index of (channel 8j+i, pixel 2*uIn): even exactly for even channels
+                    const uint32_t at = region + ((uint32_t)(CPG * j + i) * (uint32_t)p.pixels + 2u * uIn) * 2u;
+                    if ((i & 1) == 0 && second) {
+                        sts32(at, wd[i]);
+                    } else {
+                        sts16(at, wd[i] & 0xffffu);
+                        if (second)
+                            sts16(at + 2u, wd[i] >> 16);
+                    }
+                }
+            } else if constexpr (EPW == 2) {
                 sts32(base + 0u * pitch, __byte_perm(A[q].x, B[q].x, 0x5410));
                 sts32(base + 1u * pitch, __byte_perm(A[q].x, B[q].x, 0x7632));
                 sts32(base + 2u * pitch, __byte_perm(A[q].y, B[q].y, 0x5410));
@@ -226,27 +261,32 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
     }
 }
 
-// GW > 0 (plane rows of a multiple of GW = 2 or 4 words): the tile is stored with a row pitch rounded
+// GW >= 1 (plane rows of a multiple of GW = 1, 2 or 4 words): the tile is stored with a row pitch rounded
 // up to 32 words and its 16-byte column groups XOR-ed by the channel-group index, which lets eight
 // neighbouring lanes own the eight 16-byte groups of ONE pixel without bank conflicts -- every
 // warp-level store / reduction then covers whole 128-byte lines of the image (four pixels) instead
 // of sixteen scattered sectors (measured: 5.3 -> 6.4 TB/s on the fp16 add scatter).  GW is the
-// copy-in unit in words (a unit must not straddle plane rows).  GW == 0 (odd row length): dense
-// tile, sixteen-pixel lane mapping.
-// kTileChunked / kTileMulti (GW > 0 only): as in the gather.  kTileMulti keeps block b's words in
+// copy-in unit in words (a unit must not straddle plane rows; with one block per item the chunk is
+// one contiguous run, read with 16-byte loads and split into GW-word pieces when it is stored, so
+// rows of an odd number of words, GW == 1, get the same tile).  GW == 0 (fp16 blocks of an odd
+// pixel count): dense copy of the chunk, rows of an odd number of halves; words of odd channels are
+// read as two halves.  That layout needs no swizzle: channel groups are 4*P words apart, and with
+// P odd the eight groups land on eight different bank quads.
+// kTileChunked / kTileMulti (GW >= 2 only): as in the gather.  kTileMulti keeps block b's words in
 // columns [b*units, (b+1)*units) of every tile row.
 template <int MODE, typename T, int GW, int SHAPE>
 __global__ void __launch_bounds__(kPsThreads, MODE == kScatterAdd ? 2 : 3)
 planes_scatter_simt(const BlockArgs a, const SimtPlan p)
 {
     constexpr bool PCH = SHAPE == kTileChunked, MB = SHAPE == kTileMulti;
-    static_assert(SHAPE == kTileSingle || GW > 0, "pixel chunks and shared tiles need the swizzled tile");
+    static_assert(SHAPE == kTileSingle || GW > 1, "pixel chunks and shared tiles copy in whole 8- or 16-byte units");
+    static_assert(GW != 0 || sizeof(T) == 2, "odd rows of halves: fp16 only");
+    constexpr bool ODD = GW == 0;
     __shared__ __align__(128) unsigned char tileRaw[kPsTileBytes];
     constexpr int EPW = 4 / (int)sizeof(T);
     constexpr int CPG = 16 / (int)sizeof(T);
     constexpr bool SWZ = GW > 0;
-    constexpr int kMaxTasks = SWZ ? (8 * (kPsMaxPixels / EPW)) / kPsThreads
-                                  : ((kPsMaxPixels / EPW + 15) / 16 + 1) / 2;
+    constexpr int kMaxTasks = (8 * (kPsMaxPixels / EPW)) / kPsThreads;
     const uint32_t tile = smem_u32(tileRaw);
 
     // One item per CTA when the grid was sized from a host-side count; with a device-side count the
@@ -282,7 +322,7 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
         p.cChunks.divmod((uint32_t)item, ib, cc);
     }
     const int nG = min(8, p.groups - 8 * (int)cc);   // 16-byte groups in this chunk
-    const int nTasks = SWZ ? 8 * U : ((U + 15) >> 4) * 128;
+    const int nTasks = 8 * U;
     const uint32_t pitchW = SWZ ? (uint32_t)p.pitchWords : (uint32_t)U;   // tile row pitch in words
 
     // A block's window: image plane of its batch index at this item's channel chunk + window origin.
@@ -321,16 +361,11 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
             return nullptr;
         return reinterpret_cast<uint4*>(wn.img + ((long long)h * a.W + w) * a.C + j * CPG);
     };
-    // task t of this thread -> (16-byte channel group j, word column u)
+    // task t of this thread -> (16-byte channel group j, word column u): eight neighbouring lanes
+    // own the 128 bytes of one pixel (pair)
     auto task = [&](int t, int& j, int& u) {
-        if constexpr (SWZ) {
-            j = t & 7;
-            u = t >> 3;
-        } else {
-            const int uLocal = t & 15, grp = t >> 4;
-            j = grp & 7;
-            u = ((grp >> 3) << 4) + uLocal;
-        }
+        j = t & 7;
+        u = t >> 3;
     };
 
     // ---- stack -> tile: the chunk's planes are one contiguous run of 32*P words (pixel chunks: one
@@ -358,9 +393,10 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
             }
             tileW = c * pitchW + (colW ^ (4u * ((c / CPG) & 7u)));
         };
-        if constexpr (GW == 2 && SHAPE == kTileSingle) {
+        if constexpr ((GW == 2 || GW == 1) && SHAPE == kTileSingle) {
             // The chunk is one contiguous 16-byte aligned run: 16-byte loads even though plane rows
-            // are only 8-byte multiples; a vector that straddles two rows is split when it is stored.
+            // are only 8- or 4-byte multiples; a vector is stored as 4/GW pieces of GW words, each
+            // placed in its own row and column.
             const uint4* src = reinterpret_cast<const uint4*>(srcT);
             const int nVec = nG * P;
             uint4 v[kPsMaxVecs];
@@ -372,18 +408,23 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
             for (int k = 0; k < kPsMaxVecs; ++k) {
                 const int vi = (int)threadIdx.x + k * kPsThreads;
                 if (vi < nVec) {
-                    uint32_t c, col;
-                    unitsPerRow.divmod(2u * (uint32_t)vi, c, col);
-                    uint32_t w = c * pitchW + ((col * 2u) ^ (4u * ((c / CPG) & 7u)));
-                    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(tile + w * 4u), "r"(v[k].x), "r"(v[k].y)
-                                 : "memory");
-                    if (++col == unitsPerRow.div) {
-                        col = 0;
-                        ++c;
+                    uint32_t c, col;   // row and column (in GW-word units) of the vector's first piece
+                    unitsPerRow.divmod((uint32_t)(4 / GW) * (uint32_t)vi, c, col);
+                    const uint32_t piece[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+#pragma unroll
+                    for (int h = 0; h < 4 / GW; ++h) {
+                        const uint32_t w = c * pitchW + ((col * GW) ^ (4u * ((c / CPG) & 7u)));
+                        if constexpr (GW == 2)
+                            asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(tile + w * 4u), "r"(piece[2 * h]),
+                                         "r"(piece[2 * h + 1])
+                                         : "memory");
+                        else
+                            sts32(tile + w * 4u, piece[h]);
+                        if (++col == unitsPerRow.div) {
+                            col = 0;
+                            ++c;
+                        }
                     }
-                    w = c * pitchW + ((col * 2u) ^ (4u * ((c / CPG) & 7u)));
-                    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(tile + w * 4u), "r"(v[k].z), "r"(v[k].w)
-                                 : "memory");
                 }
             }
         } else if constexpr (GW == 2) {
@@ -459,8 +500,9 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
                 const Window wn = locate(u * EPW, pix);
 #pragma unroll
                 for (int e = 0; e < EPW; ++e)
-                    if (const uint4* d = dest(wn, pix + e, j))
-                        old[q][e] = *d;
+                    if (!ODD || pix + e < p.pixels)
+                        if (const uint4* d = dest(wn, pix + e, j))
+                            old[q][e] = *d;
             }
         }
     }
@@ -482,16 +524,23 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
         if constexpr (EPW == 2) {
             uint32_t w[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-                w[i] = lds32(base + (uint32_t)i * pitch);
+            for (int i = 0; i < 8; ++i) {
+                if constexpr (ODD) {   // half index of (channel 8j+i, pixel 2u): even exactly for even channels
+                    const uint32_t at = tile + ((uint32_t)(CPG * j + i) * (uint32_t)p.pixels + 2u * (uint32_t)u) * 2u;
+                    w[i] = (i & 1) == 0 ? lds32(at) : (lds16(at) | (lds16(at + 2u) << 16));
+                } else {
+                    w[i] = lds32(base + (uint32_t)i * pitch);
+                }
+            }
             const uint4 v0 = make_uint4(__byte_perm(w[0], w[1], 0x5410), __byte_perm(w[2], w[3], 0x5410),
                                         __byte_perm(w[4], w[5], 0x5410), __byte_perm(w[6], w[7], 0x5410));
             const uint4 v1 = make_uint4(__byte_perm(w[0], w[1], 0x7632), __byte_perm(w[2], w[3], 0x7632),
                                         __byte_perm(w[4], w[5], 0x7632), __byte_perm(w[6], w[7], 0x7632));
             if (uint4* d = dest(wn, pix, j))
                 image_write<16, MODE, T>(d, v0, old[q][0]);
-            if (uint4* d = dest(wn, pix + 1, j))
-                image_write<16, MODE, T>(d, v1, old[q][EPW - 1]);
+            if (!ODD || pix + 1 < p.pixels)   // an odd row's last word holds one pixel
+                if (uint4* d = dest(wn, pix + 1, j))
+                    image_write<16, MODE, T>(d, v1, old[q][EPW - 1]);
         } else {
             const uint4 v = make_uint4(lds32(base), lds32(base + pitch), lds32(base + 2u * pitch),
                                        lds32(base + 3u * pitch));
@@ -503,16 +552,16 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
     }
 }
 
-// Pixels of a multiple of 16 bytes (the last 128-byte chunk may be partial), an even number of
-// pixels per block for fp16, 16-byte aligned buffers.  Blocks of more than 384 pixels run as pixel
-// chunks (the scatter then needs plane rows of an even number of words).
+// Pixels of a multiple of 16 bytes (the last 128-byte chunk may be partial), 16-byte aligned buffers.
+// Blocks of more than 384 pixels run as pixel chunks (fp16: an even pixel count; the scatter then
+// needs plane rows of an even number of words).
 static bool planes_simt_eligible(const BlockArgs& a, int itemsize)
 {
     const char* off = getenv("SBNET_DISABLE_TMA");
     if (off && off[0] == '1')
         return false;
     const long long P = (long long)a.bSzH * a.bSzW;
-    if (((size_t)a.C * itemsize) % 16 != 0 || P > (1 << 24) || (itemsize == 2 && (P & 1)))
+    if (((size_t)a.C * itemsize) % 16 != 0 || P > (1 << 24) || (itemsize == 2 && (P & 1) && P > kPsMaxPixels))
         return false;
     return ((reinterpret_cast<uintptr_t>(a.image) | reinterpret_cast<uintptr_t>(a.stack)) & 15) == 0;
 }
@@ -531,12 +580,13 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
     p.cChunks = FastDiv((uint32_t)((p.groups + 7) / 8));
     p.blockW = FastDiv((uint32_t)a.bSzW);
     p.pixels = P;
-    p.units = itemsize == 4 ? P : P / 2;
-    const int gw = p.units % 4 == 0 ? 4 : (p.units % 2 == 0 ? 2 : 0);
+    const bool odd = itemsize == 2 && (P & 1);   // fp16 rows of an odd number of halves
+    p.units = itemsize == 4 ? P : (P + 1) / 2;
+    const int gw = odd ? 0 : (p.units % 4 == 0 ? 4 : (p.units % 2 == 0 ? 2 : 1));   // words per copy-in unit
     // Blocks of more than 384 pixels: the fewest equal pixel chunks, each a multiple of 8 pixels.
     const int nPc = (P + kPsMaxPixels - 1) / kPsMaxPixels;
     const bool pch = nPc > 1;
-    if (pch && mode != kGather && gw == 0)
+    if (pch && mode != kGather && gw < 2)
         return cudaSuccess;
     const int epw = 4 / itemsize;
     p.chunkPixels = pch ? (((P + nPc - 1) / nPc + 7) & ~7) : P;
@@ -544,8 +594,8 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
     const int chunkUnits = p.chunkPixels / epw;
     const int lastUnits = (P - ((int)p.pChunks.div - 1) * p.chunkPixels) / epw;
     p.rowsAligned = ((size_t)P * itemsize) % 16 == 0;
-    p.unitsPerRow = FastDiv((uint32_t)(gw ? (pch ? chunkUnits : p.units) / gw : 1));
-    p.unitsPerRowLast = FastDiv((uint32_t)(gw ? (pch ? lastUnits : p.units) / gw : 1));
+    p.unitsPerRow = FastDiv((uint32_t)(gw >= 1 ? (pch ? chunkUnits : p.units) / gw : 1));
+    p.unitsPerRowLast = FastDiv((uint32_t)(gw >= 1 ? (pch ? lastUnits : p.units) / gw : 1));
     p.pitchWords = ((pch ? chunkUnits : p.units) + 31) & ~31;
     // Blocks of at most 192 pixels: pack as many whole blocks into the tile as fit, but never so many
     // that fewer than four items per SM remain (small launches keep one block per item).
@@ -553,11 +603,13 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
     // pixels (measured: 8x8 0.62 -> 0.70 of copy bandwidth, but 12x12 0.88 -> 0.69: its copy-in then
     // needs two load batches), so larger blocks keep one block per scatter item.
     p.blocksPerItem = 1;
-    if (!pch && (mode == kGather || (gw > 0 && P <= 80))) {
+    if (!pch && (mode == kGather || (gw >= 2 && P <= 80))) {
         long long perSm = (long long)a.numActive * p.cChunks.div / ((long long)sm_count() * 4);
         if (const char* force = getenv("SBNET_TILE_BLOCKS"))   // tests: pack up to this many blocks regardless of the launch size
             perSm = atoi(force);
-        const long long k = std::min<long long>(std::min<long long>(kPsMaxPixels / P, kPsThreads), perSm);
+        // what fits: 384 pixels, and (rows rounded up to words) 384/EPW words per tile row
+        const long long fit = std::min<long long>(kPsMaxPixels / P, (kPsMaxPixels / epw) / p.units);
+        const long long k = std::min<long long>(std::min<long long>(fit, kPsThreads), perSm);
         if (k >= 2)
             p.blocksPerItem = (int)k;
     }
@@ -605,13 +657,22 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
         else if (gw == 2)                                             \
             SBNET_PS_SG(M, T_, 2);                                    \
         else                                                          \
-            SBNET_PS((planes_scatter_simt<M, T_, 0, kTileSingle>));   \
+            SBNET_PS((planes_scatter_simt<M, T_, 1, kTileSingle>));   \
     } while (0)
     if (mode == kGather) {
         if (dtype == 0)
             SBNET_PS_G(float);
+        else if (odd && multi)
+            SBNET_PS((planes_gather_simt<__half, kTileMulti, true>));
+        else if (odd)
+            SBNET_PS((planes_gather_simt<__half, kTileSingle, true>));
         else
             SBNET_PS_G(__half);
+    } else if (odd) {
+        if (mode == kScatterSet)
+            SBNET_PS((planes_scatter_simt<kScatterSet, __half, 0, kTileSingle>));
+        else
+            SBNET_PS((planes_scatter_simt<kScatterAtomic, __half, 0, kTileSingle>));
     } else if (dtype == 0) {
         if (mode == kScatterSet)
             SBNET_PS_SC(kScatterSet, float);

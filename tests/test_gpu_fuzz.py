@@ -58,7 +58,11 @@ def test_random_geometry(cuda_ops, oracle_port, seed):
                                            atomic=True, transpose=transpose)
         o = cuda_ops.sparse_scatter_var(stack, cnt, idx, base.copy(), bsize, bstride, boffset, add=True,
                                         atomic=True, transpose=transpose)
-        err = np.abs(o.astype(np.float64) - e.astype(np.float64)) / np.maximum(np.abs(e.astype(np.float64)), 1.0)
+        # relative to |base| + sum of |addends|, which bounds every partial sum whatever the arrival order
+        mag = oracle_port.sparse_scatter_var(np.abs(stack).astype(np.float32), cnt, idx,
+                                             np.abs(base).astype(np.float32), bsize, bstride, boffset, add=True,
+                                             atomic=True, transpose=transpose)
+        err = np.abs(o.astype(np.float64) - e.astype(np.float64)) / np.maximum(mag.astype(np.float64), 1.0)
         assert err.max() <= rtol, (err.max(), rtol)
         if disjoint:
             e = oracle_port.sparse_scatter_var(stack, cnt, idx, base.copy(), bsize, bstride, boffset, add=True,

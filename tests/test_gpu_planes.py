@@ -18,7 +18,11 @@ SHAPES = [
     (np.float16, 1, 40, 40, 128, (16, 16), (16, 16), (0, 0)),
     (np.float16, 3, 33, 29, 64, (6, 5), (4, 3), (-2, -3)),      # 30 pixels, all four borders
     (np.float16, 1, 50, 50, 64, (19, 20), (7, 9), (-5, -4)),    # 380 pixels
-    (np.float16, 1, 50, 50, 64, (5, 5), (5, 5), (0, 0)),        # odd pixel count: general kernel
+    (np.float16, 1, 50, 50, 64, (5, 5), (5, 5), (0, 0)),        # odd pixel count: rows of an odd number of halves
+    (np.float16, 2, 64, 48, 128, (17, 17), (15, 15), (-1, -1)), # 289 pixels, overlapping
+    (np.float16, 1, 60, 60, 40, (19, 19), (19, 19), (-9, -9)),  # 361 pixels, partial channel chunk
+    (np.float16, 1, 37, 41, 64, (7, 3), (5, 3), (-3, -1)),      # 21 pixels
+    (np.float16, 1, 9, 400, 64, (1, 383), (1, 383), (0, 5)),    # the largest odd block of one tile
     (np.float16, 1, 64, 64, 64, (20, 20), (16, 16), (-2, -2)),  # 400 pixels: two pixel chunks
     (np.float32, 2, 64, 48, 32, (18, 18), (16, 16), (-1, -1)),
     (np.float32, 2, 64, 48, 128, (18, 18), (16, 16), (-1, -1)),
@@ -109,11 +113,14 @@ def _run_shape(cuda_ops, oracle_port, shape):
                                        atomic=True, transpose=True)
     o = cuda_ops.sparse_scatter_var(stack, cnt, idx, base.copy(), bsize, bstride, boffset, add=True,
                                     atomic=True, transpose=True)
-    # tolerance: 1e-6 (fp32) / 1e-3 (fp16) per addend; a pixel receives the base value plus one
-    # addend per covering block, and the GPU adds them in arrival order
+    # tolerance: 1e-6 (fp32) / 1e-3 (fp16) per addend, relative to the magnitude of what is summed
+    # (|base| + sum of |addends|: every partial sum, whose rounding the arrival order decides, is
+    # bounded by it even when the final value cancels); a pixel receives one addend per covering block
     cover = -(-bsize[0] // bstride[0]) * -(-bsize[1] // bstride[1])
     rtol = (1e-6 if dtype == np.float32 else 1e-3) * (1 + cover)
-    err = np.abs(o.astype(np.float64) - e.astype(np.float64)) / np.maximum(np.abs(e.astype(np.float64)), 1.0)
+    mag = oracle_port.sparse_scatter_var(np.abs(stack).astype(np.float32), cnt, idx, np.abs(base).astype(np.float32),
+                                         bsize, bstride, boffset, add=True, atomic=True, transpose=True)
+    err = np.abs(o.astype(np.float64) - e.astype(np.float64)) / np.maximum(mag.astype(np.float64), 1.0)
     assert err.max() <= rtol, err.max()
 
 
@@ -175,6 +182,11 @@ SMALL_BLOCKS = [
     (np.float32, 1, 30, 30, 32, (1, 1), (1, 1), (0, 0)),        # one pixel per block
     (np.float32, 1, 64, 64, 32, (12, 16), (12, 16), (0, 0)),    # 192 pixels: two blocks per tile
     (np.float16, 1, 64, 64, 64, (2, 1), (2, 1), (0, 0)),        # two pixels per block
+    # fp16, odd pixel counts: the gather pairs pixels inside each block
+    (np.float16, 2, 40, 40, 64, (5, 5), (3, 3), (-1, -1)),
+    (np.float16, 1, 33, 29, 200, (3, 3), (3, 3), (0, 0)),
+    (np.float16, 1, 30, 30, 64, (1, 1), (1, 1), (0, 0)),
+    (np.float16, 1, 64, 64, 32, (13, 13), (11, 11), (-1, -1)),  # 169 pixels: two blocks per tile
 ]
 
 
