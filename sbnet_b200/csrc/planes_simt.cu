@@ -51,7 +51,7 @@ struct SimtPlan {
     int blocksPerItem; // blocks sharing one tile
     FastDiv pixelsDiv; // P
     FastDiv unitsDiv;  // units
-    FastDiv runUnits, runUnitsLast; // copy-in units of one block's chunk (full / last channel chunk)
+    FastDiv runVecs, runVecsLast; // 16-byte vectors of one block's chunk (full / last channel chunk)
 };
 
 // How a work item maps onto the 384-pixel tile.
@@ -279,7 +279,8 @@ __global__ void __launch_bounds__(kPsThreads, MODE == kScatterAdd ? 2 : 3)
 planes_scatter_simt(const BlockArgs a, const SimtPlan p)
 {
     constexpr bool PCH = SHAPE == kTileChunked, MB = SHAPE == kTileMulti;
-    static_assert(SHAPE == kTileSingle || GW > 1, "pixel chunks and shared tiles copy in whole 8- or 16-byte units");
+    static_assert(!PCH || GW > 1, "pixel chunks copy in whole 8- or 16-byte units");
+    static_assert(!MB || GW > 0, "shared tiles need word-aligned rows");
     static_assert(GW != 0 || sizeof(T) == 2, "odd rows of halves: fp16 only");
     constexpr bool ODD = GW == 0;
     __shared__ __align__(128) unsigned char tileRaw[kPsTileBytes];
@@ -375,52 +376,58 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
                         ((long long)ib * a.C + (long long)cc * (128 / (int)sizeof(T))) * p.pixels + p0;
         constexpr uint32_t G = GW > 0 ? GW : 1;
         const uint32_t rowUnits = (uint32_t)(p.pixels / EPW) / G;               // one whole plane row
-        const uint32_t blockUnits = (uint32_t)((long long)a.C * p.pixels / EPW) / G;   // one whole block
-        const FastDiv runDiv = (int)cc + 1 == (int)p.cChunks.div ? p.runUnitsLast : p.runUnits;
-        // copy-in unit vi -> its offset from srcT (in units) and its word in the tile
+        const FastDiv runDiv = (int)cc + 1 == (int)p.cChunks.div ? p.runVecsLast : p.runVecs;
+        // copy-in unit vi -> its offset from srcT (in units) and its word in the tile (one block per item)
         auto place = [&](uint32_t vi, uint32_t& srcUnit, uint32_t& tileW) {
-            uint32_t c, col, colW;
-            if constexpr (MB) {
-                uint32_t b, rest;
-                runDiv.divmod(vi, b, rest);
-                p.unitsPerRow.divmod(rest, c, col);
-                srcUnit = b * blockUnits + rest;
-                colW = b * (uint32_t)p.units + col * G;
-            } else {
-                unitsPerRow.divmod(vi, c, col);
-                srcUnit = PCH ? c * rowUnits + col : vi;
-                colW = col * G;
-            }
-            tileW = c * pitchW + (colW ^ (4u * ((c / CPG) & 7u)));
+            uint32_t c, col;
+            unitsPerRow.divmod(vi, c, col);
+            srcUnit = PCH ? c * rowUnits + col : vi;
+            tileW = c * pitchW + ((col * G) ^ (4u * ((c / CPG) & 7u)));
         };
-        if constexpr ((GW == 2 || GW == 1) && SHAPE == kTileSingle) {
-            // The chunk is one contiguous 16-byte aligned run: 16-byte loads even though plane rows
-            // are only 8- or 4-byte multiples; a vector is stored as 4/GW pieces of GW words, each
-            // placed in its own row and column.
+        if constexpr ((GW >= 1 && MB) || ((GW == 2 || GW == 1) && SHAPE == kTileSingle)) {
+            // A block's chunk is one contiguous 16-byte aligned run: 16-byte loads even where plane
+            // rows are only 8- or 4-byte multiples; a vector is stored as 4/GW pieces of GW words,
+            // each placed in its own row and column.
             const uint4* src = reinterpret_cast<const uint4*>(srcT);
             const int nVec = nG * P;
+            const uint32_t blockVecs = (uint32_t)((long long)a.C * p.pixels * (int)sizeof(T) / 16);
             uint4 v[kPsMaxVecs];
-#pragma unroll
-            for (int k = 0; k < kPsMaxVecs; ++k)
-                if ((int)threadIdx.x + k * kPsThreads < nVec)
-                    v[k] = ld_stream(src + threadIdx.x + k * kPsThreads);
 #pragma unroll
             for (int k = 0; k < kPsMaxVecs; ++k) {
                 const int vi = (int)threadIdx.x + k * kPsThreads;
                 if (vi < nVec) {
+                    uint32_t at = (uint32_t)vi;
+                    if constexpr (MB) {   // vector rest of block b's run
+                        uint32_t b, rest;
+                        runDiv.divmod((uint32_t)vi, b, rest);
+                        at = b * blockVecs + rest;
+                    }
+                    v[k] = ld_stream(src + at);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < kPsMaxVecs; ++k) {
+                const int vi = (int)threadIdx.x + k * kPsThreads;
+                if (vi < nVec) {
+                    uint32_t b = 0, rest = (uint32_t)vi;
+                    if constexpr (MB)
+                        runDiv.divmod((uint32_t)vi, b, rest);
                     uint32_t c, col;   // row and column (in GW-word units) of the vector's first piece
-                    unitsPerRow.divmod((uint32_t)(4 / GW) * (uint32_t)vi, c, col);
+                    p.unitsPerRow.divmod((uint32_t)(4 / GW) * rest, c, col);
+                    const uint32_t colBase = b * (uint32_t)p.units;
                     const uint32_t piece[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
 #pragma unroll
                     for (int h = 0; h < 4 / GW; ++h) {
-                        const uint32_t w = c * pitchW + ((col * GW) ^ (4u * ((c / CPG) & 7u)));
-                        if constexpr (GW == 2)
+                        const uint32_t w = c * pitchW + ((colBase + col * GW) ^ (4u * ((c / CPG) & 7u)));
+                        if constexpr (GW == 4)
+                            sts128(tile + w * 4u, v[k]);
+                        else if constexpr (GW == 2)
                             asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(tile + w * 4u), "r"(piece[2 * h]),
                                          "r"(piece[2 * h + 1])
                                          : "memory");
                         else
                             sts32(tile + w * 4u, piece[h]);
-                        if (++col == unitsPerRow.div) {
+                        if (++col == p.unitsPerRow.div) {
                             col = 0;
                             ++c;
                         }
@@ -599,11 +606,11 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
     p.pitchWords = ((pch ? chunkUnits : p.units) + 31) & ~31;
     // Blocks of at most 192 pixels: pack as many whole blocks into the tile as fit, but never so many
     // that fewer than four items per SM remain (small launches keep one block per item).
-    // The gather gains at every size (more bytes in flight per SM); the scatter only up to about 80
-    // pixels (measured: 8x8 0.62 -> 0.70 of copy bandwidth, but 12x12 0.88 -> 0.69: its copy-in then
-    // needs two load batches), so larger blocks keep one block per scatter item.
+    // The gather gains at every size (more bytes in flight per SM); the scatter up to about 100
+    // pixels (measured, of copy bandwidth: 5x5 fp32 0.27 -> 0.80, 8x8 0.62 -> 0.80, 10x10 0.76 -> 0.80,
+    // but 12x12 0.88 -> 0.75), so larger blocks keep one block per scatter item.
     p.blocksPerItem = 1;
-    if (!pch && (mode == kGather || (gw >= 2 && P <= 80))) {
+    if (!pch && (mode == kGather || (gw >= 1 && P <= 100))) {
         long long perSm = (long long)a.numActive * p.cChunks.div / ((long long)sm_count() * 4);
         if (const char* force = getenv("SBNET_TILE_BLOCKS"))   // tests: pack up to this many blocks regardless of the launch size
             perSm = atoi(force);
@@ -616,9 +623,9 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
     const bool multi = p.blocksPerItem > 1;
     p.pixelsDiv = FastDiv((uint32_t)P);
     p.unitsDiv = FastDiv((uint32_t)std::max(p.units, 1));
-    const int cpg = 16 / itemsize, lastGroups = p.groups - 8 * ((int)p.cChunks.div - 1);
-    p.runUnits = FastDiv((uint32_t)std::max(8 * cpg * (int)p.unitsPerRow.div, 1));
-    p.runUnitsLast = FastDiv((uint32_t)std::max(lastGroups * cpg * (int)p.unitsPerRow.div, 1));
+    const int lastGroups = p.groups - 8 * ((int)p.cChunks.div - 1);
+    p.runVecs = FastDiv((uint32_t)(8 * P));
+    p.runVecsLast = FastDiv((uint32_t)(lastGroups * P));
     if (multi)
         p.pitchWords = (p.blocksPerItem * p.units + 31) & ~31;
     const long long nItems = multi ? (long long)((a.numActive + p.blocksPerItem - 1) / p.blocksPerItem) * p.cChunks.div
@@ -656,6 +663,8 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
             SBNET_PS_SG(M, T_, 4);                                    \
         else if (gw == 2)                                             \
             SBNET_PS_SG(M, T_, 2);                                    \
+        else if (shape == kTileMulti)                                 \
+            SBNET_PS((planes_scatter_simt<M, T_, 1, kTileMulti>));    \
         else                                                          \
             SBNET_PS((planes_scatter_simt<M, T_, 1, kTileSingle>));   \
     } while (0)
