@@ -176,7 +176,7 @@ def test_device_count_calls_on_blocks_above_384_pixels(cuda_ops, dtype):
 SMALL_BLOCKS = [
     (np.float16, 2, 40, 40, 64, (6, 6), (4, 4), (-1, -1)),      # 36 pixels, overlapping
     (np.float16, 1, 33, 29, 200, (4, 6), (4, 6), (0, 0)),       # 24 pixels, partial last channel chunk
-    (np.float32, 2, 40, 40, 32, (5, 5), (3, 3), (-1, -1)),      # 25 pixels (odd rows): gather only, scatter keeps one block per tile
+    (np.float32, 2, 40, 40, 32, (5, 5), (3, 3), (-1, -1)),      # 25 pixels: rows of an odd number of words
     (np.float32, 1, 50, 50, 48, (8, 8), (8, 8), (0, 0)),        # 64 pixels, partial last channel chunk
     (np.float16, 1, 50, 50, 128, (10, 10), (8, 8), (-1, -1)),   # rows of 50 words: 8-byte copy-in
     (np.float32, 1, 30, 30, 32, (1, 1), (1, 1), (0, 0)),        # one pixel per block
