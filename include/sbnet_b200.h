@@ -36,6 +36,7 @@ extern "C" {
 /* element types of x / y / block stacks */
 #define SBNET_F32 0
 #define SBNET_F16 1 /* extension: the reference registers T = float only (sparse_gather.cc:49) */
+#define SBNET_BF16 2 /* extension: bfloat16; accumulation rounds to nearest even once per add, no flush */
 
 /* sbnet_reduce_mask flags */
 #define SBNET_SCRATCH_CLEAN 1 /* scratch[2..3] are already zero (see below): skip the memset */

@@ -37,6 +37,8 @@ _SIGS = {
     "oracle_sparse_gather_f16": (None, [_p, _i, _i, _i, _i, _p] + _GEOM + [_i, _p, _i]),
     "oracle_sparse_scatter_f32": (None, [_p, _i, _i, _i, _i, _p] + _GEOM + [_i, _p, _i, _i, _i]),
     "oracle_sparse_scatter_f16": (None, [_p, _i, _i, _i, _i, _p] + _GEOM + [_i, _p, _i, _i, _i]),
+    "oracle_sparse_gather_bf16": (None, [_p, _i, _i, _i, _i, _p] + _GEOM + [_i, _p, _i]),
+    "oracle_sparse_scatter_bf16": (None, [_p, _i, _i, _i, _i, _p] + _GEOM + [_i, _p, _i, _i, _i]),
     "oracle_copy_tensor": (None, [_p, _p, C.c_size_t]),
 }
 
@@ -104,6 +106,8 @@ class OracleLib:
             return self.lib.oracle_sparse_gather_f32, self.lib.oracle_sparse_scatter_f32
         if dtype == np.float16:
             return self.lib.oracle_sparse_gather_f16, self.lib.oracle_sparse_scatter_f16
+        if np.dtype(dtype).name == "bfloat16":   # ml_dtypes.bfloat16 (numpy itself has no bfloat16)
+            return self.lib.oracle_sparse_gather_bf16, self.lib.oracle_sparse_scatter_bf16
         raise TypeError(f"unsupported dtype {dtype}")
 
     def sparse_gather(self, x, bin_counts, active_block_indices, dynamic_bsize, dynamic_bstride,

@@ -166,6 +166,8 @@ ORACLE_API void oracle_reduce_mask_op(const float* mask, int N, int H, int W, fl
 
 DEFINE_GATHER_SCATTER(f32, float)
 DEFINE_GATHER_SCATTER(f16, _Float16)
+/* bfloat16: gcc evaluates `py[c] += v` as a float addition converted back with round-to-nearest-even */
+DEFINE_GATHER_SCATTER(bf16, __bf16)
 
 /* sparse_gather.cc:135-142 */
 ORACLE_API void oracle_copy_tensor(void* dst, const void* src, size_t bytes)

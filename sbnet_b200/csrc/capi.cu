@@ -56,7 +56,7 @@ int blocks_call(const char* op, int mode, int dtype, int N, int H, int W, int C,
                 int bStrW, int numActive, const int32_t* numActiveDev, const int16_t* idx,
                 int transpose, void* stream)
 {
-    if (dtype != SBNET_F32 && dtype != SBNET_F16)
+    if (dtype != SBNET_F32 && dtype != SBNET_F16 && dtype != SBNET_BF16)
         return reject(SBNET_ERR_INVALID_ARGUMENT, "%s: unknown dtype %d", op, dtype);
     if (N < 1 || H < 1 || W < 1 || C < 1)
         return reject(SBNET_ERR_INVALID_ARGUMENT,

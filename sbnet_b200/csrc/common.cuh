@@ -1,5 +1,8 @@
 // Shared device/host helpers for the block-op kernels (sm_100a only).
 #pragma once
+#include <type_traits>
+
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -90,6 +93,12 @@ template <> __device__ __forceinline__ uint32_t add_word<__half>(uint32_t a, uin
     return *reinterpret_cast<uint32_t*>(&r);
 }
 
+template <> __device__ __forceinline__ uint32_t add_word<__nv_bfloat16>(uint32_t a, uint32_t b)
+{
+    __nv_bfloat162 r = __hadd2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+
 template <typename T> __device__ __forceinline__ uint4 vadd(uint4 a, uint4 b)
 {
     return make_uint4(add_word<T>(a.x, b.x), add_word<T>(a.y, b.y), add_word<T>(a.z, b.z),
@@ -105,9 +114,14 @@ template <typename T> __device__ __forceinline__ uint32_t vadd(uint32_t a, uint3
 }
 template <typename T> __device__ __forceinline__ uint16_t vadd(uint16_t a, uint16_t b)
 {
-    // only reachable for T = __half (a 2-byte vector cannot hold a float)
-    __half r = __hadd(__ushort_as_half(a), __ushort_as_half(b));
-    return __half_as_ushort(r);
+    // only reachable for 2-byte element types (a 2-byte vector cannot hold a float)
+    if constexpr (sizeof(T) == 2 && !std::is_same<T, __half>::value) {
+        __nv_bfloat16 r = __hadd(__ushort_as_bfloat16(a), __ushort_as_bfloat16(b));
+        return __bfloat16_as_ushort(r);
+    } else {
+        __half r = __hadd(__ushort_as_half(a), __ushort_as_half(b));
+        return __half_as_ushort(r);
+    }
 }
 
 // ---- vector reductions into global memory (no return value, resolved in L2) ----------------------
@@ -150,6 +164,28 @@ template <> struct Red<__half> {
     static __device__ __forceinline__ void add(uint16_t* p, uint16_t v)
     {
         asm volatile("red.global.add.noftz.f16 [%0], %1;" ::"l"(p), "h"(v) : "memory");
+    }
+};
+
+template <> struct Red<__nv_bfloat16> {
+    static __device__ __forceinline__ void add(uint4* p, uint4 v)
+    {
+        asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y),
+                     "r"(v.z), "r"(v.w)
+                     : "memory");
+    }
+    static __device__ __forceinline__ void add(uint2* p, uint2 v)
+    {
+        asm volatile("red.global.add.noftz.v2.bf16x2 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y)
+                     : "memory");
+    }
+    static __device__ __forceinline__ void add(uint32_t* p, uint32_t v)
+    {
+        asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+    }
+    static __device__ __forceinline__ void add(uint16_t* p, uint16_t v)
+    {
+        asm volatile("red.global.add.noftz.bf16 [%0], %1;" ::"l"(p), "h"(v) : "memory");
     }
 };
 

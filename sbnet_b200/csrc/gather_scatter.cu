@@ -406,6 +406,10 @@ cudaError_t launch_blocks(const BlockArgs& a, int dtype, int mode, bool transpos
     // destination read.  (fp32 keeps the explicit read-add-write: red.add.f32 flushes subnormals.)
     if (mode == kScatterAdd && dtype != 0)
         mode = kScatterAtomic;
+    // bf16 (dtype 2): gather and overwrite move bytes, so they run the fp16 instantiations; only
+    // accumulation (red.add.noftz.bf16x2, same argument as for fp16) has kernels of its own.
+    if (dtype == 2 && (mode == kGather || mode == kScatterSet))
+        dtype = 1;
     const int itemsize = dtype == 0 ? 4 : 2;
     if (transpose) {
         // Aligned shapes have two implementations: one short CTA per tile (planes_simt.cu) and the
@@ -434,6 +438,8 @@ cudaError_t launch_blocks(const BlockArgs& a, int dtype, int mode, bool transpos
     const int vb = pick_vector_bytes(a, itemsize);
     if (dtype == 0)
         dispatch_mode<float>(a, mode, transpose, vb, stream);
+    else if (dtype == 2)
+        dispatch_vb<kScatterAtomic, __nv_bfloat16>(a, transpose, vb, stream);
     else
         dispatch_mode<__half>(a, mode, transpose, vb, stream);
     return cudaGetLastError();

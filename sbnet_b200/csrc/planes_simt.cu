@@ -680,8 +680,12 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
     } else if (odd) {
         if (mode == kScatterSet)
             SBNET_PS((planes_scatter_simt<kScatterSet, __half, 0, kTileSingle>));
+        else if (dtype == 2)
+            SBNET_PS((planes_scatter_simt<kScatterAtomic, __nv_bfloat16, 0, kTileSingle>));
         else
             SBNET_PS((planes_scatter_simt<kScatterAtomic, __half, 0, kTileSingle>));
+    } else if (dtype == 2) {
+        SBNET_PS_SC(kScatterAtomic, __nv_bfloat16);   // gather / overwrite arrive as fp16
     } else if (dtype == 0) {
         if (mode == kScatterSet)
             SBNET_PS_SC(kScatterSet, float);

@@ -432,6 +432,8 @@ static cudaError_t set_smem(const void* fn, int bytes)
 cudaError_t launch_planes_tma(const BlockArgs& a, int dtype, int mode, cudaStream_t stream, bool* taken)
 {
     *taken = false;
+    if (dtype == 2)
+        return cudaSuccess;   // bf16 accumulation: tile CTAs or the general kernel
     const int itemsize = dtype == 0 ? 4 : 2;
     if (!planes_tma_eligible(a, itemsize))
         return cudaSuccess;

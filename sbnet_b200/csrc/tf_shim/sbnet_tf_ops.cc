@@ -7,8 +7,8 @@
 //   SparseGather                      sparse_gather.cc:48-57,  GPU registration :229-238
 //   SparseScatter / SparseScatterVar  sparse_gather.cc:242-268, GPU registration :374-387
 //   CudaTimerStart / CudaTimerEnd     sparse_gather.cc:390-395, GPU registration :463-466
-// Only the element type list differs: T is {float, half} for gather / scatter (fp16 is an addition;
-// float graphs are unaffected).  There is no CPU kernel: this library is GPU only.
+// Only the element type list differs: T is {float, half, bfloat16} for gather / scatter (the 16-bit
+// types are additions; float graphs are unaffected).  There is no CPU kernel: this library is GPU only.
 //
 // Build (needs TensorFlow headers, which are not part of this repository's toolchain image):
 //   g++ -std=c++17 -shared -fPIC sbnet_tf_ops.cc -o libsbnet.so \
@@ -51,6 +51,7 @@ Status FromSbnet(int rc)
 template <typename T> constexpr int SbnetType();
 template <> constexpr int SbnetType<float>() { return SBNET_F32; }
 template <> constexpr int SbnetType<Eigen::half>() { return SBNET_F16; }
+template <> constexpr int SbnetType<bfloat16>() { return SBNET_BF16; }
 
 void* StreamOf(OpKernelContext* ctx) { return (void*)ctx->eigen_device<GPUDevice>().stream(); }
 
@@ -196,16 +197,16 @@ REGISTER_OP("ReduceMask").Attr("T: {float}").Attr("tol: float").Attr("avgpool: b
     .Input("mask: T").Input("dynamic_bcount: int32").Input("dynamic_bsize: int32")
     .Input("dynamic_bstride: int32").Input("dynamic_boffset: int32")
     .Output("active_block_indices: int16").Output("bin_counts: int32");
-REGISTER_OP("SparseGather").Attr("T: {float, half}").Attr("transpose: bool = false")
+REGISTER_OP("SparseGather").Attr("T: {float, half, bfloat16}").Attr("transpose: bool = false")
     .Input("x: T").Input("bin_counts: int32").Input("active_block_indices: int16")
     .Input("dynamic_bsize: int32").Input("dynamic_bstride: int32").Input("dynamic_boffset: int32")
     .Output("y: T");
-REGISTER_OP("SparseScatterVar").Attr("T: {float, half}").Attr("add: bool").Attr("atomic: bool = false")
+REGISTER_OP("SparseScatterVar").Attr("T: {float, half, bfloat16}").Attr("add: bool").Attr("atomic: bool = false")
     .Attr("transpose: bool = false")
     .Input("x: T").Input("bin_counts: int32").Input("active_block_indices: int16").Input("ybase: Ref(T)")
     .Input("dynamic_bsize: int32").Input("dynamic_bstride: int32").Input("dynamic_boffset: int32")
     .Output("y: Ref(T)");
-REGISTER_OP("SparseScatter").Attr("T: {float, half}").Attr("add: bool").Attr("atomic: bool = false")
+REGISTER_OP("SparseScatter").Attr("T: {float, half, bfloat16}").Attr("add: bool").Attr("atomic: bool = false")
     .Attr("transpose: bool = false")
     .Input("x: T").Input("bin_counts: int32").Input("active_block_indices: int16").Input("ybase: T")
     .Input("dynamic_bsize: int32").Input("dynamic_bstride: int32").Input("dynamic_boffset: int32")
@@ -232,6 +233,7 @@ REGISTER_KERNEL_BUILDER(Name("ReduceMask").Device(DEVICE_GPU).TypeConstraint<flo
                             SparseScatterGpu<T, true>);
 SBNET_REGISTER_BLOCK_OPS(float)
 SBNET_REGISTER_BLOCK_OPS(Eigen::half)
+SBNET_REGISTER_BLOCK_OPS(bfloat16)
 REGISTER_KERNEL_BUILDER(Name("CudaTimerStart").Device(DEVICE_GPU).HostMemory("start_event"), TimerStartGpu);
 REGISTER_KERNEL_BUILDER(Name("CudaTimerEnd").Device(DEVICE_GPU).HostMemory("dt").HostMemory("start_event"),
                         TimerEndGpu);

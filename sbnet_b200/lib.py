@@ -11,7 +11,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 # SBNET_B200_LIB selects another build of the same library (e.g. an instrumented one)
 LIB_PATH = os.environ.get("SBNET_B200_LIB") or os.path.join(PKG, "libsbnet_b200.so")
 
-SBNET_F32, SBNET_F16 = 0, 1
+SBNET_F32, SBNET_F16, SBNET_BF16 = 0, 1, 2
 SBNET_SCRATCH_CLEAN = 1
 SBNET_COUNT_POLL = 2
 SBNET_REDUCE_MASK_SCRATCH_INTS = 4

@@ -19,7 +19,7 @@ from . import lib as _lib
 
 ReduceMaskResult = namedtuple("ReduceMask", ["active_block_indices", "bin_counts"])
 
-_DTYPES = {torch.float32: _lib.SBNET_F32, torch.float16: _lib.SBNET_F16}
+_DTYPES = {torch.float32: _lib.SBNET_F32, torch.float16: _lib.SBNET_F16, torch.bfloat16: _lib.SBNET_BF16}
 _scratch: dict = {}
 
 

@@ -8,6 +8,22 @@ import torch
 from sbnet_b200 import ops
 
 
+def to_torch(a: np.ndarray) -> torch.Tensor:
+    """numpy -> torch on the host; bfloat16 (``ml_dtypes``) crosses as its 16-bit pattern."""
+    a = np.ascontiguousarray(a)
+    if a.dtype.name == "bfloat16":
+        return torch.from_numpy(a.view(np.int16)).view(torch.bfloat16)
+    return torch.from_numpy(a)
+
+
+def to_numpy(t: torch.Tensor) -> np.ndarray:
+    t = t.cpu()
+    if t.dtype == torch.bfloat16:
+        import ml_dtypes
+        return t.view(torch.int16).numpy().view(ml_dtypes.bfloat16)
+    return t.numpy()
+
+
 class CudaOps:
     kind = "cuda"
 
@@ -16,7 +32,7 @@ class CudaOps:
         self.guard = guard
 
     def _dev(self, a):
-        return torch.from_numpy(np.ascontiguousarray(a)).to(self.device)
+        return to_torch(a).to(self.device)
 
     def reduce_mask(self, mask, dynamic_bcount, dynamic_bsize, dynamic_bstride, dynamic_boffset, tol,
                     avgpool=False):
@@ -30,7 +46,7 @@ class CudaOps:
         y = ops.sparse_gather(self._dev(x), torch.from_numpy(np.asarray(bin_counts, dtype=np.int32)),
                               self._dev(np.asarray(active_block_indices, dtype=np.int16)),
                               dynamic_bsize, dynamic_bstride, dynamic_boffset, transpose=transpose)
-        return y.cpu().numpy()
+        return to_numpy(y)
 
     def _scatter(self, fn, x, bin_counts, active_block_indices, ybase, dynamic_bsize,
                  dynamic_bstride, dynamic_boffset, add, atomic, transpose):
@@ -40,7 +56,7 @@ class CudaOps:
                self._dev(np.asarray(active_block_indices, dtype=np.int16)), self._dev(yb),
                dynamic_bsize, dynamic_bstride, dynamic_boffset, add=add, atomic=atomic,
                transpose=transpose)
-        return y.cpu().numpy()
+        return to_numpy(y)
 
     def sparse_scatter(self, x, bin_counts, active_block_indices, ybase, dynamic_bsize,
                        dynamic_bstride, dynamic_boffset, add, atomic=False, transpose=False):

@@ -186,3 +186,34 @@ def test_reference_cuda_kernel_library_exports_its_entry_points():
     lib = refgpu._load()
     for name in ("refgpu_sparse_gather", "refgpu_sparse_scatter", "refgpu_reduce_mask"):
         assert getattr(lib, name) is not None
+
+
+def test_bf16_restatement_matches_compiled_reference(oracle_port, oracle_ref):
+    """bfloat16 instantiations of both checkers agree bit for bit, and one add equals a float
+    addition rounded to nearest even (checked against torch's CPU bfloat16 add)."""
+    ml_dtypes = pytest.importorskip("ml_dtypes")
+    import torch
+    from sbnet_b200 import configs as cfg
+    bf = ml_dtypes.bfloat16
+    oracle_ref.set_threads(1)
+    N, H, W, C = 2, 40, 40, 24
+    g = cfg.geom_for(H, W, (6, 6), (4, 4), (-1, -1))
+    idx, cnt = cfg.random_block_list(N, g.bcount, 0.6, seed=1)
+    x = cfg.normal((N, H, W, C), 1, bf)
+    for tr in (False, True):
+        a = oracle_port.sparse_gather(x, cnt, idx, g.bsize, g.bstride, g.boffset, transpose=tr)
+        b = oracle_ref.sparse_gather(x, cnt, idx, g.bsize, g.bstride, g.boffset, transpose=tr)
+        np.testing.assert_array_equal(a.view(np.uint16), b.view(np.uint16))
+        stack, base = cfg.normal(a.shape, 2, bf), cfg.normal((N, H, W, C), 3, bf)
+        ya = oracle_port.sparse_scatter_var(stack, cnt, idx, base.copy(), g.bsize, g.bstride, g.boffset,
+                                            add=True, atomic=True, transpose=tr)
+        yb = oracle_ref.sparse_scatter_var(stack, cnt, idx, base.copy(), g.bsize, g.bstride, g.boffset,
+                                           add=True, atomic=True, transpose=tr)
+        np.testing.assert_array_equal(ya.view(np.uint16), yb.view(np.uint16))
+    a = cfg.normal((50000,), 5, bf)
+    b = (cfg.normal((50000,), 6, np.float32) * 1e-2).astype(bf)
+    ta = torch.from_numpy(a.view(np.int16)).view(torch.bfloat16)
+    tb = torch.from_numpy(b.view(np.int16)).view(torch.bfloat16)
+    y = oracle_port.sparse_scatter_var(b.reshape(1, 1, 1, -1), np.array([1], np.int32), np.zeros((1, 3), np.int16),
+                                       a.reshape(1, 1, 1, -1).copy(), (1, 1), (1, 1), (0, 0), add=True)
+    np.testing.assert_array_equal(y.view(np.int16).reshape(-1), (ta + tb).view(torch.int16).numpy())

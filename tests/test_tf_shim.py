@@ -5,7 +5,7 @@ with a driver (tests/tf_stub/run_shim.cc):
 * CPU: the ops and GPU kernels it registers are compared with the registrations extracted from the
   reference's own sources (tests/golden/tf_registrations.json, made by make_tf_registrations.py) --
   names, attrs with defaults, inputs, outputs and host-memory placement must be identical; the only
-  difference allowed is `half` added to the element types of gather / scatter.
+  difference allowed is `half` and `bfloat16` added to the element types of gather / scatter.
 * GPU: every OpKernel::Compute is executed (ReduceMask -> SparseGather -> SparseScatter /
   SparseScatterVar, both layouts, timers, InvalidArgument paths) and checked against the CPU checker.
 """
@@ -46,7 +46,7 @@ def test_registrations_match_the_reference(run_shim):
         attrs = list(r["attrs"])
         if name in ("SparseGather", "SparseScatter", "SparseScatterVar"):
             assert attrs[0] == "T: {float}"
-            attrs[0] = "T: {float, half}"        # the one deliberate extension
+            attrs[0] = "T: {float, half, bfloat16}"        # the one deliberate extension
         assert ours[name]["attrs"] == attrs
         assert ours[name]["inputs"] == r["inputs"]
         assert ours[name]["outputs"] == r["outputs"]
@@ -54,10 +54,10 @@ def test_registrations_match_the_reference(run_shim):
         assert kernels and all(k["device"] == "GPU" for k in kernels)
         for k in kernels:
             assert sorted(k["host_memory"]) == r["gpu_host_memory"]
-    # float and half kernels for the block ops, float only for ReduceMask
+    # float, half and bfloat16 kernels for the block ops (stand-in type codes 0, 1, 5), float only for ReduceMask
     types = {n: sorted(k["type"] for k in dump["kernels"] if k["op"] == n) for n in ours}
-    assert types["ReduceMask"] == [0] and types["SparseGather"] == [0, 1]
-    assert types["SparseScatter"] == [0, 1] and types["SparseScatterVar"] == [0, 1]
+    assert types["ReduceMask"] == [0] and types["SparseGather"] == [0, 1, 5]
+    assert types["SparseScatter"] == [0, 1, 5] and types["SparseScatterVar"] == [0, 1, 5]
 
 
 @pytest.mark.gpu

@@ -27,11 +27,16 @@ namespace tensorflow {
 typedef int16_t int16;
 typedef int32_t int32;
 typedef long long int64;
-enum DataType { DT_FLOAT, DT_HALF, DT_INT16, DT_INT32, DT_INT64 };
-inline size_t DataTypeSize(DataType t) { return t == DT_FLOAT ? 4 : t == DT_HALF ? 2 : t == DT_INT16 ? 2 : t == DT_INT32 ? 4 : 8; }
+struct bfloat16 { uint16_t x; };
+enum DataType { DT_FLOAT, DT_HALF, DT_INT16, DT_INT32, DT_INT64, DT_BFLOAT16 };
+inline size_t DataTypeSize(DataType t)
+{
+    return t == DT_FLOAT ? 4 : (t == DT_HALF || t == DT_BFLOAT16 || t == DT_INT16) ? 2 : t == DT_INT32 ? 4 : 8;
+}
 template <typename T> struct DataTypeOf;
 template <> struct DataTypeOf<float> { static const DataType v = DT_FLOAT; };
 template <> struct DataTypeOf<Eigen::half> { static const DataType v = DT_HALF; };
+template <> struct DataTypeOf<bfloat16> { static const DataType v = DT_BFLOAT16; };
 template <> struct DataTypeOf<int16> { static const DataType v = DT_INT16; };
 template <> struct DataTypeOf<int32> { static const DataType v = DT_INT32; };
 template <> struct DataTypeOf<int64> { static const DataType v = DT_INT64; };
