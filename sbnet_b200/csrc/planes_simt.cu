@@ -1,25 +1,29 @@
 // Transposed ([nB,C,R,S]) gather and scatter, one short CTA per tile (sm_100a).
 //
-// Default implementation of the plane-layout ops for pixels of a multiple of 16 bytes (blocks of
-// more than 384 pixels are cut into pixel chunks, which for fp16 needs an even pixel count; small
-// blocks share a tile); other shapes run the general kernel of gather_scatter.cu.  Semantics follow the reference CPU functors (sbnet_ops/sparse_gather.cc:61-132,
-// transposed branches).  On B200 a grid of many short CTAs streams measurably faster than a resident
-// grid looping over the same tiles, so with a host-side block count every work item gets its own
-// CTA.  A work item is one active block x one 128-byte channel chunk (the last chunk of a pixel may
-// be narrower): a tile of P = R*S pixels x up to 128 bytes, staged ONCE in shared memory.
+// Default implementation of the plane-layout ops for pixels of a multiple of 16 bytes; other shapes
+// run the general kernel of gather_scatter.cu.  Semantics follow the reference CPU functors
+// (sbnet_ops/sparse_gather.cc:61-132, transposed branches).  On B200 a grid of many short CTAs
+// streams measurably faster than a resident grid looping over the same tiles, so with a host-side
+// block count every work item gets its own CTA.  A work item is one active block x one 128-byte
+// channel chunk (the last chunk of a pixel may be narrower): a tile of P = R*S pixels x up to 128
+// bytes, staged ONCE in shared memory (48 KB = 384 pixels).  Blocks of more than 384 pixels are cut
+// into pixel chunks; blocks of at most 192 pixels share a tile with their neighbours in the list.
 //
 //  gather : every thread issues all of its 16-byte image loads (out-of-image pixels become zeros),
 //           stores them to the tile in [pixel][128 B] order with the 16-byte groups XOR-swizzled by
 //           the pixel index; each thread then reads its share back as 16-byte channel groups, the
-//           CTA synchronises, and the same threads write words of one channel (1 fp32 pixel / 2 fp16
-//           pixels, regrouped with prmt) in [channel][pixel] order into the same buffer (in-place
-//           transpose through registers).  The tile leaves as ONE bulk store (TMA engine): a
-//           chunk's channel planes are contiguous in the stack.
+//           CTA synchronises, and the same threads write words of one channel (1 fp32 pixel / 2
+//           16-bit pixels, regrouped with prmt) in [channel][pixel] order into the same buffer
+//           (in-place transpose through registers).  The tile leaves as ONE bulk store (TMA engine):
+//           a chunk's channel planes are contiguous in the stack.
 //  scatter: the tile (contiguous in the stack) is copied in, swizzled so that eight neighbouring
 //           lanes can own the eight 16-byte groups of one pixel; words are regrouped into 16-byte
 //           channel groups and written / added / reduced into the image, whole 128-byte lines per
 //           warp instruction, with a per-pixel in-range test.  With a device-side block count the
 //           same kernel runs as one resident wave striding over the items.
+//
+// Element types: float, __half and (accumulating scatter only) __nv_bfloat16; 16-bit gathers and
+// overwrites of any type run the __half instantiations, which only move bits.
 #include <stdlib.h>
 
 #include <algorithm>
@@ -43,10 +47,10 @@ struct SimtPlan {
     int rowsAligned;   // every plane row of every pixel chunk starts and ends on a 16-byte boundary
     FastDiv blockW;    // S
     FastDiv unitsPerRow; // copy-in units (GW words each) per channel plane (swizzled scatter only)
-    int pitchWords;    // tile row pitch of the swizzled scatter: units rounded up to 32
+    int pitchWords;    // tile row pitch of the swizzled scatter: the tile's words per row rounded up to 32
     int groups;        // 16-byte channel groups per pixel (C*sizeof(T)/16); the last chunk may hold fewer than 8
     int pixels;        // P
-    int units;         // words per channel plane: P (fp32) or P/2 (fp16)
+    int units;         // words per channel plane: P (fp32) or P/2 rounded up (16-bit types)
     // several small blocks per work item (kTileMulti)
     int blocksPerItem; // blocks sharing one tile
     FastDiv pixelsDiv; // P

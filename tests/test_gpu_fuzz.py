@@ -70,3 +70,69 @@ def test_random_geometry(cuda_ops, oracle_port, seed):
             o = cuda_ops.sparse_scatter_var(stack, cnt, idx, base.copy(), bsize, bstride, boffset, add=True,
                                             transpose=transpose)
             np.testing.assert_array_equal(o, e)
+
+
+def _draw_tile(seed):
+    """Shapes the tile CTAs of the transposed layout take: pixels of a multiple of 16 bytes, blocks
+    from one pixel to beyond one tile (pixel chunks), a forced number of blocks per tile."""
+    rng = np.random.default_rng(5000 + seed)
+    N = int(rng.integers(1, 3))
+    H, W = int(rng.integers(8, 90)), int(rng.integers(8, 90))
+    kind = int(rng.integers(0, 3))            # 0 fp32, 1 fp16, 2 bfloat16
+    C = int(rng.choice([4, 8, 12, 32, 36, 64]) if kind == 0 else rng.choice([8, 16, 24, 64, 72, 128, 200]))
+    lo, hi = [(1, 13), (12, 19), (20, 40)][int(rng.integers(0, 3))]   # several per tile / one tile / pixel chunks
+    H, W = max(H, lo), max(W, lo)
+    bsize = (int(rng.integers(lo, min(H, hi) + 1)), int(rng.integers(lo, min(W, hi) + 1)))
+    bstride = (int(rng.integers(max(1, bsize[0] - 2), bsize[0] + 3)), int(rng.integers(max(1, bsize[1] - 2), bsize[1] + 3)))
+    boffset = (int(rng.integers(-bsize[0] + 1, 1)), int(rng.integers(-bsize[1] + 1, 1)))
+    pack = str(rng.choice([1, 2, 5, 1000]))
+    return N, H, W, C, bsize, bstride, boffset, kind, pack
+
+
+@pytest.mark.parametrize("seed", range(60))
+def test_random_tile_shapes(cuda_ops, oracle_port, seed):
+    import os
+    N, H, W, C, bsize, bstride, boffset, kind, pack = _draw_tile(seed)
+    if kind == 2:
+        ml_dtypes = pytest.importorskip("ml_dtypes")
+        dtype, rtol1 = ml_dtypes.bfloat16, 2.0 ** -7
+    else:
+        dtype, rtol1 = (np.float32, 1e-6) if kind == 0 else (np.float16, 1e-3)
+    bits = np.uint32 if kind == 0 else np.uint16
+    g = cfg.geom_for(H, W, bsize, bstride, boffset)
+    idx, cnt = cfg.random_block_list(N, g.bcount, 0.7, seed=seed)
+    nb = int(cnt[0])
+    x = cfg.normal((N, H, W, C), seed, dtype)
+    base = cfg.normal((N, H, W, C), seed + 1, dtype)
+    stack = cfg.normal((nb, C, *bsize), seed + 2, dtype)
+    disjoint = bstride[0] >= bsize[0] and bstride[1] >= bsize[1]
+    cover = -(-bsize[0] // bstride[0]) * -(-bsize[1] // bstride[1])
+    saved = os.environ.get("SBNET_TILE_BLOCKS")
+    os.environ["SBNET_TILE_BLOCKS"] = pack
+    try:
+        exp = oracle_port.sparse_gather(x, cnt, idx, bsize, bstride, boffset, transpose=True)
+        got = cuda_ops.sparse_gather(x, cnt, idx, bsize, bstride, boffset, transpose=True)
+        np.testing.assert_array_equal(got.view(bits), exp.view(bits))
+        e = oracle_port.sparse_scatter_var(exp, cnt, idx, base.copy(), bsize, bstride, boffset, add=False, transpose=True)
+        o = cuda_ops.sparse_scatter_var(exp, cnt, idx, base.copy(), bsize, bstride, boffset, add=False, transpose=True)
+        np.testing.assert_array_equal(o.view(bits), e.view(bits))
+        if disjoint:
+            e = oracle_port.sparse_scatter_var(stack, cnt, idx, base.copy(), bsize, bstride, boffset, add=True,
+                                               transpose=True)
+            o = cuda_ops.sparse_scatter_var(stack, cnt, idx, base.copy(), bsize, bstride, boffset, add=True,
+                                            transpose=True)
+            np.testing.assert_array_equal(o.view(bits), e.view(bits))
+        e = oracle_port.sparse_scatter_var(stack, cnt, idx, base.copy(), bsize, bstride, boffset, add=True, atomic=True,
+                                           transpose=True)
+        o = cuda_ops.sparse_scatter_var(stack, cnt, idx, base.copy(), bsize, bstride, boffset, add=True, atomic=True,
+                                        transpose=True)
+        mag = oracle_port.sparse_scatter_var(np.abs(stack.astype(np.float32)), cnt, idx,
+                                             np.abs(base.astype(np.float32)), bsize, bstride, boffset, add=True,
+                                             atomic=True, transpose=True)
+        err = np.abs(o.astype(np.float64) - e.astype(np.float64)) / np.maximum(mag.astype(np.float64), 1.0)
+        assert err.max() <= rtol1 * (1 + cover), (err.max(), rtol1, cover)
+    finally:
+        if saved is None:
+            os.environ.pop("SBNET_TILE_BLOCKS", None)
+        else:
+            os.environ["SBNET_TILE_BLOCKS"] = saved
