@@ -67,9 +67,10 @@ constexpr int kTileMulti = 2;    // blocks of at most 192 pixels: as many whole 
 // one run per channel plane.
 // kTileMulti: the tile holds the pixels of several consecutive blocks of the list back to back; each
 // block's region is transposed in place on its own and leaves as its own bulk store.
-// ODD (fp16 blocks of an odd pixel count): plane rows are an odd number of halves, so a channel's
-// row starts on a word boundary only for even channels; words of odd channels are written as two
-// halves, and p.units counts a row's words rounded up.
+// ODD (16-bit blocks of an odd pixel count, whole blocks): plane rows are an odd number of halves,
+// so a channel's row starts on a word boundary only for even channels; words of odd channels are
+// written as two halves, and p.units counts a row's words rounded up.  (Pixel chunks of such
+// blocks keep word-aligned tile rows and shift the rows of odd channels on their way out.)
 template <typename T, int SHAPE, bool ODD = false>
 __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gather_simt(const BlockArgs a, const SimtPlan p)
 {
@@ -90,7 +91,7 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
         p.pChunks.divmod(rest, ib, pc);
         p0 = (int)pc * p.chunkPixels;
         P = min(p.chunkPixels, p.pixels - p0);
-        U = P / EPW;
+        U = (P + EPW - 1) / EPW;   // a 16-bit block of an odd pixel count ends in a chunk of an odd count
     } else if constexpr (MB) {
         uint32_t grp;
         p.cChunks.divmod(blockIdx.x, grp, cc);
@@ -231,7 +232,33 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
     if constexpr (PCH) {
         // one run of U words per channel plane, p.pixels elements apart
         const int rows = nG * CPG;
-        if (p.rowsAligned) {
+        if (EPW == 2 && (p.pixels & 1)) {
+            // 16-bit rows of an odd length: the rows of odd channels start on an odd half.  Tile rows
+            // are word aligned, so such a row leaves as its first half, then words made of the high
+            // half of one tile word and the low half of the next, then (even chunk) its last half.
+            unsigned short* dstH = reinterpret_cast<unsigned short*>(dst);
+            const int lane = threadIdx.x & 31;
+            for (int c = threadIdx.x >> 5; c < rows; c += kPsThreads / 32) {
+                unsigned short* row = dstH + (long long)c * p.pixels;
+                const uint32_t trow = tile + (uint32_t)(c * U) * 4u;
+                if ((c & 1) == 0) {
+                    uint32_t* rowW = reinterpret_cast<uint32_t*>(row);
+                    for (int u = lane; u < P / 2; u += 32)
+                        rowW[u] = lds32(trow + (uint32_t)u * 4u);
+                    if ((P & 1) && lane == 0)
+                        row[P - 1] = (unsigned short)lds16(trow + (uint32_t)(P - 1) * 2u);
+                } else {
+                    uint32_t* rowW = reinterpret_cast<uint32_t*>(row + 1);
+                    const int nW = (P - 1) / 2;
+                    if (lane == 0)
+                        row[0] = (unsigned short)lds16(trow);
+                    for (int k = lane; k < nW; k += 32)
+                        rowW[k] = __funnelshift_r(lds32(trow + (uint32_t)k * 4u), lds32(trow + (uint32_t)k * 4u + 4u), 16);
+                    if (((P - 1) & 1) && lane == 0)
+                        row[P - 1] = (unsigned short)lds16(trow + (uint32_t)(P - 1) * 2u);
+                }
+            }
+        } else if (p.rowsAligned) {
             if ((int)threadIdx.x < rows) {
                 bulk_store_1d(dst + (long long)threadIdx.x * p.pixels, tile + threadIdx.x * (uint32_t)U * 4u, (uint32_t)U * 4u);
                 bulk_wait_read<0>();
@@ -564,15 +591,15 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
 }
 
 // Pixels of a multiple of 16 bytes (the last 128-byte chunk may be partial), 16-byte aligned buffers.
-// Blocks of more than 384 pixels run as pixel chunks (fp16: an even pixel count; the scatter then
-// needs plane rows of an even number of words).
+// Blocks of more than 384 pixels run as pixel chunks (the scatter then needs plane rows of an even
+// number of words).
 static bool planes_simt_eligible(const BlockArgs& a, int itemsize)
 {
     const char* off = getenv("SBNET_DISABLE_TMA");
     if (off && off[0] == '1')
         return false;
     const long long P = (long long)a.bSzH * a.bSzW;
-    if (((size_t)a.C * itemsize) % 16 != 0 || P > (1 << 24) || (itemsize == 2 && (P & 1) && P > kPsMaxPixels))
+    if (((size_t)a.C * itemsize) % 16 != 0 || P > (1 << 24))
         return false;
     return ((reinterpret_cast<uintptr_t>(a.image) | reinterpret_cast<uintptr_t>(a.stack)) & 15) == 0;
 }
@@ -677,7 +704,7 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
             SBNET_PS_G(float);
         else if (odd && multi)
             SBNET_PS((planes_gather_simt<__half, kTileMulti, true>));
-        else if (odd)
+        else if (odd && !pch)
             SBNET_PS((planes_gather_simt<__half, kTileSingle, true>));
         else
             SBNET_PS_G(__half);

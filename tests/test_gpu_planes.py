@@ -48,7 +48,9 @@ SHAPES = [
     (np.float32, 2, 80, 70, 48, (27, 22), (20, 17), (-5, -4)),    # 594 pixels, overlapping, partial channel chunk
     (np.float16, 1, 130, 150, 128, (41, 48), (41, 48), (0, 0)),   # 1968 pixels: six chunks of 328
     (np.float16, 2, 140, 130, 40, (64, 64), (61, 59), (-9, -7)),  # 4096 pixels, partial channel chunk
-    (np.float16, 1, 170, 170, 64, (81, 81), (81, 81), (-4, -4)),  # odd pixel count: general kernel
+    (np.float16, 1, 170, 170, 64, (81, 81), (81, 81), (-4, -4)),  # 6561 pixels (odd), fp16: gather chunks shift odd rows
+    (np.float16, 2, 70, 70, 128, (21, 21), (19, 19), (-1, -1)),   # 441 pixels (odd), overlapping: chunks of 224 + 217
+    (np.float16, 1, 80, 70, 40, (25, 19), (25, 19), (-3, -3)),    # 475 pixels (odd), partial channel chunk
     (np.float32, 1, 170, 170, 16, (81, 81), (70, 70), (-4, -4)),  # 6561 pixels (odd), fp32 gather chunks
 ]
 
