@@ -1,5 +1,5 @@
 // sparse_gather / sparse_scatter for sm_100a: the row-layout kernels, the general plane-layout
-// kernel (any block size, stride, offset, channel count, fp32 or fp16), the flat copy, and the
+// kernel (any block size, stride, offset, channel count and element type), the flat copy, and the
 // dispatch between these and the aligned plane-layout kernels of planes_simt.cu / planes_tma.cu.
 //
 // Replaces the reference's blockGatherTiled0/1 and blockScatterTiled0/1 families and their launcher
@@ -18,7 +18,7 @@
 //    so that the image side moves channel runs and the stack side moves runs of consecutive pixels
 //    of one channel plane, both conflict-free.
 // Scatter has three write modes: overwrite, read-add-write (legal only for disjoint blocks) and
-// vector reductions (red.global.add .v4.f32 / .v4.f16x2 and narrower) for overlapping halos.
+// vector reductions (red.global.add .v4.f32 / .v4.f16x2 / .v4.bf16x2 and narrower) for overlapping halos.
 //
 // With the block count on the host every work item gets its own short CTA (measured faster on B200
 // than a resident grid); when the count lives in device memory (written by reduce_mask earlier on
