@@ -201,6 +201,31 @@ def main(args):
         torch.cuda.synchronize()
         ms = a.elapsed_time(b) / 64
         emit(f"reduce_mask_{tag}_back_to_back", ms, ms, nbytes, {"active": nb, "launches": 64})
+    # the op as a C caller sees it: one sbnet_reduce_mask call per mask with preallocated buffers and the
+    # count polled in pinned memory (host wall clock per call, rotating masks; includes ~2 us of ctypes)
+    import ctypes as C
+    import time
+    from . import lib as _lib
+    handle = _lib.load()
+    idx_buf = torch.empty((8 * g.bcount[0] * g.bcount[1], 3), dtype=torch.int16, device=dev)
+    cnt_pin = torch.empty(1, dtype=torch.int32, pin_memory=True)
+    scratch = torch.zeros(_lib.SBNET_REDUCE_MASK_SCRATCH_INTS, dtype=torch.int32, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    for run in c2["runs"]:
+        def call(k):
+            _lib.check(handle.sbnet_reduce_mask(
+                masks[k % 8].data_ptr(), 8, 800, 704, float(run["tol"]), int(run["avgpool"]), g.boffset[0], g.boffset[1],
+                g.bsize[0], g.bsize[1], g.bstride[0], g.bstride[1], g.bcount[0], g.bcount[1], idx_buf.data_ptr(),
+                scratch.data_ptr(), cnt_pin.data_ptr(), _lib.SBNET_SCRATCH_CLEAN | _lib.SBNET_COUNT_POLL, stream))
+        for k in range(16):
+            call(k)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for k in range(200):
+            call(k)
+        dt = (time.perf_counter() - t0) / 200
+        tag = "avg" if run["avgpool"] else "max"
+        emit(f"reduce_mask_{tag}_c_abi_call_with_count", dt * 1e3, dt * 1e3, 18022400, {"active": int(cnt_pin[0]), "calls": 200})
     del masks
 
     # ---- sparse_gather on [8,512,512,128] ----
