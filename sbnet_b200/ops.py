@@ -10,6 +10,7 @@ only; every computation happens in ``libsbnet_b200.so``.
 from __future__ import annotations
 
 import ctypes as C
+import threading
 from collections import namedtuple
 from typing import Sequence
 
@@ -78,6 +79,22 @@ def _count(bin_counts) -> int:
     return int(list(bin_counts)[0]) if not isinstance(bin_counts, int) else int(bin_counts)
 
 
+_pinned_slab: list = [None, 0]
+_pinned_lock = threading.Lock()
+
+
+def _pinned_count() -> torch.Tensor:
+    """A fresh one-element pinned int32 tensor.  Pinned allocations are slow, so slots are handed out
+    from a slab of 1,024; every slot is used once (the caller keeps the returned view), and a slab
+    is released by reference counting when the last of its views is gone."""
+    with _pinned_lock:
+        slab, used = _pinned_slab
+        if slab is None or used >= slab.numel():
+            slab, used = torch.empty(1024, dtype=torch.int32, pin_memory=True), 0
+        _pinned_slab[0], _pinned_slab[1] = slab, used + 1
+    return slab[used:used + 1]
+
+
 def scratch_for(device, stream: int) -> tuple:
     """Per (device, stream) reduce_mask scratch, zero-filled once; later calls pass SCRATCH_CLEAN."""
     key = (device.index if isinstance(device, torch.device) else torch.device(device).index, stream)
@@ -109,7 +126,7 @@ def reduce_mask(mask: torch.Tensor, dynamic_bcount: Sequence[int], dynamic_bsize
     with _on(mask.device):
         stream = _stream(mask.device)
         idx = torch.empty((max(N * bch * bcw, 0), 3), dtype=torch.int16, device=mask.device)
-        counts = torch.empty(1, dtype=torch.int32, pin_memory=True)
+        counts = _pinned_count()
         scratch, flags = scratch_for(mask.device, stream)
         _lib.check(_lib.load().sbnet_reduce_mask(
             mask.data_ptr(), N, H, W, float(tol), int(bool(avgpool)), boh, bow, bsh, bsw, bth, btw,
