@@ -427,7 +427,7 @@ def run_ours(args):
         alg = {"reduce_mask": bytes_mask, "gather": bytes_gather, "scatter": bytes_scatter}
         gbs = {k: alg[k] / (med[k] * 1e-3) / 1e9 for k in med}
         dom = max(("gather", "scatter"), key=lambda k: med[k])
-        kernel_name = {"gather": "planes_gather_simt<__half> (sparse_gather transpose=True)",
+        kernel_name = {"gather": "planes_gather_tma_tile<__half> (sparse_gather transpose=True)",
                        "scatter": "planes_scatter_simt<atomic,__half,4> (sparse_scatter_var add=True transpose=True)"}[dom]
         # DRAM bytes per active block from one ncu capture of each kernel on a smaller case of the same
         # shape (1,641 blocks; profiles/planes_*_c256_d20.txt), scaled by the blocks of this launch

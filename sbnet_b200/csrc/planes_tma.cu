@@ -30,6 +30,8 @@
 #include <cudaTypedefs.h>
 #include <stdlib.h>
 
+#include <algorithm>
+
 #include "async_ptx.cuh"
 #include "common.cuh"
 #include "kernels.h"
@@ -390,6 +392,134 @@ __global__ void __launch_bounds__(kTmaThreads, 1) planes_scatter_tma(const Block
     }
 }
 
+// ---- gather, one short CTA per tile, fed by TMA ---------------------------------------------------
+// The default gather for blocks of at most 384 pixels when the block count is on the host: the tile
+// of planes_simt.cu (one block, or several small blocks sharing the 48 KB), but filled by one tiled
+// TMA load per block issued by one thread (zero fill outside the image included) instead of by
+// plain loads.  That frees the registers and instructions of the load phase -- the 256 threads only
+// transpose -- which is worth about 3 % on one-block tiles (four CTAs per SM for fp32 too) and up
+// to 20 % on shared tiles, where plain loads are issue-bound (two divisions and an index lookup per
+// 16-byte load).  Block b's box lands at region b of the tile; regions are padded to a multiple of 8
+// pixels (1,024 bytes) so that the 128-byte swizzle pattern of every box starts at its own first
+// pixel.  Each region is transposed in place and leaves as its own bulk store.
+struct TmaTilePlan {
+    FastDiv cChunks;    // 128-byte channel chunks per pixel
+    FastDiv unitsDiv;   // units
+    int pixels;         // P
+    int units;          // words per channel plane row: P (fp32) or P/2 (16-bit types, P even)
+    int regionPixels;   // P rounded up to a multiple of 8
+    int blocksPerItem;
+    int groups;         // 16-byte channel groups per pixel; the last chunk may hold fewer than 8
+};
+constexpr int kTileThreads = 256;
+constexpr int kTileBytesMax = 128 * kMaxPixels;
+
+template <typename T>
+__global__ void __launch_bounds__(kTileThreads, 4)
+planes_gather_tma_tile(const __grid_constant__ CUtensorMap imageMap, const BlockArgs a, const TmaTilePlan p)
+{
+    extern __shared__ unsigned char dynSmem[];
+    __shared__ __align__(8) unsigned long long barStorage;
+    __shared__ int abortFlag;
+    constexpr int EPW = 4 / (int)sizeof(T);
+    constexpr int CPG = 16 / (int)sizeof(T);
+    constexpr int kMaxTasks = ((kMaxPixels / EPW + 15) / 16 + 1) / 2;
+    const uint32_t tile = (smem_u32(dynSmem) + 1023u) & ~1023u;
+    const uint32_t bar = smem_u32(&barStorage);
+
+    uint32_t grp, cc;
+    p.cChunks.divmod(blockIdx.x, grp, cc);
+    const uint32_t ib = grp * (uint32_t)p.blocksPerItem;
+    const int nBlk = min(p.blocksPerItem, a.numActive - (int)ib);
+    const int nG = min(8, p.groups - 8 * (int)cc);
+    const uint32_t regionBytes = (uint32_t)p.regionPixels * 128u;
+
+    if (threadIdx.x == 0) {
+        abortFlag = 0;
+        mbar_init(bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        mbar_expect_tx(bar, (uint32_t)nBlk * (uint32_t)p.pixels * 128u);
+        for (int b = 0; b < nBlk; ++b) {
+            const int16_t* ix = a.idx + (size_t)(ib + b) * 3;
+            tma_load_4d(tile + (uint32_t)b * regionBytes, &imageMap, (int)cc * (128 / (int)sizeof(T)),
+                        a.bOffsW + ix[2] * a.bStrW, a.bOffsH + ix[1] * a.bStrH, ix[0], bar);
+        }
+    }
+    // Every warp's lane 0 waits (bounded); a warp that gives up waits once more, again bounded, so
+    // that this CTA's copies are not left in flight over shared memory it has given back.
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) {
+        ok = mbar_wait(bar, 0, &abortFlag) ? 1 : 0;
+        if (!ok) {
+            int again = 0;
+            (void)mbar_wait(bar, 0, &again);
+        }
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (__syncthreads_or(ok == 0))
+        return;
+
+    // ---- tile -> registers (16-byte channel groups), then registers -> tile in [channel][pixel] order
+    const int U = nBlk * p.units;
+    const int nTasks = ((U + 15) >> 4) * 128;
+    uint4 A[kMaxTasks], B[kMaxTasks];
+#pragma unroll
+    for (int q = 0; q < kMaxTasks; ++q) {
+        const int t = threadIdx.x + q * kTileThreads;
+        const int uLocal = t & 15, g16 = t >> 4;
+        const int j = g16 & 7, u = ((g16 >> 3) << 4) + uLocal;
+        if (t < nTasks && u < U && j < nG) {
+            uint32_t b, uIn;
+            p.unitsDiv.divmod((uint32_t)u, b, uIn);
+            const uint32_t region = tile + b * regionBytes;
+            const uint32_t r0 = EPW * uIn;   // pixel inside the block: the swizzle restarts with every region
+            A[q] = lds128(region + r0 * 128u + ((j ^ (r0 & 7u)) << 4));
+            if constexpr (EPW == 2)
+                B[q] = lds128(region + (r0 + 1u) * 128u + ((j ^ ((r0 + 1u) & 7u)) << 4));
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < kMaxTasks; ++q) {
+        const int t = threadIdx.x + q * kTileThreads;
+        const int uLocal = t & 15, g16 = t >> 4;
+        const int j = g16 & 7, u = ((g16 >> 3) << 4) + uLocal;
+        if (t < nTasks && u < U && j < nG) {
+            uint32_t b, uIn;
+            p.unitsDiv.divmod((uint32_t)u, b, uIn);
+            const uint32_t base = tile + b * regionBytes + ((uint32_t)(CPG * j) * p.units + uIn) * 4u;
+            const uint32_t pitch = (uint32_t)p.units * 4u;
+            if constexpr (EPW == 2) {
+                sts32(base + 0u * pitch, __byte_perm(A[q].x, B[q].x, 0x5410));
+                sts32(base + 1u * pitch, __byte_perm(A[q].x, B[q].x, 0x7632));
+                sts32(base + 2u * pitch, __byte_perm(A[q].y, B[q].y, 0x5410));
+                sts32(base + 3u * pitch, __byte_perm(A[q].y, B[q].y, 0x7632));
+                sts32(base + 4u * pitch, __byte_perm(A[q].z, B[q].z, 0x5410));
+                sts32(base + 5u * pitch, __byte_perm(A[q].z, B[q].z, 0x7632));
+                sts32(base + 6u * pitch, __byte_perm(A[q].w, B[q].w, 0x5410));
+                sts32(base + 7u * pitch, __byte_perm(A[q].w, B[q].w, 0x7632));
+            } else {
+                sts32(base + 0u * pitch, A[q].x);
+                sts32(base + 1u * pitch, A[q].y);
+                sts32(base + 2u * pitch, A[q].z);
+                sts32(base + 3u * pitch, A[q].w);
+            }
+        }
+    }
+    fence_async_smem();   // the bulk stores read what the generic proxy just wrote
+    __syncthreads();
+    if ((int)threadIdx.x < nBlk) {   // block b's planes of this chunk: one contiguous run of the stack
+        T* dst = reinterpret_cast<T*>(a.stack) +
+                 ((long long)(ib + threadIdx.x) * a.C + (long long)cc * (128 / (int)sizeof(T))) * p.pixels;
+        bulk_store_1d(dst, tile + threadIdx.x * regionBytes, (uint32_t)(16 * nG * p.pixels));
+        bulk_wait_read<0>();
+    }
+}
+
 // ---- host side ----------------------------------------------------------------------------------
 static PFN_cuTensorMapEncodeTiled encode_fn()
 {
@@ -508,6 +638,57 @@ cudaError_t launch_planes_tma(const BlockArgs& a, int dtype, int mode, cudaStrea
             SBNET_SCATTER_TMA(kScatterAtomic, __half);
     }
 #undef SBNET_SCATTER_TMA
+    *taken = true;
+    return cudaGetLastError();
+}
+
+// Gather with `blocksPerItem` (>= 1) blocks per tile; not taken (the plain-load kernel of
+// planes_simt.cu runs instead) for blocks of more than 384 pixels, 16-bit blocks of an odd pixel
+// count, a block count on the device, or when the driver has no tensor-map encoder.
+cudaError_t launch_gather_tma_tile(const BlockArgs& a, int dtype, int blocksPerItem, cudaStream_t stream, bool* taken)
+{
+    *taken = false;
+    const int itemsize = dtype == 0 ? 4 : 2;
+    const int P = a.bSzH * a.bSzW;
+    if (a.num_active_dev != nullptr || (itemsize == 2 && (P & 1)) || a.bSzH > 256 || a.bSzW > 256 ||
+        ((size_t)a.C * itemsize) % 16 != 0)
+        return cudaSuccess;
+    TmaTilePlan p;
+    p.pixels = P;
+    p.units = itemsize == 4 ? P : P / 2;
+    p.regionPixels = (P + 7) & ~7;
+    p.blocksPerItem = std::min(blocksPerItem, kMaxPixels / p.regionPixels);
+    if (p.blocksPerItem < 1)
+        return cudaSuccess;
+    p.groups = (int)((size_t)a.C * itemsize / 16);
+    p.cChunks = FastDiv((uint32_t)((p.groups + 7) / 8));
+    p.unitsDiv = FastDiv((uint32_t)p.units);
+    PFN_cuTensorMapEncodeTiled enc = encode_fn();
+    if (enc == nullptr)
+        return cudaSuccess;
+    CUtensorMap map;
+    const cuuint64_t dims[4] = {(cuuint64_t)a.C, (cuuint64_t)a.W, (cuuint64_t)a.H, (cuuint64_t)a.N};
+    const cuuint64_t strides[3] = {(cuuint64_t)a.C * itemsize, (cuuint64_t)a.W * a.C * itemsize,
+                                   (cuuint64_t)a.H * a.W * a.C * itemsize};
+    const cuuint32_t box[4] = {(cuuint32_t)(128 / itemsize), (cuuint32_t)a.bSzW, (cuuint32_t)a.bSzH, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    if (enc(&map, itemsize == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, a.image, dims,
+            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaSuccess;
+    const long long nItems = (long long)((a.numActive + p.blocksPerItem - 1) / p.blocksPerItem) * p.cChunks.div;
+    if (nItems > 0x7fffffffll)
+        return cudaSuccess;
+    const int smem = kTileBytesMax + 1024;
+    if (dtype == 0) {
+        if (cudaError_t e = set_smem((const void*)planes_gather_tma_tile<float>, smem))
+            return e;
+        planes_gather_tma_tile<float><<<(unsigned)nItems, kTileThreads, smem, stream>>>(map, a, p);
+    } else {
+        if (cudaError_t e = set_smem((const void*)planes_gather_tma_tile<__half>, smem))
+            return e;
+        planes_gather_tma_tile<__half><<<(unsigned)nItems, kTileThreads, smem, stream>>>(map, a, p);
+    }
     *taken = true;
     return cudaGetLastError();
 }

@@ -59,9 +59,11 @@ def _ids():
     return [f"{np.dtype(s[0]).name}_C{s[4]}_b{s[5][0]}x{s[5][1]}_s{s[6][0]}x{s[6][1]}" for s in SHAPES]
 
 
-@pytest.fixture(params=["tile_ctas", "tma_pipeline", "general"])
+@pytest.fixture(params=["default", "tile_ctas", "tma_pipeline", "general"])
 def tma_off(request):
-    """Selects which of the three plane-layout implementations takes the call."""
+    """Selects which plane-layout implementation takes the call: the default dispatch (tile CTAs,
+    gathers fed by TMA), the tile CTAs with plain loads, the persistent TMA pipeline, or the general
+    kernel."""
     saved = {k: os.environ.get(k) for k in ("SBNET_DISABLE_TMA", "SBNET_PLANES")}
     os.environ.pop("SBNET_DISABLE_TMA", None)
     os.environ.pop("SBNET_PLANES", None)
@@ -69,7 +71,7 @@ def tma_off(request):
         os.environ["SBNET_DISABLE_TMA"] = "1"
     elif request.param == "tma_pipeline":
         os.environ["SBNET_PLANES"] = "tma"
-    else:
+    elif request.param == "tile_ctas":
         os.environ["SBNET_PLANES"] = "tile"
     yield request.param
     for k, v in saved.items():
@@ -124,16 +126,6 @@ def _run_shape(cuda_ops, oracle_port, shape):
                                          bsize, bstride, boffset, add=True, atomic=True, transpose=True)
     err = np.abs(o.astype(np.float64) - e.astype(np.float64)) / np.maximum(mag.astype(np.float64), 1.0)
     assert err.max() <= rtol, err.max()
-
-
-def test_no_bounded_wait_gave_up(cuda_ops):
-    import ctypes as C
-    import torch
-    from sbnet_b200 import lib
-    torch.cuda.synchronize()
-    n = C.c_uint(99)
-    lib.check(lib.load().sbnet_wait_timeouts(C.byref(n)))
-    assert n.value == 0
 
 
 @pytest.mark.parametrize("dtype", [np.float32, np.float16])
@@ -192,13 +184,19 @@ SMALL_BLOCKS = [
 ]
 
 
+@pytest.mark.parametrize("gather_loads", ["plain", "tma"])
 @pytest.mark.parametrize("blocks_per_tile", ["2", "7", "1000"])
 @pytest.mark.parametrize("shape", SMALL_BLOCKS,
                          ids=[f"{np.dtype(s[0]).name}_C{s[4]}_b{s[5][0]}x{s[5][1]}" for s in SMALL_BLOCKS])
-def test_several_blocks_per_tile(cuda_ops, oracle_port, shape, blocks_per_tile):
+def test_several_blocks_per_tile(cuda_ops, oracle_port, shape, blocks_per_tile, gather_loads):
+    """``plain``: the plain-load kernels of the tile CTAs; ``tma``: the default dispatch, whose gather
+    feeds the shared tile with one TMA load per block where it can."""
     saved = {k: os.environ.get(k) for k in ("SBNET_TILE_BLOCKS", "SBNET_PLANES", "SBNET_DISABLE_TMA")}
     os.environ["SBNET_TILE_BLOCKS"] = blocks_per_tile
-    os.environ["SBNET_PLANES"] = "tile"
+    if gather_loads == "plain":
+        os.environ["SBNET_PLANES"] = "tile"
+    else:
+        os.environ.pop("SBNET_PLANES", None)
     os.environ.pop("SBNET_DISABLE_TMA", None)
     try:
         _run_shape(cuda_ops, oracle_port, shape)
@@ -234,3 +232,13 @@ def test_several_blocks_per_tile_chosen_by_launch_size(cuda_ops, oracle_port):
     exp = oracle_port.sparse_scatter_var(stack[:nb].cpu().numpy(), cnt_h, idx_h, base.cpu().numpy(), bsize, bstride,
                                          boffset, add=True, transpose=True)
     np.testing.assert_array_equal(y2.cpu().numpy(), exp)
+
+
+def test_no_bounded_wait_gave_up(cuda_ops):
+    import ctypes as C
+    import torch
+    from sbnet_b200 import lib
+    torch.cuda.synchronize()
+    n = C.c_uint(99)
+    lib.check(lib.load().sbnet_wait_timeouts(C.byref(n)))
+    assert n.value == 0
