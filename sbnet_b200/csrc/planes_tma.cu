@@ -414,10 +414,14 @@ struct TmaTilePlan {
 constexpr int kTileThreads = 256;
 constexpr int kTileBytesMax = 128 * kMaxPixels;
 
-template <typename T>
+// ODD (16-bit blocks of an odd pixel count): plane rows are an odd number of halves, so a channel's
+// row starts on a word boundary only for even channels; words of odd channels are written as two
+// halves, and p.units counts a row's words rounded up.
+template <typename T, bool ODD = false>
 __global__ void __launch_bounds__(kTileThreads, 4)
 planes_gather_tma_tile(const __grid_constant__ CUtensorMap imageMap, const BlockArgs a, const TmaTilePlan p)
 {
+    static_assert(!ODD || sizeof(T) == 2, "odd rows of halves: 16-bit types only");
     extern __shared__ unsigned char dynSmem[];
     __shared__ __align__(8) unsigned long long barStorage;
     __shared__ int abortFlag;
@@ -478,8 +482,11 @@ planes_gather_tma_tile(const __grid_constant__ CUtensorMap imageMap, const Block
             const uint32_t region = tile + b * regionBytes;
             const uint32_t r0 = EPW * uIn;   // pixel inside the block: the swizzle restarts with every region
             A[q] = lds128(region + r0 * 128u + ((j ^ (r0 & 7u)) << 4));
-            if constexpr (EPW == 2)
-                B[q] = lds128(region + (r0 + 1u) * 128u + ((j ^ ((r0 + 1u) & 7u)) << 4));
+            if constexpr (EPW == 2) {
+                B[q] = make_uint4(0, 0, 0, 0);
+                if (!ODD || (int)r0 + 1 < p.pixels)   // an odd row's last word holds one pixel
+                    B[q] = lds128(region + (r0 + 1u) * 128u + ((j ^ ((r0 + 1u) & 7u)) << 4));
+            }
         }
     }
     __syncthreads();
@@ -493,7 +500,26 @@ planes_gather_tma_tile(const __grid_constant__ CUtensorMap imageMap, const Block
             p.unitsDiv.divmod((uint32_t)u, b, uIn);
             const uint32_t base = tile + b * regionBytes + ((uint32_t)(CPG * j) * p.units + uIn) * 4u;
             const uint32_t pitch = (uint32_t)p.units * 4u;
-            if constexpr (EPW == 2) {
+            if constexpr (ODD) {
+                const uint32_t region = tile + b * regionBytes;
+                const bool second = (int)(2u * uIn) + 1 < p.pixels;
+                const uint32_t wd[8] = {__byte_perm(A[q].x, B[q].x, 0x5410), __byte_perm(A[q].x, B[q].x, 0x7632),
+                                        __byte_perm(A[q].y, B[q].y, 0x5410), __byte_perm(A[q].y, B[q].y, 0x7632),
+                                        __byte_perm(A[q].z, B[q].z, 0x5410), __byte_perm(A[q].z, B[q].z, 0x7632),
+                                        __byte_perm(A[q].w, B[q].w, 0x5410), __byte_perm(A[q].w, B[q].w, 0x7632)};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    // half index of (channel 8j+i, pixel 2*uIn): even exactly for even channels
+                    const uint32_t at = region + ((uint32_t)(CPG * j + i) * (uint32_t)p.pixels + 2u * uIn) * 2u;
+                    if ((i & 1) == 0 && second) {
+                        sts32(at, wd[i]);
+                    } else {
+                        sts16(at, wd[i] & 0xffffu);
+                        if (second)
+                            sts16(at + 2u, wd[i] >> 16);
+                    }
+                }
+            } else if constexpr (EPW == 2) {
                 sts32(base + 0u * pitch, __byte_perm(A[q].x, B[q].x, 0x5410));
                 sts32(base + 1u * pitch, __byte_perm(A[q].x, B[q].x, 0x7632));
                 sts32(base + 2u * pitch, __byte_perm(A[q].y, B[q].y, 0x5410));
@@ -643,21 +669,22 @@ cudaError_t launch_planes_tma(const BlockArgs& a, int dtype, int mode, cudaStrea
 }
 
 // Gather with `blocksPerItem` (>= 1) blocks per tile; not taken (the plain-load kernel of
-// planes_simt.cu runs instead) for blocks of more than 384 pixels, 16-bit blocks of an odd pixel
-// count, a block count on the device, or when the driver has no tensor-map encoder.
+// planes_simt.cu runs instead) for blocks of more than 384 pixels, a block count on the device, or
+// when the driver has no tensor-map encoder.
 cudaError_t launch_gather_tma_tile(const BlockArgs& a, int dtype, int blocksPerItem, cudaStream_t stream, bool* taken)
 {
     *taken = false;
     const int itemsize = dtype == 0 ? 4 : 2;
     const int P = a.bSzH * a.bSzW;
-    if (a.num_active_dev != nullptr || (itemsize == 2 && (P & 1)) || a.bSzH > 256 || a.bSzW > 256 ||
-        ((size_t)a.C * itemsize) % 16 != 0)
+    if (a.num_active_dev != nullptr || a.bSzH > 256 || a.bSzW > 256 || ((size_t)a.C * itemsize) % 16 != 0)
         return cudaSuccess;
+    const bool odd = itemsize == 2 && (P & 1);
     TmaTilePlan p;
     p.pixels = P;
-    p.units = itemsize == 4 ? P : P / 2;
+    p.units = itemsize == 4 ? P : (P + 1) / 2;
     p.regionPixels = (P + 7) & ~7;
-    p.blocksPerItem = std::min(blocksPerItem, kMaxPixels / p.regionPixels);
+    // what fits: 384 pixels in padded regions, and 384/EPW words per tile row (odd rows round up)
+    p.blocksPerItem = std::min(blocksPerItem, std::min(kMaxPixels / p.regionPixels, (kMaxPixels * itemsize / 4) / p.units));
     if (p.blocksPerItem < 1)
         return cudaSuccess;
     p.groups = (int)((size_t)a.C * itemsize / 16);
@@ -684,6 +711,10 @@ cudaError_t launch_gather_tma_tile(const BlockArgs& a, int dtype, int blocksPerI
         if (cudaError_t e = set_smem((const void*)planes_gather_tma_tile<float>, smem))
             return e;
         planes_gather_tma_tile<float><<<(unsigned)nItems, kTileThreads, smem, stream>>>(map, a, p);
+    } else if (odd) {
+        if (cudaError_t e = set_smem((const void*)planes_gather_tma_tile<__half, true>, smem))
+            return e;
+        planes_gather_tma_tile<__half, true><<<(unsigned)nItems, kTileThreads, smem, stream>>>(map, a, p);
     } else {
         if (cudaError_t e = set_smem((const void*)planes_gather_tma_tile<__half>, smem))
             return e;
