@@ -23,6 +23,7 @@ cudaError_t launch_planes_tma(const BlockArgs& a, int dtype, int mode, cudaStrea
 
 // Same shapes as launch_planes_tma, one short CTA per tile; host-side block count only.
 cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStream_t stream, bool* taken);
+cudaError_t launch_gather_tma_rows(const BlockArgs& a, int dtype, cudaStream_t stream, bool* taken);
 cudaError_t launch_gather_tma_tile(const BlockArgs& a, int dtype, int blocksPerItem, cudaStream_t stream, bool* taken);
 bool planes_tma_eligible(const BlockArgs& a, int itemsize);
 

@@ -655,10 +655,11 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
     // Gathers of at most 384 pixels per block are fed by TMA where possible (planes_tma.cu: same tile,
     // one TMA load per block instead of plain loads; measured +3 % on one-block tiles, up to +20 % on
     // shared tiles).  SBNET_PLANES=tile keeps the plain-load kernel (A/B measurements, tests).
-    if (mode == kGather && !pch) {
+    if (mode == kGather) {
         const char* force = getenv("SBNET_PLANES");
         if (!(force && force[0] == 't' && force[1] == 'i')) {
-            if (cudaError_t e = launch_gather_tma_tile(a, dtype, p.blocksPerItem, stream, taken))
+            if (cudaError_t e = pch ? launch_gather_tma_rows(a, dtype, stream, taken)
+                                    : launch_gather_tma_tile(a, dtype, p.blocksPerItem, stream, taken))
                 return e;
             if (*taken)
                 return cudaSuccess;

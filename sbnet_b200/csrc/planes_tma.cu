@@ -414,6 +414,23 @@ struct TmaTilePlan {
 constexpr int kTileThreads = 256;
 constexpr int kTileBytesMax = 128 * kMaxPixels;
 
+// Whole CTA: waits for the tile's TMA loads.  Every warp's lane 0 waits (bounded); a warp that
+// gives up waits once more, again bounded, so that this CTA's copies are not left in flight over
+// shared memory it has given back.  false (for every thread) if any warp gave up.
+__device__ __forceinline__ bool tile_arrived(uint32_t bar, int* abortFlag)
+{
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) {
+        ok = mbar_wait(bar, 0, abortFlag) ? 1 : 0;
+        if (!ok) {
+            int again = 0;
+            (void)mbar_wait(bar, 0, &again);
+        }
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    return __syncthreads_or(ok == 0) == 0;
+}
+
 // ODD (16-bit blocks of an odd pixel count): plane rows are an odd number of halves, so a channel's
 // row starts on a word boundary only for even channels; words of odd channels are written as two
 // halves, and p.units counts a row's words rounded up.
@@ -453,18 +470,7 @@ planes_gather_tma_tile(const __grid_constant__ CUtensorMap imageMap, const Block
                         a.bOffsW + ix[2] * a.bStrW, a.bOffsH + ix[1] * a.bStrH, ix[0], bar);
         }
     }
-    // Every warp's lane 0 waits (bounded); a warp that gives up waits once more, again bounded, so
-    // that this CTA's copies are not left in flight over shared memory it has given back.
-    int ok = 1;
-    if ((threadIdx.x & 31) == 0) {
-        ok = mbar_wait(bar, 0, &abortFlag) ? 1 : 0;
-        if (!ok) {
-            int again = 0;
-            (void)mbar_wait(bar, 0, &again);
-        }
-    }
-    ok = __shfl_sync(0xffffffffu, ok, 0);
-    if (__syncthreads_or(ok == 0))
+    if (!tile_arrived(bar, &abortFlag))
         return;
 
     // ---- tile -> registers (16-byte channel groups), then registers -> tile in [channel][pixel] order
@@ -543,6 +549,165 @@ planes_gather_tma_tile(const __grid_constant__ CUtensorMap imageMap, const Block
                  ((long long)(ib + threadIdx.x) * a.C + (long long)cc * (128 / (int)sizeof(T))) * p.pixels;
         bulk_store_1d(dst, tile + threadIdx.x * regionBytes, (uint32_t)(16 * nG * p.pixels));
         bulk_wait_read<0>();
+    }
+}
+
+// ---- gather of blocks of more than 384 pixels: row chunks fed by TMA -----------------------------
+// A work item is (block, chunk of whole block rows, channel chunk): the chunk is a box of the image,
+// so one TMA load fills the tile; two tensor maps, one for full chunks and one for the shorter last
+// chunk of a block.  After the in-place transposition the tile holds one word-aligned row per channel
+// plane, which leaves as a run of the stack's plane row: one bulk store per plane where runs are
+// 16-byte multiples, else 8- or 4-byte stores, else (16-bit runs that start on an odd half) the first
+// half, words funnel-shifted out of two tile words, and the last half.
+struct TmaRowsPlan {
+    FastDiv cChunks;     // 128-byte channel chunks per pixel
+    FastDiv rChunks;     // row chunks per block
+    int groups;          // 16-byte channel groups per pixel
+    int pixels;          // P = R*S
+    int blockW;          // S
+    int blockH;          // R
+    int chunkRows;       // block rows per chunk; the last chunk of a block holds blockH - (rChunks-1)*chunkRows
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kTileThreads, 4)
+planes_gather_tma_rows(const __grid_constant__ CUtensorMap mapFull, const __grid_constant__ CUtensorMap mapLast,
+                       const BlockArgs a, const TmaRowsPlan p)
+{
+    extern __shared__ unsigned char dynSmem[];
+    __shared__ __align__(8) unsigned long long barStorage;
+    __shared__ int abortFlag;
+    constexpr int EPW = 4 / (int)sizeof(T);
+    constexpr int CPG = 16 / (int)sizeof(T);
+    constexpr int kMaxTasks = ((kMaxPixels / EPW + 15) / 16 + 1) / 2;
+    const uint32_t tile = (smem_u32(dynSmem) + 1023u) & ~1023u;
+    const uint32_t bar = smem_u32(&barStorage);
+
+    uint32_t rest, cc, ib, kc;
+    p.cChunks.divmod(blockIdx.x, rest, cc);
+    p.rChunks.divmod(rest, ib, kc);
+    const bool last = kc + 1 == p.rChunks.div;
+    const int rows = last ? p.blockH - (int)kc * p.chunkRows : p.chunkRows;
+    const int P = rows * p.blockW;            // pixels of this chunk
+    const int p0 = (int)kc * p.chunkRows * p.blockW;
+    const int U = (P + EPW - 1) / EPW;        // words per tile row
+    const int nG = min(8, p.groups - 8 * (int)cc);
+
+    if (threadIdx.x == 0) {
+        abortFlag = 0;
+        mbar_init(bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int16_t* ix = a.idx + (size_t)ib * 3;
+        mbar_expect_tx(bar, (uint32_t)P * 128u);
+        tma_load_4d(tile, last ? &mapLast : &mapFull, (int)cc * (128 / (int)sizeof(T)), a.bOffsW + ix[2] * a.bStrW,
+                    a.bOffsH + ix[1] * a.bStrH + (int)kc * p.chunkRows, ix[0], bar);
+    }
+    if (!tile_arrived(bar, &abortFlag))
+        return;
+
+    // ---- tile -> registers (16-byte channel groups), then registers -> tile in [channel][pixel] order
+    const int nTasks = ((U + 15) >> 4) * 128;
+    uint4 A[kMaxTasks], B[kMaxTasks];
+#pragma unroll
+    for (int q = 0; q < kMaxTasks; ++q) {
+        const int t = threadIdx.x + q * kTileThreads;
+        const int uLocal = t & 15, g16 = t >> 4;
+        const int j = g16 & 7, u = ((g16 >> 3) << 4) + uLocal;
+        if (t < nTasks && u < U && j < nG) {
+            const uint32_t r0 = EPW * u;
+            A[q] = lds128(tile + r0 * 128u + ((j ^ (r0 & 7u)) << 4));
+            if constexpr (EPW == 2) {
+                B[q] = make_uint4(0, 0, 0, 0);
+                if ((int)r0 + 1 < P)   // a chunk of an odd pixel count: the last word holds one pixel
+                    B[q] = lds128(tile + (r0 + 1u) * 128u + ((j ^ ((r0 + 1u) & 7u)) << 4));
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < kMaxTasks; ++q) {
+        const int t = threadIdx.x + q * kTileThreads;
+        const int uLocal = t & 15, g16 = t >> 4;
+        const int j = g16 & 7, u = ((g16 >> 3) << 4) + uLocal;
+        if (t < nTasks && u < U && j < nG) {
+            const uint32_t base = tile + ((uint32_t)(CPG * j) * U + u) * 4u;
+            const uint32_t pitch = (uint32_t)U * 4u;
+            if constexpr (EPW == 2) {
+                sts32(base + 0u * pitch, __byte_perm(A[q].x, B[q].x, 0x5410));
+                sts32(base + 1u * pitch, __byte_perm(A[q].x, B[q].x, 0x7632));
+                sts32(base + 2u * pitch, __byte_perm(A[q].y, B[q].y, 0x5410));
+                sts32(base + 3u * pitch, __byte_perm(A[q].y, B[q].y, 0x7632));
+                sts32(base + 4u * pitch, __byte_perm(A[q].z, B[q].z, 0x5410));
+                sts32(base + 5u * pitch, __byte_perm(A[q].z, B[q].z, 0x7632));
+                sts32(base + 6u * pitch, __byte_perm(A[q].w, B[q].w, 0x5410));
+                sts32(base + 7u * pitch, __byte_perm(A[q].w, B[q].w, 0x7632));
+            } else {
+                sts32(base + 0u * pitch, A[q].x);
+                sts32(base + 1u * pitch, A[q].y);
+                sts32(base + 2u * pitch, A[q].z);
+                sts32(base + 3u * pitch, A[q].w);
+            }
+        }
+    }
+    fence_async_smem();   // bulk stores read what the generic proxy just wrote
+    __syncthreads();
+
+    // ---- tile rows -> runs of the stack's plane rows (p.pixels elements apart, starting at pixel p0)
+    const int planes = nG * CPG;
+    T* dst = reinterpret_cast<T*>(a.stack) + ((long long)ib * a.C + (long long)cc * (128 / (int)sizeof(T))) * p.pixels + p0;
+    const int sz = (int)sizeof(T);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // alignment that every run of this chunk shares (the stack base is 16-byte aligned and a block
+    // starts on a 16-byte boundary, so only the row pitch, the chunk's first pixel and its length count)
+    const int common = (p.pixels * sz) | (p0 * sz) | (P * sz);
+    if ((common & 15) == 0) {
+        if ((int)threadIdx.x < planes) {
+            bulk_store_1d(dst + (long long)threadIdx.x * p.pixels, tile + threadIdx.x * (uint32_t)U * 4u, (uint32_t)(P * sz));
+            bulk_wait_read<0>();
+        }
+    } else if ((common & 7) == 0) {
+        const int U2 = U / 2;
+        for (int c = warp; c < planes; c += kTileThreads / 32) {
+            uint2* row = reinterpret_cast<uint2*>(dst + (long long)c * p.pixels);
+            for (int u = lane; u < U2; u += 32) {
+                uint2 v;
+                asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(tile + (uint32_t)(c * U2 + u) * 8u));
+                row[u] = v;
+            }
+        }
+    } else if ((common & 3) == 0) {
+        for (int c = warp; c < planes; c += kTileThreads / 32) {
+            uint32_t* row = reinterpret_cast<uint32_t*>(dst + (long long)c * p.pixels);
+            for (int u = lane; u < U; u += 32)
+                row[u] = lds32(tile + (uint32_t)(c * U + u) * 4u);
+        }
+    } else if constexpr (EPW == 2) {
+        // 16-bit runs of which some start on an odd half (odd row pitch and / or odd first pixel)
+        unsigned short* dstH = reinterpret_cast<unsigned short*>(dst);
+        for (int c = warp; c < planes; c += kTileThreads / 32) {
+            unsigned short* row = dstH + (long long)c * p.pixels;
+            const uint32_t trow = tile + (uint32_t)(c * U) * 4u;
+            if ((((long long)c * p.pixels + p0) & 1) == 0) {
+                uint32_t* rowW = reinterpret_cast<uint32_t*>(row);
+                for (int u = lane; u < P / 2; u += 32)
+                    rowW[u] = lds32(trow + (uint32_t)u * 4u);
+                if ((P & 1) && lane == 0)
+                    row[P - 1] = (unsigned short)lds16(trow + (uint32_t)(P - 1) * 2u);
+            } else {
+                uint32_t* rowW = reinterpret_cast<uint32_t*>(row + 1);
+                const int nW = (P - 1) / 2;
+                if (lane == 0)
+                    row[0] = (unsigned short)lds16(trow);
+                for (int k = lane; k < nW; k += 32)
+                    rowW[k] = __funnelshift_r(lds32(trow + (uint32_t)k * 4u), lds32(trow + (uint32_t)k * 4u + 4u), 16);
+                if (((P - 1) & 1) && lane == 0)
+                    row[P - 1] = (unsigned short)lds16(trow + (uint32_t)(P - 1) * 2u);
+            }
+        }
     }
 }
 
@@ -719,6 +884,59 @@ cudaError_t launch_gather_tma_tile(const BlockArgs& a, int dtype, int blocksPerI
         if (cudaError_t e = set_smem((const void*)planes_gather_tma_tile<__half>, smem))
             return e;
         planes_gather_tma_tile<__half><<<(unsigned)nItems, kTileThreads, smem, stream>>>(map, a, p);
+    }
+    *taken = true;
+    return cudaGetLastError();
+}
+
+// Gather of blocks of more than 384 pixels by row chunks; not taken (the pixel chunks of
+// planes_simt.cu run instead) for blocks wider than 256 pixels, a block count on the device, or when
+// the driver has no tensor-map encoder.
+cudaError_t launch_gather_tma_rows(const BlockArgs& a, int dtype, cudaStream_t stream, bool* taken)
+{
+    *taken = false;
+    const int itemsize = dtype == 0 ? 4 : 2;
+    if (a.num_active_dev != nullptr || a.bSzW > 256 || ((size_t)a.C * itemsize) % 16 != 0)
+        return cudaSuccess;
+    TmaRowsPlan p;
+    p.blockW = a.bSzW, p.blockH = a.bSzH, p.pixels = a.bSzH * a.bSzW;
+    const int maxRows = std::min(kMaxPixels / a.bSzW, 256);
+    if (maxRows < 1)
+        return cudaSuccess;
+    const int nChunks = (a.bSzH + maxRows - 1) / maxRows;
+    p.chunkRows = (a.bSzH + nChunks - 1) / nChunks;                   // the fewest, nearly equal chunks
+    p.rChunks = FastDiv((uint32_t)((a.bSzH + p.chunkRows - 1) / p.chunkRows));
+    const int lastRows = a.bSzH - ((int)p.rChunks.div - 1) * p.chunkRows;
+    p.groups = (int)((size_t)a.C * itemsize / 16);
+    p.cChunks = FastDiv((uint32_t)((p.groups + 7) / 8));
+    PFN_cuTensorMapEncodeTiled enc = encode_fn();
+    if (enc == nullptr)
+        return cudaSuccess;
+    CUtensorMap maps[2];
+    const cuuint64_t dims[4] = {(cuuint64_t)a.C, (cuuint64_t)a.W, (cuuint64_t)a.H, (cuuint64_t)a.N};
+    const cuuint64_t strides[3] = {(cuuint64_t)a.C * itemsize, (cuuint64_t)a.W * a.C * itemsize,
+                                   (cuuint64_t)a.H * a.W * a.C * itemsize};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    for (int m = 0; m < 2; ++m) {
+        const cuuint32_t box[4] = {(cuuint32_t)(128 / itemsize), (cuuint32_t)a.bSzW,
+                                   (cuuint32_t)(m == 0 ? p.chunkRows : lastRows), 1};
+        if (enc(&maps[m], itemsize == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, a.image,
+                dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaSuccess;
+    }
+    const long long nItems = (long long)a.numActive * p.rChunks.div * p.cChunks.div;
+    if (nItems > 0x7fffffffll)
+        return cudaSuccess;
+    const int smem = kTileBytesMax + 1024;
+    if (dtype == 0) {
+        if (cudaError_t e = set_smem((const void*)planes_gather_tma_rows<float>, smem))
+            return e;
+        planes_gather_tma_rows<float><<<(unsigned)nItems, kTileThreads, smem, stream>>>(maps[0], maps[1], a, p);
+    } else {
+        if (cudaError_t e = set_smem((const void*)planes_gather_tma_rows<__half>, smem))
+            return e;
+        planes_gather_tma_rows<__half><<<(unsigned)nItems, kTileThreads, smem, stream>>>(maps[0], maps[1], a, p);
     }
     *taken = true;
     return cudaGetLastError();
