@@ -771,6 +771,7 @@ def main():
     ap.add_argument("--case", default="gather_f16_t1")
     ap.add_argument("--density", type=float, default=0.2)
     ap.add_argument("--one-channels", type=int, default=None)
+    ap.add_argument("--one-block", default=None, help="--suite one: square block SIZE,STRIDE,OFFSET instead of 18,16,-1")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.suite == "refgpu":

@@ -1,11 +1,14 @@
-// Transposed ([nB,C,R,S]) gather and scatter as TMA pipelines (sm_100a).
+// Transposed ([nB,C,R,S]) gather and scatter through the TMA unit (sm_100a).
 //
-// Persistent-pipeline implementation of the plane-layout ops for C*sizeof(T) a multiple of 128 bytes
-// and blocks of at most 384 pixels.  It serves gather calls whose block count lives in device memory
-// (a resident grid does not need the count at launch) and is the A/B partner of the one-CTA-per-tile
-// kernels of planes_simt.cu, which take the host-count calls.  Semantics are identical (reference:
-// sbnet_ops/sparse_gather.cc:61-132,
-// transposed branches of sbnet_ops/sparse_blocks.cu.h:135-171 and :217-251).
+// Three things live here, all of them users of tiled TMA loads from the NHWC image (semantics as the
+// reference: sbnet_ops/sparse_gather.cc:61-132, transposed branches of
+// sbnet_ops/sparse_blocks.cu.h:135-171 and :217-251):
+//  * planes_gather_tma_tile / planes_gather_tma_rows (further down): the default gather when the
+//    block count is on the host -- one short CTA per tile, the tile filled by TMA;
+//  * planes_gather_tma / planes_scatter_tma (next): a persistent pipeline for C*sizeof(T) a multiple
+//    of 128 bytes and blocks of at most 384 pixels.  It serves gather calls whose block count lives
+//    in device memory (a resident grid does not need the count at launch) and is the A/B partner of
+//    the one-CTA-per-tile kernels.
 //
 // One persistent CTA per SM: a producer warp keeps a ring of shared-memory stages filled through
 // the async proxy, eight consumer warps transpose out of them.  A work item is one active block x

@@ -62,7 +62,7 @@ def emit(name, med_ms, min_ms, nbytes, extra):
 
 
 def one(args):
-    """``bench.py --suite one --case NAME [--density D]``: a few launches of ONE op on a mid-sized
+    """``bench.py --suite one --case NAME [--density D] [--one-channels C] [--one-block SIZE,STRIDE,OFFSET]``: a few launches of ONE op on a mid-sized
     input (larger than L2, well under a GB), for profiler captures.  Prints one JSON line."""
     import torch
     from . import build, ops
@@ -87,6 +87,9 @@ def one(args):
         C = args.one_channels or (128 if kind == "gather" else 64)
         halo = kind == "gather" or mode == "atomic"
         g = cfg.halo_geom(H, W) if halo else cfg.inner_geom(H, W)
+        if getattr(args, "one_block", None):   # --one-block SIZE,STRIDE,OFFSET: square blocks of another geometry
+            b, stride, off = (int(v) for v in args.one_block.split(","))
+            g = cfg.geom_for(H, W, (b, b), (stride, stride), (off, off))
         idx_h, cnt_h = cfg.random_block_list(N, g.bcount, dens, seed=11)
         nb = int(cnt_h[0])
         U = cfg.union_pixels(idx_h, nb, g, N, H, W)
