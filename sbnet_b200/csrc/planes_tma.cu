@@ -732,6 +732,49 @@ static PFN_cuTensorMapEncodeTiled encode_fn()
     return fn;
 }
 
+// Tensor map of the NHWC image for boxes of 128 bytes of channels x boxW x boxH pixels (128-byte
+// swizzle, zero fill outside the image).  Encoding costs a couple of microseconds on the host, and
+// callers tend to come back with the same buffers, so each thread keeps its last few maps.
+// false: no encoder in this driver, or a shape the encoder rejects (the caller falls back).
+static bool image_map(const BlockArgs& a, int itemsize, int boxW, int boxH, CUtensorMap* out)
+{
+    struct Entry {
+        const void* base;
+        int N, H, W, C, itemsize, boxW, boxH;
+        CUtensorMap map;
+    };
+    constexpr int kEntries = 8;
+    thread_local Entry cache[kEntries];
+    thread_local int used = 0, next = 0;
+    for (int i = 0; i < used; ++i) {
+        const Entry& e = cache[i];
+        if (e.base == a.image && e.N == a.N && e.H == a.H && e.W == a.W && e.C == a.C && e.itemsize == itemsize &&
+            e.boxW == boxW && e.boxH == boxH) {
+            *out = e.map;
+            return true;
+        }
+    }
+    PFN_cuTensorMapEncodeTiled enc = encode_fn();
+    if (enc == nullptr)
+        return false;
+    const cuuint64_t dims[4] = {(cuuint64_t)a.C, (cuuint64_t)a.W, (cuuint64_t)a.H, (cuuint64_t)a.N};
+    const cuuint64_t strides[3] = {(cuuint64_t)a.C * itemsize, (cuuint64_t)a.W * a.C * itemsize,
+                                   (cuuint64_t)a.H * a.W * a.C * itemsize};
+    const cuuint32_t box[4] = {(cuuint32_t)(128 / itemsize), (cuuint32_t)boxW, (cuuint32_t)boxH, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    if (enc(out, itemsize == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, a.image, dims,
+            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    Entry& e = cache[next];
+    e.base = a.image, e.N = a.N, e.H = a.H, e.W = a.W, e.C = a.C, e.itemsize = itemsize, e.boxW = boxW, e.boxH = boxH;
+    e.map = *out;
+    next = (next + 1) % kEntries;
+    if (used < kEntries)
+        ++used;
+    return true;
+}
+
 bool planes_tma_eligible(const BlockArgs& a, int itemsize)
 {
     const char* off = getenv("SBNET_DISABLE_TMA");
@@ -748,9 +791,30 @@ bool planes_tma_eligible(const BlockArgs& a, int itemsize)
     return true;
 }
 
+// Raises a kernel's dynamic shared memory limit; remembers the last few (kernel, device, size)
+// triples per thread so that repeated launches skip the runtime call.
 static cudaError_t set_smem(const void* fn, int bytes)
 {
-    return cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    struct Done {
+        const void* fn;
+        int device, bytes;
+    };
+    constexpr int kEntries = 16;
+    thread_local Done done[kEntries];
+    thread_local int used = 0, next = 0;
+    int device = 0;
+    if (cudaError_t e = cudaGetDevice(&device))
+        return e;
+    for (int i = 0; i < used; ++i)
+        if (done[i].fn == fn && done[i].device == device && done[i].bytes >= bytes)
+            return cudaSuccess;
+    if (cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))
+        return e;
+    done[next] = Done{fn, device, bytes};
+    next = (next + 1) % kEntries;
+    if (used < kEntries)
+        ++used;
+    return cudaSuccess;
 }
 
 cudaError_t launch_planes_tma(const BlockArgs& a, int dtype, int mode, cudaStream_t stream, bool* taken)
@@ -773,21 +837,9 @@ cudaError_t launch_planes_tma(const BlockArgs& a, int dtype, int mode, cudaStrea
     const int grid = (int)(nItems < sm_count() ? nItems : sm_count());
 
     if (mode == kGather) {
-        PFN_cuTensorMapEncodeTiled enc = encode_fn();
-        if (enc == nullptr)
-            return cudaSuccess;   // no driver entry point: the general kernel takes the call
         CUtensorMap map;
-        const cuuint64_t dims[4] = {(cuuint64_t)a.C, (cuuint64_t)a.W, (cuuint64_t)a.H, (cuuint64_t)a.N};
-        const cuuint64_t strides[3] = {(cuuint64_t)a.C * itemsize, (cuuint64_t)a.W * a.C * itemsize,
-                                       (cuuint64_t)a.H * a.W * a.C * itemsize};
-        const cuuint32_t box[4] = {(cuuint32_t)(128 / itemsize), (cuuint32_t)a.bSzW, (cuuint32_t)a.bSzH, 1};
-        const cuuint32_t estr[4] = {1, 1, 1, 1};
-        const CUresult rc = enc(&map, itemsize == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16,
-                                4, a.image, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (rc != CUDA_SUCCESS)
-            return cudaSuccess;   // shape the encoder rejects: general kernel
+        if (!image_map(a, itemsize, a.bSzW, a.bSzH, &map))
+            return cudaSuccess;   // no encoder, or a shape it rejects: the general kernel takes the call
         p.outStages = 2;
         p.inStageBytes = (p.tileBytes + 1023) & ~1023;
         p.outStageBytes = (p.tileBytes + 127) & ~127;
@@ -858,18 +910,8 @@ cudaError_t launch_gather_tma_tile(const BlockArgs& a, int dtype, int blocksPerI
     p.groups = (int)((size_t)a.C * itemsize / 16);
     p.cChunks = FastDiv((uint32_t)((p.groups + 7) / 8));
     p.unitsDiv = FastDiv((uint32_t)p.units);
-    PFN_cuTensorMapEncodeTiled enc = encode_fn();
-    if (enc == nullptr)
-        return cudaSuccess;
     CUtensorMap map;
-    const cuuint64_t dims[4] = {(cuuint64_t)a.C, (cuuint64_t)a.W, (cuuint64_t)a.H, (cuuint64_t)a.N};
-    const cuuint64_t strides[3] = {(cuuint64_t)a.C * itemsize, (cuuint64_t)a.W * a.C * itemsize,
-                                   (cuuint64_t)a.H * a.W * a.C * itemsize};
-    const cuuint32_t box[4] = {(cuuint32_t)(128 / itemsize), (cuuint32_t)a.bSzW, (cuuint32_t)a.bSzH, 1};
-    const cuuint32_t estr[4] = {1, 1, 1, 1};
-    if (enc(&map, itemsize == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, a.image, dims,
-            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    if (!image_map(a, itemsize, a.bSzW, a.bSzH, &map))
         return cudaSuccess;
     const long long nItems = (long long)((a.numActive + p.blocksPerItem - 1) / p.blocksPerItem) * p.cChunks.div;
     if (nItems > 0x7fffffffll)
@@ -912,22 +954,9 @@ cudaError_t launch_gather_tma_rows(const BlockArgs& a, int dtype, cudaStream_t s
     const int lastRows = a.bSzH - ((int)p.rChunks.div - 1) * p.chunkRows;
     p.groups = (int)((size_t)a.C * itemsize / 16);
     p.cChunks = FastDiv((uint32_t)((p.groups + 7) / 8));
-    PFN_cuTensorMapEncodeTiled enc = encode_fn();
-    if (enc == nullptr)
-        return cudaSuccess;
     CUtensorMap maps[2];
-    const cuuint64_t dims[4] = {(cuuint64_t)a.C, (cuuint64_t)a.W, (cuuint64_t)a.H, (cuuint64_t)a.N};
-    const cuuint64_t strides[3] = {(cuuint64_t)a.C * itemsize, (cuuint64_t)a.W * a.C * itemsize,
-                                   (cuuint64_t)a.H * a.W * a.C * itemsize};
-    const cuuint32_t estr[4] = {1, 1, 1, 1};
-    for (int m = 0; m < 2; ++m) {
-        const cuuint32_t box[4] = {(cuuint32_t)(128 / itemsize), (cuuint32_t)a.bSzW,
-                                   (cuuint32_t)(m == 0 ? p.chunkRows : lastRows), 1};
-        if (enc(&maps[m], itemsize == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, a.image,
-                dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-            return cudaSuccess;
-    }
+    if (!image_map(a, itemsize, a.bSzW, p.chunkRows, &maps[0]) || !image_map(a, itemsize, a.bSzW, lastRows, &maps[1]))
+        return cudaSuccess;
     const long long nItems = (long long)a.numActive * p.rChunks.div * p.cChunks.div;
     if (nItems > 0x7fffffffll)
         return cudaSuccess;
