@@ -88,6 +88,7 @@ int sbnet_reduce_mask(const float* mask, int N, int H, int W, float tol, int avg
  *
  *   x  [N,H,W,C] NHWC;  y  [numActive,bSzH,bSzW,C], or [numActive,C,bSzH,bSzW] when transpose != 0.
  *   Pixels outside the image read as zero.  numActive == 0 is a successful no-op.
+ *   dtype (here and below): SBNET_F32, SBNET_F16 or SBNET_BF16, the element type of x and y.
  */
 int sbnet_sparse_gather(const void* x, int dtype, int N, int H, int W, int C, void* y,
                         int bOffsH, int bOffsW, int bSzH, int bSzW, int bStrH, int bStrW,
