@@ -303,15 +303,14 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
 // pixel count): dense copy of the chunk, rows of an odd number of halves; words of odd channels are
 // read as two halves.  That layout needs no swizzle: channel groups are 4*P words apart, and with
 // P odd the eight groups land on eight different bank quads.
-// kTileChunked / kTileMulti (GW >= 2 only): as in the gather.  kTileMulti keeps block b's words in
-// columns [b*units, (b+1)*units) of every tile row.
+// kTileChunked (GW >= 2 only) / kTileMulti: as in the gather.  kTileMulti keeps block b's words in
+// columns [b*units, (b+1)*units) of every tile row (GW == 0: the blocks' dense copies back to back).
 template <int MODE, typename T, int GW, int SHAPE>
 __global__ void __launch_bounds__(kPsThreads, MODE == kScatterAdd ? 2 : 3)
 planes_scatter_simt(const BlockArgs a, const SimtPlan p)
 {
     constexpr bool PCH = SHAPE == kTileChunked, MB = SHAPE == kTileMulti;
     static_assert(!PCH || GW > 1, "pixel chunks copy in whole 8- or 16-byte units");
-    static_assert(!MB || GW > 0, "shared tiles need word-aligned rows");
     static_assert(GW != 0 || sizeof(T) == 2, "odd rows of halves: fp16 only");
     constexpr bool ODD = GW == 0;
     __shared__ __align__(128) unsigned char tileRaw[kPsTileBytes];
@@ -375,7 +374,12 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
         own = window(ib);
     // tile pixel slot -> its block's window and the pixel index inside that block
     auto locate = [&](int slot, int& pix) -> Window {
-        if constexpr (MB) {
+        if constexpr (MB && ODD) {   // blocks of an odd pixel count: a block's words do not tile its slots
+            uint32_t b, uIn;
+            p.unitsDiv.divmod((uint32_t)slot >> 1, b, uIn);
+            pix = (int)(2u * uIn);
+            return window(ib + b);
+        } else if constexpr (MB) {
             uint32_t b, q;
             p.pixelsDiv.divmod((uint32_t)slot, b, q);
             pix = (int)q;
@@ -504,8 +508,13 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
                     const int vi = (int)threadIdx.x + (b * kPer + k) * kPsThreads;
                     if (vi < nVec) {
                         uint32_t srcUnit = (uint32_t)vi, w;
-                        if constexpr (SHAPE != kTileSingle)
+                        if constexpr (ODD && MB) {   // dense regions packed back to back: only the source needs the block
+                            uint32_t blk, rest;
+                            runDiv.divmod((uint32_t)vi, blk, rest);
+                            srcUnit = blk * (uint32_t)((long long)a.C * p.pixels * (int)sizeof(T) / 16) + rest;
+                        } else if constexpr (SHAPE != kTileSingle) {
                             place((uint32_t)vi, srcUnit, w);
+                        }
                         v[k] = ld_stream(src + srcUnit);
                     }
                 }
@@ -564,7 +573,13 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 if constexpr (ODD) {   // half index of (channel 8j+i, pixel 2u): even exactly for even channels
-                    const uint32_t at = tile + ((uint32_t)(CPG * j + i) * (uint32_t)p.pixels + 2u * (uint32_t)u) * 2u;
+                    uint32_t region = tile, uIn = (uint32_t)u;
+                    if constexpr (MB) {   // block b's dense copy starts b runs into the tile
+                        uint32_t b;
+                        p.unitsDiv.divmod((uint32_t)u, b, uIn);
+                        region = tile + b * (uint32_t)(16 * nG * p.pixels);
+                    }
+                    const uint32_t at = region + ((uint32_t)(CPG * j + i) * (uint32_t)p.pixels + 2u * uIn) * 2u;
                     w[i] = (i & 1) == 0 ? lds32(at) : (lds16(at) | (lds16(at + 2u) << 16));
                 } else {
                     w[i] = lds32(base + (uint32_t)i * pitch);
@@ -641,7 +656,7 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
     // pixels (measured, of copy bandwidth: 5x5 fp32 0.27 -> 0.80, 8x8 0.62 -> 0.80, 10x10 0.76 -> 0.80,
     // but 12x12 0.88 -> 0.75), so larger blocks keep one block per scatter item.
     p.blocksPerItem = 1;
-    if (!pch && (mode == kGather || (gw >= 1 && P <= 100))) {
+    if (!pch && (mode == kGather || P <= 100)) {
         long long perSm = (long long)a.numActive * p.cChunks.div / ((long long)sm_count() * 4);
         if (const char* force = getenv("SBNET_TILE_BLOCKS"))   // tests: pack up to this many blocks regardless of the launch size
             perSm = atoi(force);
@@ -722,12 +737,20 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
         else
             SBNET_PS_G(__half);
     } else if (odd) {
+#define SBNET_PS_ODD(M, T_)                                           \
+    do {                                                              \
+        if (multi)                                                    \
+            SBNET_PS((planes_scatter_simt<M, T_, 0, kTileMulti>));    \
+        else                                                          \
+            SBNET_PS((planes_scatter_simt<M, T_, 0, kTileSingle>));   \
+    } while (0)
         if (mode == kScatterSet)
-            SBNET_PS((planes_scatter_simt<kScatterSet, __half, 0, kTileSingle>));
+            SBNET_PS_ODD(kScatterSet, __half);
         else if (dtype == 2)
-            SBNET_PS((planes_scatter_simt<kScatterAtomic, __nv_bfloat16, 0, kTileSingle>));
+            SBNET_PS_ODD(kScatterAtomic, __nv_bfloat16);
         else
-            SBNET_PS((planes_scatter_simt<kScatterAtomic, __half, 0, kTileSingle>));
+            SBNET_PS_ODD(kScatterAtomic, __half);
+#undef SBNET_PS_ODD
     } else if (dtype == 2) {
         SBNET_PS_SC(kScatterAtomic, __nv_bfloat16);   // gather / overwrite arrive as fp16
     } else if (dtype == 0) {
