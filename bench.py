@@ -677,6 +677,29 @@ def refgpu_suite(args):
         del stack
     del base
 
+    # ---- small blocks: 8x8 on a 6-pixel pitch and 10x10 on an 8-pixel pitch over [8,512,512,64], 20 % ----
+    x = torch.randn((8, 512, 512, 64), device=dev)
+    for b, stride in ((8, 6), (10, 8)):
+        gs = cfg.geom_for(512, 512, (b, b), (stride, stride), (-1, -1))
+        idx_h, cnt_h = cfg.random_block_list(8, gs.bcount, 0.20, seed=b)
+        nb = int(cnt_h[0])
+        U = cfg.union_pixels(idx_h, nb, gs, 8, 512, 512)
+        idx, cnt = torch.from_numpy(idx_h).to(dev), torch.from_numpy(cnt_h)
+        for tr in (False, True):
+            out = torch.empty((nb, 64, b, b) if tr else (nb, b, b, 64), device=dev)
+            nbytes = cfg.algorithmic_bytes("gather", nB=nb, geom=gs, C=64, itemsize=4, U=U)
+            r, _ = tm.run(lambda: refgpu.sparse_gather(x, nb, idx, gs.bsize, gs.bstride, gs.boffset, tr, out))
+            o, _ = tm.run(lambda: ops.sparse_gather(x, cnt, idx, gs.bsize, gs.bstride, gs.boffset, transpose=tr, out=out))
+            line(f"gather_f32_t{int(tr)}_b{b}_d20", nbytes, r, o, {"blocks": nb})
+            nbytes = cfg.algorithmic_bytes("scatter_add", nB=nb, geom=gs, C=64, itemsize=4, U=U)
+            r, _ = tm.run(lambda: refgpu.sparse_scatter_var(out, nb, idx, x, gs.bsize, gs.bstride, gs.boffset,
+                                                            add=True, atomic=True, transpose=tr))
+            o, _ = tm.run(lambda: ops.sparse_scatter_var(out, cnt, idx, x, gs.bsize, gs.bstride, gs.boffset, add=True,
+                                                         atomic=True, transpose=tr))
+            line(f"scatter_var_f32_t{int(tr)}_atomic_b{b}_d20", nbytes, r, o, {"blocks": nb})
+            del out
+    del x
+
     # ---- the sparse bottleneck's block ops, 8 of the 32 images: [8,400,352,256] ----
     # reference fp32 (its only type) against this library's fp32 and fp16 paths on the same block list
     N, H, W, C = 8, 400, 352, 256
