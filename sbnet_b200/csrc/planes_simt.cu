@@ -625,8 +625,13 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
     const int itemsize = dtype == 0 ? 4 : 2;
     if (!planes_simt_eligible(a, itemsize))
         return cudaSuccess;
-    if (a.num_active_dev != nullptr && mode == kGather)
-        return cudaSuccess;   // device-side count: the gather goes through the TMA pipeline
+    // Gather with the block count on the device: shapes the persistent TMA pipeline takes go there (a
+    // resident grid does not need the count at launch: 449 vs 460 us per step of the sync-free
+    // pipeline benchmark); the others run the TMA-fed tile kernels over a grid sized for the largest
+    // possible count, whose surplus CTAs leave at once.
+    const bool dynGather = a.num_active_dev != nullptr && mode == kGather;
+    if (dynGather && planes_tma_eligible(a, itemsize))
+        return cudaSuccess;
     SimtPlan p;
     const int P = a.bSzH * a.bSzW;
     p.groups = (int)((size_t)a.C * itemsize / 16);
@@ -680,6 +685,8 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
                 return cudaSuccess;
         }
     }
+    if (dynGather)
+        return cudaSuccess;   // the plain-load gather needs the count at launch
     p.pixelsDiv = FastDiv((uint32_t)P);
     p.unitsDiv = FastDiv((uint32_t)std::max(p.units, 1));
     const int lastGroups = p.groups - 8 * ((int)p.cChunks.div - 1);

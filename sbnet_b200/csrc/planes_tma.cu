@@ -454,7 +454,12 @@ planes_gather_tma_tile(const __grid_constant__ CUtensorMap imageMap, const Block
     uint32_t grp, cc;
     p.cChunks.divmod(blockIdx.x, grp, cc);
     const uint32_t ib = grp * (uint32_t)p.blocksPerItem;
-    const int nBlk = min(p.blocksPerItem, a.numActive - (int)ib);
+    // With the block count on the device the grid covers the largest possible count and the CTAs
+    // past the actual one leave at once.
+    const int nActive = device_count(a);
+    if ((int)ib >= nActive)
+        return;
+    const int nBlk = min(p.blocksPerItem, nActive - (int)ib);
     const int nG = min(8, p.groups - 8 * (int)cc);
     const uint32_t regionBytes = (uint32_t)p.regionPixels * 128u;
 
@@ -589,6 +594,8 @@ planes_gather_tma_rows(const __grid_constant__ CUtensorMap mapFull, const __grid
     uint32_t rest, cc, ib, kc;
     p.cChunks.divmod(blockIdx.x, rest, cc);
     p.rChunks.divmod(rest, ib, kc);
+    if ((int)ib >= device_count(a))   // count on the device: the grid covers the largest possible count
+        return;
     const bool last = kc + 1 == p.rChunks.div;
     const int rows = last ? p.blockH - (int)kc * p.chunkRows : p.chunkRows;
     const int P = rows * p.blockW;            // pixels of this chunk
@@ -896,7 +903,7 @@ cudaError_t launch_gather_tma_tile(const BlockArgs& a, int dtype, int blocksPerI
     *taken = false;
     const int itemsize = dtype == 0 ? 4 : 2;
     const int P = a.bSzH * a.bSzW;
-    if (a.num_active_dev != nullptr || a.bSzH > 256 || a.bSzW > 256 || ((size_t)a.C * itemsize) % 16 != 0)
+    if (a.bSzH > 256 || a.bSzW > 256 || ((size_t)a.C * itemsize) % 16 != 0)
         return cudaSuccess;
     const bool odd = itemsize == 2 && (P & 1);
     TmaTilePlan p;
@@ -941,7 +948,7 @@ cudaError_t launch_gather_tma_rows(const BlockArgs& a, int dtype, cudaStream_t s
 {
     *taken = false;
     const int itemsize = dtype == 0 ? 4 : 2;
-    if (a.num_active_dev != nullptr || a.bSzW > 256 || ((size_t)a.C * itemsize) % 16 != 0)
+    if (a.bSzW > 256 || ((size_t)a.C * itemsize) % 16 != 0)
         return cudaSuccess;
     TmaRowsPlan p;
     p.blockW = a.bSzW, p.blockH = a.bSzH, p.pixels = a.bSzH * a.bSzW;

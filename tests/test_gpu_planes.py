@@ -234,6 +234,36 @@ def test_several_blocks_per_tile_chosen_by_launch_size(cuda_ops, oracle_port):
     np.testing.assert_array_equal(y2.cpu().numpy(), exp)
 
 
+@pytest.mark.parametrize("case", [
+    (np.float16, 40, (8, 8), (6, 6), (-1, -1)),      # several blocks per tile
+    (np.float32, 24, (18, 18), (16, 16), (-1, -1)),  # one block per tile, partial channel chunk
+    (np.float16, 72, (17, 17), (15, 15), (-1, -1)),  # odd pixel count
+    (np.float32, 32, (40, 30), (40, 30), (0, 0)),    # row chunks
+], ids=["shared_tile", "one_block", "odd_pixels", "row_chunks"])
+def test_device_count_gather_outside_the_pipeline(cuda_ops, case):
+    """Gathers with the block count on the device whose pixels are not 128-byte multiples (or whose
+    blocks exceed one tile): the TMA-fed tile kernels run over a grid sized for every candidate block
+    and the surplus CTAs leave at once.  Compared with the host-count call; rows past the count stay
+    untouched."""
+    import torch
+    from sbnet_b200 import ops
+    from cuda_ops import to_torch
+    dtype, C, bsize, bstride, boffset = case
+    N, H, W = 2, 128, 120
+    g = cfg.geom_for(H, W, bsize, bstride, boffset)
+    idx_h, cnt_h = cfg.random_block_list(N, g.bcount, 0.4, seed=C)
+    nb, max_blocks = int(cnt_h[0]), idx_h.shape[0]
+    dev = torch.device("cuda:0")
+    idx, cnt = torch.from_numpy(idx_h).to(dev), torch.from_numpy(cnt_h)
+    x = to_torch(cfg.normal((N, H, W, C), 41, dtype)).to(dev)
+    ref = ops.sparse_gather(x, cnt, idx, bsize, bstride, boffset, transpose=True)
+    out = torch.full((max_blocks, C, *bsize), -3.0, dtype=x.dtype, device=dev)
+    ops.sparse_gather_dyn(x, cnt.to(dev), max_blocks, idx, bsize, bstride, boffset, transpose=True, out=out)
+    torch.cuda.synchronize()
+    assert torch.equal(out[:nb], ref)
+    assert bool((out[nb:] == -3.0).all())
+
+
 def test_no_bounded_wait_gave_up(cuda_ops):
     import ctypes as C
     import torch
