@@ -4,7 +4,7 @@
  * Every entry point replaces one seam of the reference library (paths below are relative to
  * sbnet_tensorflow/sbnet_ops/ of uber-research/sbnet).  A TensorFlow OpKernel (or any other host)
  * calls these with raw device pointers exactly where the reference's Compute() methods call their
- * functors; see INTEGRATION.md for the binding.
+ * functors (the repository's integration notes show the binding).
  *
  * Conventions
  *  - All tensor pointers are DEVICE pointers unless a parameter says "host".  The caller owns every
@@ -16,8 +16,18 @@
  *  - Return value: 0 = success; negative = SBNET_ERR_* (the argument was rejected, nothing was
  *    launched; sbnet_last_error() has the text); positive = a cudaError_t from the CUDA runtime.
  *    The library never terminates the process (the reference calls exit(), op_utils.h:27-37).
- *  - Re-entrant: no global mutable state; calls on different streams may run concurrently as long
- *    as they do not share scratch or output buffers.
+ *  - Threads and streams: calls may be made from several host threads and on several streams at once
+ *    as long as they do not share scratch or output buffers.  State the library keeps: per-thread
+ *    caches (the last error text, the last few TMA tensor maps -- keyed by base address, shape and
+ *    element size, so a buffer freed and re-allocated at the same address with the same shape reuses
+ *    a still-valid map -- and which kernels already had their shared-memory limit raised); per-device
+ *    caches (SM count, resolved address of the static scratch); two device-side counters of bounded
+ *    waits that gave up (sbnet_wait_timeouts); the process-wide option table (sbnet_set_option), which
+ *    is initialised from the environment once, at first use; and the fixed scratch array of
+ *    sbnet_reduce_mask_static, which all calls of that one entry point on a GPU share.
+ *  - A call that returns 0 has enqueued its work.  The TMA-fed kernels bound their waits on
+ *    shared-memory barriers; should one ever give up, the kernel returns early, the output is
+ *    incomplete and sbnet_wait_timeouts() reports it -- success of the launch does not imply that.
  */
 #ifndef SBNET_B200_H
 #define SBNET_B200_H
@@ -41,6 +51,9 @@ extern "C" {
 /* sbnet_reduce_mask flags */
 #define SBNET_SCRATCH_CLEAN 1 /* scratch[2..3] are already zero (see below): skip the memset */
 #define SBNET_COUNT_POLL 2    /* pinned count_host: return as soon as the count has arrived (see below) */
+#define SBNET_MASK_STABLE 4   /* the mask is not written by the operation queued just before this call on
+                                 `stream`: its loads may overlap the tail of that operation (see below) */
+#define SBNET_COUNT_YIELD 8   /* with SBNET_COUNT_POLL: give the core away between looks at the count */
 
 /* int32 words of device scratch sbnet_reduce_mask needs */
 #define SBNET_REDUCE_MASK_SCRATCH_INTS 4
@@ -74,8 +87,19 @@ const char* sbnet_last_error(void);
  *                         word instead of synchronising the stream and returns as soon as the count is
  *                         there: the kernel's last index writes may still be in flight, but they are
  *                         ordered before anything enqueued on `stream` afterwards (use an event or a
- *                         stream synchronisation before reading the indices from another stream).  An empty result is reported as ONE block with index (0,0,0),
+ *                         stream synchronisation before reading the indices from another stream).
+ *                         The poll spins on one core for at most 0.2 s; SBNET_COUNT_YIELD makes it call
+ *                         sched_yield() between looks (for hosts that run one such thread per GPU on
+ *                         shared cores).  An empty result is reported as ONE block with index (0,0,0),
  *                         as the reference does.
+ *   SBNET_MASK_STABLE     the kernel is launched with programmatic stream serialization: its prologue
+ *                         overlaps the tail of the kernel queued before it on `stream`, and everything
+ *                         that touches scratch_dev or active_block_indices waits for that kernel.  With
+ *                         this flag the MASK is read before that wait as well, which is only correct when
+ *                         the mask is not produced by that preceding kernel (e.g. the previous layer's
+ *                         scatter precedes, and the mask has been resident for longer).
+ *   Limits                N, bCntH, bCntW <= 32767 (int16 triples); N*bCntH*bCntW < 2^31 (int32 count),
+ *                         larger products are rejected with SBNET_ERR_UNSUPPORTED.
  */
 int sbnet_reduce_mask(const float* mask, int N, int H, int W, float tol, int avgpool,
                       int bOffsH, int bOffsW, int bSzH, int bSzW, int bStrH, int bStrW,
@@ -153,6 +177,22 @@ int sbnet_cuda_timer_end(int64_t handle, float* elapsed_ms);
  * output was left incomplete.  Synchronises the device.
  */
 int sbnet_wait_timeouts(unsigned int* count);
+
+/*
+ * Process-wide switches (no counterpart in the reference), for A/B measurements and for tests that
+ * push one input through every kernel family.  Initialised once from the environment variables in
+ * brackets; afterwards only these calls change them.  Not synchronised with launches in flight on other
+ * threads.  Unknown names are rejected with SBNET_ERR_INVALID_ARGUMENT.
+ *   "planes"          0 default dispatch, 1 persistent TMA pipeline, 2 tile CTAs with plain loads [SBNET_PLANES=tma|tile]
+ *   "disable_tma"     1: plane layouts run the general kernel only                               [SBNET_DISABLE_TMA]
+ *   "tile_blocks"     > 0: small blocks sharing one tile, whatever the launch size               [SBNET_TILE_BLOCKS]
+ *   "rm_kernel"       reduce_mask: 0 default, 1 register-fed band kernel, 2 one thread per block  [SBNET_RM_KERNEL]
+ *   "rm_ctas_per_sm"  reduce_mask: CTAs per SM the column tiling aims at (default 8)             [SBNET_RM_CTAS_PER_SM]
+ *   "rm_pdl"          reduce_mask: 0 launches without programmatic serialization (default 1)     [SBNET_RM_PDL]
+ *   "tail_waves"      plane tiles: launches under this many resident waves get finer work items  [SBNET_TAIL_WAVES]
+ */
+int sbnet_set_option(const char* name, int value);
+int sbnet_get_option(const char* name, int* value);
 
 /*
  * ReduceMask without caller-provided scratch.  No counterpart in the reference.

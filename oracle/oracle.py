@@ -43,10 +43,22 @@ _SIGS = {
 }
 
 
+def reference_ops_dir():
+    """``sbnet_tensorflow/sbnet_ops`` of the reference tree, or None: ``$SBNET_REFERENCE`` names the
+    tree's root, else a directory called ``reference`` beside this repository is tried."""
+    root = os.environ.get("SBNET_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    ops = os.path.join(root, "sbnet_tensorflow", "sbnet_ops")
+    return ops if os.path.isfile(os.path.join(ops, "sparse_gather.cc")) else None
+
+
+def make(targets) -> None:
+    ops = reference_ops_dir()
+    subprocess.run(["make", "-s", "-C", _HERE] + list(targets) + ([f"REF={ops}"] if ops else []), check=True)
+
+
 def build(ref: bool = True) -> None:
     """Compile the checkers (``make -C oracle``).  Building the checker is not using it."""
-    targets = ["port"] + (["ref"] if ref else [])
-    subprocess.run(["make", "-s", "-C", _HERE] + targets, check=True)
+    make(["port"] + (["ref"] if ref else []))
 
 
 class OracleLib:

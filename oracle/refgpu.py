@@ -29,7 +29,8 @@ _lib = None
 
 def build() -> None:
     """``make -C oracle refgpu`` (a no-op with a message when the reference tree is absent)."""
-    subprocess.run(["make", "-s", "-C", _HERE, "refgpu"], check=True)
+    from . import oracle
+    oracle.make(["refgpu"])
 
 
 def available() -> bool:

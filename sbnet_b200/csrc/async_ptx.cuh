@@ -1,9 +1,13 @@
-// Thin wrappers over the PTX used by the plane-layout kernels: shared-memory accesses by 32-bit
-// shared-space address, and the bulk (TMA engine) copy from shared to global memory.
+// Thin wrappers over the PTX used by the TMA-fed kernels: shared-memory accesses by 32-bit
+// shared-space address, bulk (TMA engine) copies in both directions, mbarriers with bounded waits,
+// and the programmatic-dependent-launch controls.
 #pragma once
+#include <cuda.h>
 #include <stdint.h>
 
 namespace sbnet {
+
+constexpr long long kWaitCycles = 1ll << 31;        // bound of every mbarrier wait: ~1.1 s at 1.9 GHz
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p)
 {
@@ -68,6 +72,89 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint4 v)
 {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                  : "memory");
+}
+
+// ---- mbarriers ----------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  false: gave up (or another role of this CTA did): the CTA-wide abort flag is then
+// set and the wait has counted itself in *timeouts (a __device__ counter of the calling file).
+static __device__ __noinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abortFlag,
+                                               unsigned int* timeouts)
+{
+    const long long t0 = clock64();
+    for (uint32_t i = 0;; ++i) {
+        if (mbar_try_wait(bar, parity))
+            return true;
+        if ((i & 31u) == 31u) {
+            if (*abortFlag)
+                return false;
+            if (clock64() - t0 > kWaitCycles)
+                break;
+        }
+    }
+    atomicAdd(timeouts, 1u);
+    *abortFlag = 1;
+    return false;
+}
+
+// ---- loads through the TMA engine (this GPU's memory only; never multicast) -----------------------
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                            int c3, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+        : "memory");
+}
+// Untiled bulk copy: both addresses 16-byte aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+        "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+
+// ---- programmatic dependent launch ----------------------------------------------------------------
+// wait: blocks until the kernel this one was launched behind (with the programmatic-serialization
+// attribute) has completed and its writes are visible; a no-op for an ordinary launch.
+__device__ __forceinline__ void pdl_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+// launch_dependents: lets a kernel queued behind this one with that attribute start its prologue
+// once every CTA of this grid has passed this point; a no-op when nothing of the kind is queued.
+__device__ __forceinline__ void pdl_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 } // namespace sbnet

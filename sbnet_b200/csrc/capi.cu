@@ -3,11 +3,18 @@
 #include <limits.h>
 #include <stdarg.h>
 #include <stdio.h>
+#include <sched.h>
 #include <time.h>
 
 #include "../../include/sbnet_b200.h"
+#include <stdlib.h>
+#include <string.h>
+
+#include <mutex>
+
 #include "common.cuh"
 #include "kernels.h"
+#include "options.h"
 
 #define SBNET_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -100,7 +107,63 @@ int scatter_mode(const char* op, int add, int atomic, int bSzH, int bSzW, int bS
 namespace sbnet {
 // Lets other translation units of the library report through sbnet_last_error().
 void set_last_error(const char* text) { snprintf(g_err, sizeof(g_err), "%s", text); }
+
+static int env_number(const char* name, int dflt)
+{
+    const char* v = getenv(name);
+    return (v && *v) ? atoi(v) : dflt;
+}
+
+Options& options()
+{
+    static Options opt;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        const char* planes = getenv("SBNET_PLANES");
+        opt.planes = (planes && planes[0] == 't') ? (planes[1] == 'i' ? 2 : 1) : 0;
+        opt.disableTma = env_number("SBNET_DISABLE_TMA", 0) == 1;
+        opt.tileBlocks = env_number("SBNET_TILE_BLOCKS", 0);
+        opt.rmKernel = env_number("SBNET_RM_KERNEL", 0);
+        opt.rmCtasPerSm = env_number("SBNET_RM_CTAS_PER_SM", 8);
+        opt.rmPdl = env_number("SBNET_RM_PDL", 1);
+        opt.tailSplit = env_number("SBNET_TAIL_WAVES", 4);
+    });
+    return opt;
+}
 } // namespace sbnet
+
+namespace {
+struct OptionName {
+    const char* name;
+    int sbnet::Options::*field;
+};
+const OptionName kOptionNames[] = {
+    {"planes", &sbnet::Options::planes},          {"disable_tma", &sbnet::Options::disableTma},
+    {"tile_blocks", &sbnet::Options::tileBlocks}, {"rm_kernel", &sbnet::Options::rmKernel},
+    {"rm_ctas_per_sm", &sbnet::Options::rmCtasPerSm}, {"rm_pdl", &sbnet::Options::rmPdl},
+    {"tail_waves", &sbnet::Options::tailSplit},
+};
+} // namespace
+
+SBNET_EXPORT int sbnet_set_option(const char* name, int value)
+{
+    for (const OptionName& o : kOptionNames)
+        if (name != nullptr && strcmp(name, o.name) == 0) {
+            sbnet::options().*(o.field) = value;
+            return SBNET_OK;
+        }
+    return reject(SBNET_ERR_INVALID_ARGUMENT, "sbnet_set_option: unknown option '%s'", name ? name : "(null)");
+}
+
+SBNET_EXPORT int sbnet_get_option(const char* name, int* value)
+{
+    for (const OptionName& o : kOptionNames)
+        if (name != nullptr && value != nullptr && strcmp(name, o.name) == 0) {
+            *value = sbnet::options().*(o.field);
+            return SBNET_OK;
+        }
+    return reject(SBNET_ERR_INVALID_ARGUMENT, "sbnet_get_option: unknown option '%s'", name ? name : "(null)");
+}
 
 SBNET_EXPORT int sbnet_version(void) { return 100; }
 
@@ -123,6 +186,9 @@ SBNET_EXPORT int sbnet_reduce_mask(const float* mask, int N, int H, int W, float
         return reject(SBNET_ERR_INVALID_ARGUMENT,
                       "%s: N, bCntH and bCntW must fit the int16 index triples (<= 32767), got %d, %d, %d",
                       op, N, bCntH, bCntW);
+    if ((long long)N * bCntH * bCntW >= (1ll << 31))
+        return reject(SBNET_ERR_UNSUPPORTED, "%s: N*bCntH*bCntW = %lld candidate blocks do not fit the int32 count",
+                      op, (long long)N * bCntH * bCntW);
     if (int rc = check_geometry(op, bOffsH, bOffsW, bSzH, bSzW, bStrH, bStrW, bCntH, bCntW))
         return rc;
     if (mask == nullptr || active_block_indices == nullptr || scratch_dev == nullptr)
@@ -147,7 +213,8 @@ SBNET_EXPORT int sbnet_reduce_mask(const float* mask, int N, int H, int W, float
             return cuda_status(e);
     if (cudaError_t e = sbnet::launch_reduce_mask(mask, N, H, W, tol, avgpool != 0, bOffsH, bOffsW, bSzH,
                                                   bSzW, bStrH, bStrW, bCntH, bCntW,
-                                                  active_block_indices, scratch_dev, hostDev, s))
+                                                  active_block_indices, scratch_dev, hostDev,
+                                                  (flags & SBNET_MASK_STABLE) != 0, s))
         return cuda_status(e);
     if (count_host != nullptr) {
         if (hostDev != nullptr && (flags & SBNET_COUNT_POLL)) {
@@ -157,8 +224,11 @@ SBNET_EXPORT int sbnet_reduce_mask(const float* mask, int N, int H, int W, float
             volatile int32_t* word = count_host;
             timespec t0;
             clock_gettime(CLOCK_MONOTONIC, &t0);
+            const bool yield = (flags & SBNET_COUNT_YIELD) != 0;
             for (unsigned spins = 0; *word == kCountSentinel; ++spins) {
-                if ((spins & 1023u) == 1023u) {
+                if (yield)
+                    sched_yield();   // several such threads (one per GPU) may share this core
+                if (yield || (spins & 1023u) == 1023u) {
                     timespec t1;
                     clock_gettime(CLOCK_MONOTONIC, &t1);
                     if ((t1.tv_sec - t0.tv_sec) * 1000000000ll + (t1.tv_nsec - t0.tv_nsec) > 200000000ll)
@@ -275,5 +345,11 @@ SBNET_EXPORT int sbnet_wait_timeouts(unsigned int* count)
 {
     if (count == nullptr)
         return reject(SBNET_ERR_INVALID_ARGUMENT, "sbnet_wait_timeouts: null output");
-    return cuda_status(sbnet::read_wait_timeouts(count));
+    unsigned int planes = 0, mask = 0;
+    if (cudaError_t e = sbnet::read_wait_timeouts(&planes))
+        return cuda_status(e);
+    if (cudaError_t e = sbnet::read_rm_wait_timeouts(&mask))
+        return cuda_status(e);
+    *count = planes + mask;
+    return SBNET_OK;
 }

@@ -25,8 +25,10 @@
 // the same stream) a fixed-size grid strides over the items instead.
 #include <stdlib.h>
 
+#include "async_ptx.cuh"
 #include "common.cuh"
 #include "kernels.h"
+#include "options.h"
 
 namespace sbnet {
 
@@ -105,6 +107,7 @@ __device__ __forceinline__ void rows_item(const BlockArgs& a, const RowPlan& p, 
 template <int VB, int MODE, typename T>
 __global__ void __launch_bounds__(kThreads) rows_kernel(const BlockArgs a, const RowPlan p)
 {
+    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
     uint32_t ib, chunk;
     p.chunksPerBlock.divmod(blockIdx.x, ib, chunk);
     rows_item<VB, MODE, T>(a, p, ib, chunk);
@@ -113,6 +116,7 @@ __global__ void __launch_bounds__(kThreads) rows_kernel(const BlockArgs a, const
 template <int VB, int MODE, typename T>
 __global__ void __launch_bounds__(kThreads) rows_kernel_dyn(const BlockArgs a, const RowPlan p)
 {
+    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
     const long long nItems = (long long)active_count(a) * p.chunksPerBlock.div;
     for (long long item = blockIdx.x; item < nItems; item += gridDim.x) {
         uint32_t ib, chunk;
@@ -165,6 +169,7 @@ template <int VB, typename T> __device__ __forceinline__ typename Vec<VB>::type 
 template <int VB, int MODE, typename T>
 __global__ void __launch_bounds__(kThreads, 4) planes_kernel(const BlockArgs a, const PlanePlan p)
 {
+    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
     typedef typename Vec<VB>::type V;
     constexpr int EPV = VB / (int)sizeof(T);   // elements per vector
     __shared__ __align__(16) unsigned char tileRaw[kTileBytes];
@@ -280,15 +285,16 @@ int sm_count()
     return cached[dev];
 }
 
-// CTAs of `kernel` that fit one SM at once; persistent grids are sized to exactly one resident wave.
-template <typename K> static int resident_ctas(K kernel, int threads)
+// CTAs of `kernel` that fit one SM at once (a property of the kernel and of sm_100a, the only target);
+// persistent grids are sized to exactly one resident wave of the CURRENT device.
+template <typename K> static int ctas_per_sm(K kernel, int threads)
 {
     int perSm = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, kernel, threads, 0) != cudaSuccess || perSm < 1) {
         (void)cudaGetLastError();
         perSm = 1;
     }
-    return perSm * sm_count();
+    return perSm;
 }
 
 static int pick_vector_bytes(const BlockArgs& a, int itemsize)
@@ -319,7 +325,8 @@ static void launch_rows(const BlockArgs& a, cudaStream_t stream)
     if (a.num_active_dev == nullptr && nItems <= 0x7fffffffll) {
         rows_kernel<VB, MODE, T><<<(unsigned)nItems, kThreads, 0, stream>>>(a, p);
     } else {
-        static const int wave = resident_ctas(rows_kernel_dyn<VB, MODE, T>, kThreads);
+        static const int perSm = ctas_per_sm(rows_kernel_dyn<VB, MODE, T>, kThreads);
+        const int wave = perSm * sm_count();
         const int grid = (int)(nItems < wave ? nItems : wave);
         rows_kernel_dyn<VB, MODE, T><<<grid, kThreads, 0, stream>>>(a, p);
     }
@@ -356,7 +363,8 @@ static void launch_planes(const BlockArgs& a, cudaStream_t stream)
     const long long nItems = (long long)a.numActive * nC * nP;
     // host-side count: one CTA per item (short CTAs stream faster than a resident grid); device-side
     // count: one resident wave striding over the items
-    static const int wave = resident_ctas(planes_kernel<VB, MODE, T>, kThreads);
+    static const int perSm = ctas_per_sm(planes_kernel<VB, MODE, T>, kThreads);
+    const int wave = perSm * sm_count();
     const bool perItem = a.num_active_dev == nullptr && nItems <= 0x7fffffffll;
     const unsigned grid = (unsigned)(perItem ? nItems : (nItems < wave ? nItems : wave));
     planes_kernel<VB, MODE, T><<<grid, kThreads, 0, stream>>>(a, p);
@@ -418,12 +426,9 @@ cudaError_t launch_blocks(const BlockArgs& a, int dtype, int mode, bool transpos
         // cover whole 128-byte image lines (about 20 % faster than the pipeline's dense tile); for
         // gather the two are within a few percent (tile CTAs +3 % at the largest sizes), so the
         // pipeline only serves calls whose block count lives on the device.
-        // SBNET_PLANES=tma|tile forces one of them (A/B measurements).
+        // The `planes` option (SBNET_PLANES=tma|tile) forces one of them (A/B measurements).
         bool taken = false;
-        const char* force = getenv("SBNET_PLANES");
-        bool tileFirst = true;
-        if (force && force[0] == 't')
-            tileFirst = force[1] == 'i';
+        const bool tileFirst = options().planes != 1;
         if (tileFirst) {
             if (cudaError_t e = launch_planes_simt(a, dtype, mode, stream, &taken))
                 return e;
@@ -453,6 +458,7 @@ __global__ void __launch_bounds__(kThreads) copy_kernel(uint4* __restrict__ dst,
                                                         unsigned char* dstTail,
                                                         const unsigned char* srcTail, int tailBytes)
 {
+    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
     const size_t base = (size_t)blockIdx.x * (kThreads * kCopyUnroll) + threadIdx.x;
     uint4 v[kCopyUnroll];
 #pragma unroll
@@ -469,6 +475,7 @@ __global__ void __launch_bounds__(kThreads) copy_kernel(uint4* __restrict__ dst,
 
 __global__ void copy_bytes_kernel(unsigned char* dst, const unsigned char* src, size_t n)
 {
+    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
         dst[i] = src[i];

@@ -8,11 +8,13 @@ namespace sbnet {
 
 struct BlockArgs;
 
-// scratch: 4 x int32 on the device; [1] and [2] must be zero on entry and are zero again on exit.
+// scratch: 4 x int32 on the device; [2] and [3] must be zero on entry and are zero again on exit.
+// maskStable: the mask is not written by the operation queued just before this call on `stream`.
 cudaError_t launch_reduce_mask(const float* mask, int N, int H, int W, float tol, bool avgpool,
                                int bOffsH, int bOffsW, int bSzH, int bSzW, int bStrH, int bStrW,
                                int bCntH, int bCntW, int16_t* idx, int32_t* scratch,
-                               int32_t* host_count_dev, cudaStream_t stream);
+                               int32_t* host_count_dev, bool maskStable, cudaStream_t stream);
+cudaError_t read_rm_wait_timeouts(unsigned int* out);
 
 // mode: 0 gather, 1 scatter overwrite, 2 scatter add (disjoint blocks), 3 scatter atomic add
 cudaError_t launch_blocks(const BlockArgs& a, int dtype, int mode, bool transpose,

@@ -1,0 +1,22 @@
+// Process-wide switches of the library, for A/B measurements and for tests that push one input
+// through every kernel family.  Read from the environment ONCE, at first use; changed afterwards
+// only through sbnet_set_option() (include/sbnet_b200.h).  Plain ints: a change made while another
+// thread is launching is seen by that launch or by the next one.
+#pragma once
+
+namespace sbnet {
+
+struct Options {
+    int planes;        // plane-layout dispatch: 0 default, 1 persistent TMA pipeline, 2 tile CTAs with plain loads
+                       //   (SBNET_PLANES=tma|tile)
+    int disableTma;    // 1: plane layouts run the general kernel only (SBNET_DISABLE_TMA=1)
+    int tileBlocks;    // > 0: blocks per shared tile regardless of the launch size (SBNET_TILE_BLOCKS)
+    int rmKernel;      // reduce_mask: 0 default, 1 band kernel, 2 one thread per block (SBNET_RM_KERNEL)
+    int rmCtasPerSm;   // reduce_mask tile kernel: CTAs per SM the column tiling aims at (SBNET_RM_CTAS_PER_SM)
+    int rmPdl;         // reduce_mask tile kernel: launch with programmatic serialization (SBNET_RM_PDL)
+    int tailSplit;     // plane tiles: cut the tiles of launches under this many resident waves (SBNET_TAIL_WAVES)
+};
+
+Options& options();
+
+} // namespace sbnet

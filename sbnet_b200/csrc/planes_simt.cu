@@ -31,6 +31,7 @@
 #include "async_ptx.cuh"
 #include "common.cuh"
 #include "kernels.h"
+#include "options.h"
 
 namespace sbnet {
 
@@ -74,6 +75,7 @@ constexpr int kTileMulti = 2;    // blocks of at most 192 pixels: as many whole 
 template <typename T, int SHAPE, bool ODD = false>
 __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gather_simt(const BlockArgs a, const SimtPlan p)
 {
+    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
     constexpr bool PCH = SHAPE == kTileChunked, MB = SHAPE == kTileMulti;
     static_assert(!ODD || (sizeof(T) == 2 && !PCH), "odd rows: fp16, whole blocks only");
     __shared__ __align__(1024) unsigned char tileRaw[kPsTileBytes];
@@ -309,6 +311,7 @@ template <int MODE, typename T, int GW, int SHAPE>
 __global__ void __launch_bounds__(kPsThreads, MODE == kScatterAdd ? 2 : 3)
 planes_scatter_simt(const BlockArgs a, const SimtPlan p)
 {
+    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
     constexpr bool PCH = SHAPE == kTileChunked, MB = SHAPE == kTileMulti;
     static_assert(!PCH || GW > 1, "pixel chunks copy in whole 8- or 16-byte units");
     static_assert(GW != 0 || sizeof(T) == 2, "odd rows of halves: fp16 only");
@@ -610,8 +613,7 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
 // number of words).
 static bool planes_simt_eligible(const BlockArgs& a, int itemsize)
 {
-    const char* off = getenv("SBNET_DISABLE_TMA");
-    if (off && off[0] == '1')
+    if (options().disableTma)
         return false;
     const long long P = (long long)a.bSzH * a.bSzW;
     if (((size_t)a.C * itemsize) % 16 != 0 || P > (1 << 24))
@@ -663,8 +665,8 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
     p.blocksPerItem = 1;
     if (!pch && (mode == kGather || P <= 100)) {
         long long perSm = (long long)a.numActive * p.cChunks.div / ((long long)sm_count() * 4);
-        if (const char* force = getenv("SBNET_TILE_BLOCKS"))   // tests: pack up to this many blocks regardless of the launch size
-            perSm = atoi(force);
+        if (options().tileBlocks > 0)   // tests: pack up to this many blocks regardless of the launch size
+            perSm = options().tileBlocks;
         // what fits: 384 pixels, and (rows rounded up to words) 384/EPW words per tile row
         const long long fit = std::min<long long>(kPsMaxPixels / P, (kPsMaxPixels / epw) / p.units);
         const long long k = std::min<long long>(std::min<long long>(fit, kPsThreads), perSm);
@@ -674,10 +676,9 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
     const bool multi = p.blocksPerItem > 1;
     // Gathers of at most 384 pixels per block are fed by TMA where possible (planes_tma.cu: same tile,
     // one TMA load per block instead of plain loads; measured +3 % on one-block tiles, up to +20 % on
-    // shared tiles).  SBNET_PLANES=tile keeps the plain-load kernel (A/B measurements, tests).
+    // shared tiles).  The `planes` option set to 2 (SBNET_PLANES=tile) keeps the plain-load kernel (A/B measurements, tests).
     if (mode == kGather) {
-        const char* force = getenv("SBNET_PLANES");
-        if (!(force && force[0] == 't' && force[1] == 'i')) {
+        if (options().planes != 2) {
             if (cudaError_t e = pch ? launch_gather_tma_rows(a, dtype, stream, taken)
                                     : launch_gather_tma_tile(a, dtype, p.blocksPerItem, stream, taken))
                 return e;

@@ -38,6 +38,7 @@
 #include "async_ptx.cuh"
 #include "common.cuh"
 #include "kernels.h"
+#include "options.h"
 
 namespace sbnet {
 
@@ -45,7 +46,6 @@ constexpr int kConsumerWarps = 8;
 constexpr int kConsumers = kConsumerWarps * 32;
 constexpr int kTmaThreads = kConsumers + 32;
 constexpr int kMaxPixels = 384;                     // 48 KB stages
-constexpr long long kWaitCycles = 1ll << 31;        // ~1.1 s at 1.9 GHz
 
 __device__ unsigned int g_wait_timeouts = 0;
 
@@ -59,64 +59,10 @@ struct TmaPlan {
     int inStageBytes, outStageBytes;
 };
 
-// ---- PTX wrappers -------------------------------------------------------------------------------
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+// ---- PTX wrappers (mbarriers, TMA loads: async_ptx.cuh) -------------------------------------------
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abortFlag)
 {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait.  false: gave up (or another role of this CTA did).
-__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abortFlag)
-{
-    const long long t0 = clock64();
-    for (uint32_t i = 0;; ++i) {
-        if (mbar_try_wait(bar, parity))
-            return true;
-        if ((i & 31u) == 31u) {
-            if (*abortFlag)
-                return false;
-            if (clock64() - t0 > kWaitCycles)
-                break;
-        }
-    }
-    atomicAdd(&g_wait_timeouts, 1u);
-    *abortFlag = 1;
-    return false;
-}
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2,
-                                            int c3, uint32_t bar)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
-        "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
-        : "memory");
-}
-__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
-{
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-        "l"(src), "r"(bytes), "r"(bar)
-        : "memory");
+    return mbar_wait_bounded(bar, parity, abortFlag, &g_wait_timeouts);
 }
 // Barrier among the consumer warps only (the producer warp never joins), with an OR vote.
 __device__ __forceinline__ bool consumers_any(bool pred)
@@ -160,10 +106,22 @@ __device__ __forceinline__ void ring_init(const Ring& r, const TmaPlan& p, int* 
             mbar_init(r.full0 + 8u * s, 1);
             mbar_init(r.empty0 + 8u * s, kConsumerWarps);
         }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_init_fence();
         fence_async_smem();
     }
     __syncthreads();
+}
+
+// Producer, after its last issue: waits (bounded, on a flag of its own, so that an abort raised by
+// the consumers does not cut it short) until the last loads it issued -- `issued` in total, at most
+// one per stage still open -- have landed.  The CTA's shared memory is therefore never given back
+// with a copy in flight over it, whether the consumers finished their items or gave up.
+__device__ __forceinline__ void drain_loads(const Ring& r, const TmaPlan& p, int issued)
+{
+    int gaveUp = 0;
+    for (int j = max(issued - p.inStages, 0); j < issued; ++j)
+        if (!mbar_wait(r.full0 + 8u * (uint32_t)(j % p.inStages), (uint32_t)(j / p.inStages) & 1u, &gaveUp))
+            break;
 }
 
 __device__ __forceinline__ int device_count(const BlockArgs& a)
@@ -179,6 +137,7 @@ template <typename T>
 __global__ void __launch_bounds__(kTmaThreads, 1)
 planes_gather_tma(const __grid_constant__ CUtensorMap imageMap, const BlockArgs a, const TmaPlan p)
 {
+    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
     extern __shared__ unsigned char dynSmem[];
     __shared__ int abortFlag;
     constexpr int EPW = 4 / (int)sizeof(T);        // pixels per 32-bit word of a channel plane
@@ -207,6 +166,7 @@ planes_gather_tma(const __grid_constant__ CUtensorMap imageMap, const BlockArgs 
                 tma_load_4d(ring.in0 + (uint32_t)s * p.inStageBytes, &imageMap,
                             (int)cc * (128 / (int)sizeof(T)), w0, h0, n, ring.full0 + 8u * s);
             }
+            drain_loads(ring, p, k);
         }
         return;
     }
@@ -277,6 +237,7 @@ planes_gather_tma(const __grid_constant__ CUtensorMap imageMap, const BlockArgs 
 template <int MODE, typename T>
 __global__ void __launch_bounds__(kTmaThreads, 1) planes_scatter_tma(const BlockArgs a, const TmaPlan p)
 {
+    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
     extern __shared__ unsigned char dynSmem[];
     __shared__ int abortFlag;
     constexpr int EPW = 4 / (int)sizeof(T);
@@ -305,6 +266,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) planes_scatter_tma(const Block
                 bulk_load_1d(ring.in0 + (uint32_t)s * p.inStageBytes, src, (uint32_t)p.tileBytes,
                              ring.full0 + 8u * s);
             }
+            drain_loads(ring, p, k);
         }
         return;
     }
@@ -441,6 +403,7 @@ template <typename T, bool ODD = false>
 __global__ void __launch_bounds__(kTileThreads, 4)
 planes_gather_tma_tile(const __grid_constant__ CUtensorMap imageMap, const BlockArgs a, const TmaTilePlan p)
 {
+    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
     static_assert(!ODD || sizeof(T) == 2, "odd rows of halves: 16-bit types only");
     extern __shared__ unsigned char dynSmem[];
     __shared__ __align__(8) unsigned long long barStorage;
@@ -466,7 +429,7 @@ planes_gather_tma_tile(const __grid_constant__ CUtensorMap imageMap, const Block
     if (threadIdx.x == 0) {
         abortFlag = 0;
         mbar_init(bar, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_init_fence();
         fence_async_smem();
     }
     __syncthreads();
@@ -582,6 +545,7 @@ __global__ void __launch_bounds__(kTileThreads, 4)
 planes_gather_tma_rows(const __grid_constant__ CUtensorMap mapFull, const __grid_constant__ CUtensorMap mapLast,
                        const BlockArgs a, const TmaRowsPlan p)
 {
+    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
     extern __shared__ unsigned char dynSmem[];
     __shared__ __align__(8) unsigned long long barStorage;
     __shared__ int abortFlag;
@@ -606,7 +570,7 @@ planes_gather_tma_rows(const __grid_constant__ CUtensorMap mapFull, const __grid
     if (threadIdx.x == 0) {
         abortFlag = 0;
         mbar_init(bar, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_init_fence();
         fence_async_smem();
     }
     __syncthreads();
@@ -784,8 +748,7 @@ static bool image_map(const BlockArgs& a, int itemsize, int boxW, int boxH, CUte
 
 bool planes_tma_eligible(const BlockArgs& a, int itemsize)
 {
-    const char* off = getenv("SBNET_DISABLE_TMA");
-    if (off && off[0] == '1')
+    if (options().disableTma)
         return false;
     const long long P = (long long)a.bSzH * a.bSzW;
     const size_t pixelBytes = (size_t)a.C * itemsize;
@@ -896,8 +859,9 @@ cudaError_t launch_planes_tma(const BlockArgs& a, int dtype, int mode, cudaStrea
 }
 
 // Gather with `blocksPerItem` (>= 1) blocks per tile; not taken (the plain-load kernel of
-// planes_simt.cu runs instead) for blocks of more than 384 pixels, a block count on the device, or
-// when the driver has no tensor-map encoder.
+// planes_simt.cu runs instead) for blocks of more than 384 pixels or when the driver has no
+// tensor-map encoder.  With the block count on the device the grid covers every candidate block and
+// the surplus CTAs leave at once.
 cudaError_t launch_gather_tma_tile(const BlockArgs& a, int dtype, int blocksPerItem, cudaStream_t stream, bool* taken)
 {
     *taken = false;
@@ -942,8 +906,8 @@ cudaError_t launch_gather_tma_tile(const BlockArgs& a, int dtype, int blocksPerI
 }
 
 // Gather of blocks of more than 384 pixels by row chunks; not taken (the pixel chunks of
-// planes_simt.cu run instead) for blocks wider than 256 pixels, a block count on the device, or when
-// the driver has no tensor-map encoder.
+// planes_simt.cu run instead) for blocks wider than 256 pixels or when the driver has no tensor-map
+// encoder.  With the block count on the device the grid covers every candidate block.
 cudaError_t launch_gather_tma_rows(const BlockArgs& a, int dtype, cudaStream_t stream, bool* taken)
 {
     *taken = false;

@@ -6,12 +6,21 @@
 // reduce_mask.cc:203-220).  Results follow the reference CPU functor (reduce_mask.cc:66-96): same
 // set of indices, same count; the order of the list is arrival order, as on the reference GPU path.
 //
-// Layout of the work: one CTA owns a horizontal BAND of the image -- the rows of one block row bh
-// of one image n -- and a tile of consecutive block columns.  Threads own image columns (four at a
-// time, one 128-bit load per row) and run down the band's rows keeping all loads of a batch in
-// flight; the per-column partial results go to shared memory, then one thread per block combines
-// the columns of its window.  Every mask byte is fetched from DRAM once (neighbouring bands share
-// their halo rows through L2).
+// Layout of the work: one CTA owns a TILE of the image -- the rows of one block row bh of one image
+// n, cut into runs of at most 32 consecutive block columns.  Every mask byte is fetched from DRAM
+// once (neighbouring tiles share their halo rows and columns through L2).
+//  * reduce_mask_tile (rows of a multiple of four pixels, 16-byte aligned mask, tile fits shared
+//    memory -- every benchmark shape): the tile's in-range rows are brought into shared memory by
+//    the TMA engine, one untiled bulk copy per row issued by the lanes of one warp onto one
+//    mbarrier, so the load phase costs no registers and no load instructions.  Eight lanes then sum
+//    (or test) the window of one block straight out of shared memory, combine by shuffles, and the
+//    first warp ballots the verdicts, reserves the tile's run of the index list with ONE 64-bit atomic
+//    and writes the triples.  The kernel is launched with the programmatic-serialization attribute:
+//    its prologue (and, when the caller vouches for the mask, its loads) overlap the tail of the
+//    kernel queued before it.
+//  * reduce_mask_band (any other shape): threads own image columns (four at a time, one 128-bit load
+//    per row) and run down the band's rows keeping all loads of a batch in flight; per-column partial
+//    results go to shared memory, then one thread per block combines the columns of its window.
 //
 // Exactness.  Max pooling is "any pixel > tol", which does not depend on evaluation order.  Average
 // pooling compares fl(sum/area) with tol, and the reference sums the window row-major in fp32; the
@@ -19,10 +28,14 @@
 // the sum of magnitudes, which bounds the difference between ANY two summation orders; only when
 // the threshold falls inside that bound (practically never for 0/1 masks, rarely for real-valued
 // ones) is the block re-evaluated by one thread in the reference's exact order.
+#include "async_ptx.cuh"
 #include "common.cuh"
 #include "kernels.h"
+#include "options.h"
 
 namespace sbnet {
+
+__device__ unsigned int g_rm_wait_timeouts = 0;   // bounded waits of reduce_mask_tile that gave up
 
 constexpr int kRmThreads = 192;      // 176 threads cover a 704-pixel row with 128-bit loads; 3 CTAs per SM
                                     // keep the 400 bands of an [8,800,704] mask in a single wave
@@ -38,6 +51,7 @@ struct RmArgs {
     float tol;
     int bOffsH, bOffsW, bSzH, bSzW, bStrH, bStrW, bCntH, bCntW;
     int tileBlocks;        // block columns per CTA
+    int earlyLoads;        // tile kernel: the mask may be read before the preceding kernel has finished
     float area;            // (float)(bSzH*bSzW)
 };
 
@@ -93,10 +107,168 @@ __device__ __forceinline__ void publish(const RmArgs& a, int count)
     a.scratch[0] = count;
     *cursor64(a) = 0ull;
     if (a.host_count) {
+        // a host that sees the count may hand scratch[0] (or the indices) to other work at once:
+        // everything published so far must be visible system-wide before the host-visible store
+        __threadfence_system();
         *reinterpret_cast<volatile int32_t*>(a.host_count) = count;
         __threadfence_system();
     }
 }
+
+// Verdict of an average-pooled block from its window sum s and sum of magnitudes m, both taken in
+// an arbitrary order over `terms` in-range pixels: decided from the error bound where that is
+// conclusive, else re-evaluated in the reference's order.
+__device__ __forceinline__ bool avg_verdict(const RmArgs& a, float s, float m, float terms, int n, int bh, int bw)
+{
+    // |sum in any order - exact sum| <= ~terms * 2^-24 * m; two orders differ by at most twice
+    // that.  A factor-two margin on top covers the rounding of m itself.
+    const float rel = terms * 5.9604645e-8f;
+    const float delta = 4.0f * rel * m;   // exactly 0 for an all-zero window
+    const bool yes = __fdiv_rn(s - delta, a.area) > a.tol;
+    const bool no = !(__fdiv_rn(s + delta, a.area) > a.tol);
+    if (rel < 0.125f && m < 3.0e38f && yes)
+        return true;
+    if (rel < 0.125f && m < 3.0e38f && no)
+        return false;
+    return block_active_exact<true>(a, n, bh, bw);
+}
+
+// ---- tile kernel ------------------------------------------------------------------------------------
+constexpr int kRmLanesPerBlock = 8;     // lanes that share one block's window
+constexpr int kRmTileMaxBlocks = 32;    // block columns per tile: one warp ballots and appends them
+constexpr int kRmTileMaxThreads = kRmLanesPerBlock * kRmTileMaxBlocks;
+constexpr int kRmTileSmemMax = 96 * 1024;
+
+template <bool AVG>
+__global__ void __launch_bounds__(kRmTileMaxThreads) reduce_mask_tile(const RmArgs a)
+{
+    extern __shared__ __align__(128) unsigned char rmSmem[];   // [nRows][pitch] fp32
+    __shared__ __align__(8) unsigned long long barStorage;
+    __shared__ int abortFlag;
+    __shared__ unsigned char verdict[kRmTileMaxBlocks];
+
+    const int n = blockIdx.z, bh = blockIdx.y;
+    const int bw0 = blockIdx.x * a.tileBlocks;
+    const int nBlk = min(a.tileBlocks, a.bCntW - bw0);
+    const int h0 = a.bOffsH + bh * a.bStrH;
+    const int hBeg = max(h0, 0), hEnd = min(h0 + a.bSzH, a.H);
+    const int nRows = max(hEnd - hBeg, 0);
+    // columns this tile touches, widened to whole 16-byte groups (W is a multiple of four)
+    const int cBeg = max(a.bOffsW + bw0 * a.bStrW, 0) & ~3;
+    const int cEnd = min((min(a.bOffsW + (bw0 + nBlk - 1) * a.bStrW + a.bSzW, a.W) + 3) & ~3, a.W);
+    const int nCols = max(cEnd - cBeg, 0);
+    const bool haveTile = nRows > 0 && nCols > 0;
+    const uint32_t tile = smem_u32(rmSmem);
+    const uint32_t bar = smem_u32(&barStorage);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    if (threadIdx.x == 0) {
+        abortFlag = 0;
+        mbar_init(bar, 1);
+        mbar_init_fence();
+        fence_async_smem();
+    }
+    __syncthreads();
+    if (!a.earlyLoads)
+        pdl_wait();   // the mask may be the output of the kernel queued before this one
+    if (warp == 0 && haveTile) {
+        if (lane == 0)
+            mbar_expect_tx(bar, (uint32_t)nRows * (uint32_t)nCols * 4u);
+        __syncwarp();
+        const float* src = a.mask + ((size_t)n * a.H + hBeg) * a.W + cBeg;
+        for (int r = lane; r < nRows; r += 32)
+            bulk_load_1d(tile + (uint32_t)(r * nCols) * 4u, src + (size_t)r * a.W, (uint32_t)nCols * 4u, bar);
+    }
+    if (haveTile) {
+        // every warp waits for the tile (bounded); a warp that gives up waits once more, again
+        // bounded, so that copies are not left in flight over shared memory the CTA has given back
+        int ok = 1;
+        if (lane == 0) {
+            ok = mbar_wait_bounded(bar, 0, &abortFlag, &g_rm_wait_timeouts) ? 1 : 0;
+            if (!ok) {
+                int again = 0;
+                (void)mbar_wait_bounded(bar, 0, &again, &g_rm_wait_timeouts);
+            }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (__syncthreads_or(ok == 0)) {
+            // The tile never arrived: the CTA still takes its finish ticket (appending nothing), so the
+            // call completes and the wait counter tells the host that the result is incomplete.
+            if (threadIdx.x == 0) {
+                pdl_wait();
+                const unsigned long long old = atomicAdd(cursor64(a), 1ull << 32);
+                if ((unsigned)(old >> 32) == gridDim.x * gridDim.y * gridDim.z - 1)
+                    publish(a, (int)(unsigned)old);
+            }
+            return;
+        }
+    }
+
+    // ---- window of block b: eight lanes stride over its columns, each running down the rows
+    const float* tileF = reinterpret_cast<const float*>(rmSmem);
+    // (whole warps take every trip: lanes past the last block hold zeros and shuffle along)
+    for (int t0 = warp * 32; t0 < nBlk * kRmLanesPerBlock; t0 += blockDim.x) {
+        const int t = t0 + lane;
+        const int b = t / kRmLanesPerBlock, g = t % kRmLanesPerBlock;
+        const bool mine = b < nBlk;
+        const int w0 = a.bOffsW + (bw0 + b) * a.bStrW;
+        const int wBeg = max(w0, 0), wEnd = mine ? min(w0 + a.bSzW, a.W) : 0;
+        float s = 0.0f, m = 0.0f;
+        bool any = false;
+        for (int c = wBeg + g - cBeg; c < wEnd - cBeg; c += kRmLanesPerBlock) {
+            const float* col = tileF + c;
+#pragma unroll 6
+            for (int r = 0; r < nRows; ++r) {
+                const float v = col[r * nCols];
+                if (AVG) {
+                    s = __fadd_rn(s, v);
+                    m = __fadd_rn(m, fabsf(v));
+                } else {
+                    any |= v > a.tol;
+                }
+            }
+        }
+        bool active = false;
+        if (AVG) {
+#pragma unroll
+            for (int d = kRmLanesPerBlock / 2; d > 0; d >>= 1) {   // a block's lanes are neighbours in one warp
+                s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, d));
+                m = __fadd_rn(m, __shfl_xor_sync(0xffffffffu, m, d));
+            }
+            if (g == 0 && mine) {
+                const float terms = (float)nRows * (float)max(wEnd - wBeg, 0);
+                active = avg_verdict(a, s, m, terms, n, bh, bw0 + b);
+            }
+        } else {
+            const unsigned hits = __ballot_sync(0xffffffffu, any);
+            active = ((hits >> (lane & ~(kRmLanesPerBlock - 1))) & ((1u << kRmLanesPerBlock) - 1u)) != 0u;
+        }
+        if (g == 0 && mine)
+            verdict[b] = active ? 1 : 0;
+    }
+    __syncthreads();
+
+    // ---- first warp: ballot, ONE atomic reserves the tile's run and takes the finish ticket, append
+    if (warp == 0) {
+        const bool act = lane < nBlk && verdict[lane] != 0;
+        const unsigned ballot = __ballot_sync(0xffffffffu, act);
+        const unsigned total = __popc(ballot);
+        unsigned long long old = 0ull;
+        pdl_wait();   // scratch and the index list may still be in use by the kernel queued before this one
+        if (lane == 0)
+            old = atomicAdd(cursor64(a), (1ull << 32) | total);
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (act) {
+            int16_t* out = a.idx + (size_t)((unsigned)old + __popc(ballot & ((1u << lane) - 1u))) * 3;
+            out[0] = (int16_t)n;
+            out[1] = (int16_t)bh;
+            out[2] = (int16_t)(bw0 + lane);
+        }
+        if (lane == 0 && (unsigned)(old >> 32) == gridDim.x * gridDim.y * gridDim.z - 1)
+            publish(a, (int)((unsigned)old + total));
+    }
+}
+
 
 template <bool AVG, bool VEC4>
 __global__ void __launch_bounds__(kRmThreads, 3) reduce_mask_band(const RmArgs a)
@@ -192,19 +364,8 @@ __global__ void __launch_bounds__(kRmThreads, 3) reduce_mask_band(const RmArgs a
             if (!AVG) {
                 active = s > 0.0f;
             } else {
-                // |sum in any order - exact sum| <= ~terms * 2^-24 * m; two orders differ by at
-                // most twice that.  A factor-two margin on top covers the rounding of m itself.
                 const float terms = (float)(hEnd - hBeg) * (float)max(wEnd - wBeg, 0);
-                const float rel = terms * 5.9604645e-8f;
-                const float delta = 4.0f * rel * m;   // exactly 0 for an all-zero window
-                const bool yes = __fdiv_rn(s - delta, a.area) > a.tol;
-                const bool no = !(__fdiv_rn(s + delta, a.area) > a.tol);
-                if (rel < 0.125f && m < 3.0e38f && yes)
-                    active = true;
-                else if (rel < 0.125f && m < 3.0e38f && no)
-                    active = false;
-                else
-                    active = block_active_exact<true>(a, n, bh, bw);
+                active = avg_verdict(a, s, m, terms, n, bh, bw);
             }
         } else if (b < nBlk) {
             // a band with no in-range row: empty window => max: inactive; avg: 0/area > tol
@@ -283,10 +444,53 @@ __global__ void __launch_bounds__(kRmThreads) reduce_mask_naive(const RmArgs a)
     }
 }
 
+// Raises the tile kernel's dynamic shared memory limit once per device.
+template <bool AVG> static cudaError_t tile_smem_limit()
+{
+    static bool done[64] = {false};
+    int dev = 0;
+    if (cudaError_t e = cudaGetDevice(&dev))
+        return e;
+    if (dev >= 0 && dev < 64 && done[dev])
+        return cudaSuccess;
+    if (cudaError_t e = cudaFuncSetAttribute(reduce_mask_tile<AVG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kRmTileSmemMax))
+        return e;
+    if (dev >= 0 && dev < 64)
+        done[dev] = true;
+    return cudaSuccess;
+}
+
+// Column tiles per block row for the tile kernel: about `kRmCtasPerSm` CTAs per SM in total, at most
+// 32 block columns per tile, and a tile that fits shared memory.  0: the shape is not eligible.
+static int tile_blocks_for(int N, int H, int W, int bSzH, int bSzW, int bStrW, int bCntH, int bCntW)
+{
+    const long long rows = bSzH < H ? bSzH : H;
+    // widest run of block columns whose pixel span (plus the rounding to 16-byte groups) fits
+    const long long maxCols = kRmTileSmemMax / 4 / rows;
+    long long fit = (maxCols - 9 - bSzW) >= 0 ? (maxCols - 9 - bSzW) / bStrW + 1 : 0;
+    if (fit > kRmTileMaxBlocks)
+        fit = kRmTileMaxBlocks;
+    if (fit < 1)
+        return 0;
+    const long long want = (long long)sm_count() * (options().rmCtasPerSm > 0 ? options().rmCtasPerSm : 8);
+    const long long bands = (long long)bCntH * N;
+    long long tiles = (want + bands / 2) / bands;       // column tiles per band, rounded to nearest
+    if (tiles < 1)
+        tiles = 1;
+    if (tiles > bCntW)
+        tiles = bCntW;
+    long long tb = (bCntW + tiles - 1) / tiles;
+    if (tb > fit)
+        tb = fit;
+    tiles = (bCntW + tb - 1) / tb;
+    return (int)((bCntW + tiles - 1) / tiles);          // equal tiles
+}
+
 cudaError_t launch_reduce_mask(const float* mask, int N, int H, int W, float tol, bool avgpool,
                                int bOffsH, int bOffsW, int bSzH, int bSzW, int bStrH, int bStrW,
                                int bCntH, int bCntW, int16_t* idx, int32_t* scratch,
-                               int32_t* host_count_dev, cudaStream_t stream)
+                               int32_t* host_count_dev, bool maskStable, cudaStream_t stream)
 {
     RmArgs a;
     a.mask = mask, a.idx = idx, a.scratch = scratch, a.host_count = host_count_dev;
@@ -294,14 +498,46 @@ cudaError_t launch_reduce_mask(const float* mask, int N, int H, int W, float tol
     a.bOffsH = bOffsH, a.bOffsW = bOffsW, a.bSzH = bSzH, a.bSzW = bSzW;
     a.bStrH = bStrH, a.bStrW = bStrW, a.bCntH = bCntH, a.bCntW = bCntW;
     a.area = (float)(bSzH * bSzW);
+    a.earlyLoads = maskStable ? 1 : 0;
+
+    const bool vec4 = (W % 4 == 0) && ((reinterpret_cast<uintptr_t>(mask) & 15) == 0);
+    const int tb = vec4 && options().rmKernel == 0
+                       ? tile_blocks_for(N, H, W, bSzH, bSzW, bStrW, bCntH, bCntW) : 0;
+    if (tb >= 1) {
+        a.tileBlocks = tb;
+        const int rows = bSzH < H ? bSzH : H;
+        long long cols = ((long long)(tb - 1) * bStrW + bSzW + 9) & ~3ll;
+        if (cols > W)
+            cols = W;
+        const size_t smem = (size_t)rows * (size_t)cols * 4;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((bCntW + tb - 1) / tb, bCntH, N);
+        cfg.blockDim = dim3((unsigned)((tb * kRmLanesPerBlock + 31) & ~31));
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        // programmatic serialization: this kernel's prologue may overlap the tail of the kernel queued
+        // before it; everything that depends on that kernel sits behind griddepcontrol.wait
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = options().rmPdl ? 1 : 0;
+        if (avgpool) {
+            if (cudaError_t e = tile_smem_limit<true>())
+                return e;
+            return cudaLaunchKernelEx(&cfg, reduce_mask_tile<true>, a);
+        }
+        if (cudaError_t e = tile_smem_limit<false>())
+            return e;
+        return cudaLaunchKernelEx(&cfg, reduce_mask_tile<false>, a);
+    }
 
     // widest run of block columns whose pixel span (plus 4-column rounding) fits the staging area
     const long long spare = (long long)kRmMaxCols - 8 - bSzW;
-    if (spare >= 0) {
+    if (spare >= 0 && options().rmKernel != 2) {
         long long tb = spare / bStrW + 1;
         a.tileBlocks = (int)(tb < bCntW ? tb : bCntW);
         const dim3 grid((bCntW + a.tileBlocks - 1) / a.tileBlocks, bCntH, N);
-        const bool vec4 = (W % 4 == 0) && ((reinterpret_cast<uintptr_t>(mask) & 15) == 0);
         if (avgpool) {
             if (vec4)
                 reduce_mask_band<true, true><<<grid, kRmThreads, 0, stream>>>(a);
@@ -325,6 +561,11 @@ cudaError_t launch_reduce_mask(const float* mask, int N, int H, int W, float tol
             reduce_mask_naive<false><<<grid, kRmThreads, 0, stream>>>(a);
     }
     return cudaGetLastError();
+}
+
+cudaError_t read_rm_wait_timeouts(unsigned int* out)
+{
+    return cudaMemcpyFromSymbol(out, g_rm_wait_timeouts, sizeof(unsigned int));
 }
 
 } // namespace sbnet

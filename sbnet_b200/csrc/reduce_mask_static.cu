@@ -68,12 +68,14 @@ SBNET_EXPORT int sbnet_reduce_mask_static(const float* mask, int N, int H, int W
     char msg[256];
     // The 32-bit cursor kept in the fixed scratch counts candidate blocks; this variant states its
     // limit instead of inheriting the int16 bound of the index triples.
-    const long long candidates = (long long)N * bCntH * bCntW;
-    if (N < 1 || bCntH < 1 || bCntW < 1 || candidates > (long long)SBNET_STATIC_MAX_BLOCKS) {
+    // each factor is bounded first (the int16 index triples allow no more), so the product cannot overflow
+    const bool factorsOk = N >= 1 && bCntH >= 1 && bCntW >= 1 && N <= 32767 && bCntH <= 32767 && bCntW <= 32767;
+    const long long candidates = factorsOk ? (long long)N * bCntH * bCntW : -1;
+    if (!factorsOk || candidates > (long long)SBNET_STATIC_MAX_BLOCKS) {
         snprintf(msg, sizeof(msg),
-                 "ReduceMask (static scratch): N*bCntH*bCntW = %lld candidate blocks is outside 1..%d, "
-                 "the most this entry point's fixed scratch is specified for",
-                 candidates, SBNET_STATIC_MAX_BLOCKS);
+                 "ReduceMask (static scratch): N, bCntH, bCntW = %d, %d, %d must each lie in 1..32767 and their "
+                 "product must not exceed %d, the most this entry point's fixed scratch is specified for",
+                 N, bCntH, bCntW, SBNET_STATIC_MAX_BLOCKS);
         sbnet::set_last_error(msg);
         return SBNET_ERR_INVALID_ARGUMENT;
     }

@@ -14,6 +14,8 @@ LIB_PATH = os.environ.get("SBNET_B200_LIB") or os.path.join(PKG, "libsbnet_b200.
 SBNET_F32, SBNET_F16, SBNET_BF16 = 0, 1, 2
 SBNET_SCRATCH_CLEAN = 1
 SBNET_COUNT_POLL = 2
+SBNET_MASK_STABLE = 4
+SBNET_COUNT_YIELD = 8
 SBNET_REDUCE_MASK_SCRATCH_INTS = 4
 
 _i, _f, _p, _sz = C.c_int, C.c_float, C.c_void_p, C.c_size_t
@@ -33,6 +35,8 @@ SIGNATURES = {
     "sbnet_cuda_timer_start": (_i, [C.POINTER(C.c_int64)]),
     "sbnet_cuda_timer_end": (_i, [C.c_int64, C.POINTER(_f)]),
     "sbnet_wait_timeouts": (_i, [C.POINTER(C.c_uint)]),
+    "sbnet_set_option": (_i, [C.c_char_p, _i]),
+    "sbnet_get_option": (_i, [C.c_char_p, C.POINTER(_i)]),
     "sbnet_reduce_mask_static": (_i, [_p, _i, _i, _i, _f, _i] + _GEOM + [_i, _i, _p, _p, _p, _p]),
 }
 
@@ -66,3 +70,21 @@ def check(status: int) -> None:
     if status < 0:
         raise ValueError(msg)
     raise SbnetError(msg)
+
+
+def set_option(name: str, value: int) -> None:
+    """Sets one of the library's process-wide switches (``sbnet_set_option``)."""
+    check(load().sbnet_set_option(name.encode(), int(value)))
+
+
+def get_option(name: str) -> int:
+    out = _i(0)
+    check(load().sbnet_get_option(name.encode(), C.byref(out)))
+    return out.value
+
+
+def wait_timeouts() -> int:
+    """Bounded device-side waits that gave up since the library was loaded (0 in a healthy process)."""
+    out = C.c_uint(0)
+    check(load().sbnet_wait_timeouts(C.byref(out)))
+    return out.value

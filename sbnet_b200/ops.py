@@ -71,6 +71,59 @@ def _require_cuda(t: torch.Tensor, name: str) -> None:
         raise ValueError(f"{name} must be contiguous")
 
 
+def _check_mask(mask: torch.Tensor):
+    """Shape / dtype rules of the ReduceMask input (``sbnet_ops/reduce_mask.cc:140-143``); device-free,
+    so they can be exercised without a GPU.  Returns (N, H, W)."""
+    if mask.dtype != torch.float32:
+        raise ValueError("mask must be float32")
+    if mask.dim() not in (3, 4) or (mask.dim() == 4 and mask.shape[3] != 1):
+        raise ValueError("mask must be [N,H,W,1]")
+    if not mask.is_contiguous():
+        raise ValueError("mask must be contiguous")
+    return mask.shape[0], mask.shape[1], mask.shape[2]
+
+
+def _check_indices(active_block_indices: torch.Tensor, rows: int) -> None:
+    """``active_block_indices`` is int16 ``[>= rows, 3]``, contiguous: every kernel reads ``rows`` triples."""
+    a = active_block_indices
+    if a.dtype != torch.int16:
+        raise ValueError("active_block_indices must be int16")
+    if a.dim() != 2 or a.shape[1] != 3 or not a.is_contiguous():
+        raise ValueError("active_block_indices must be a contiguous [numBlocks, 3] tensor")
+    if a.shape[0] < rows:
+        raise ValueError(f"active_block_indices holds {a.shape[0]} rows, the call reads {rows}")
+
+
+def _check_image(t: torch.Tensor, name: str):
+    if t.dim() != 4:  # sparse_gather.cc:164, :327
+        raise ValueError(f"{name} must be rank 4")
+    if t.dtype not in _DTYPES:
+        raise ValueError(f"unsupported dtype {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    return tuple(t.shape)
+
+
+def _check_stack(t: torch.Tensor, name: str, blocks: int, block_elems: int, like: torch.Tensor) -> None:
+    """A block stack (gather output / scatter input): same dtype and device as the image, contiguous,
+    room for ``blocks`` blocks of ``block_elems`` elements."""
+    if t.dtype != like.dtype:
+        raise ValueError(f"{name} and the image tensor must share a dtype, got {t.dtype} and {like.dtype}")
+    if t.device != like.device:
+        raise ValueError(f"{name} and the image tensor must live on one device")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if t.numel() < blocks * block_elems:
+        raise ValueError(f"{name} holds {t.numel()} elements, the call needs {blocks * block_elems}")
+
+
+def _check_count_dev(count_dev: torch.Tensor, like: torch.Tensor) -> None:
+    if not isinstance(count_dev, torch.Tensor) or count_dev.dtype != torch.int32 or count_dev.numel() < 1:
+        raise ValueError("count_dev must be an int32 tensor with at least one element")
+    if count_dev.device != like.device:
+        raise ValueError("count_dev must live on the device of the tensors")
+
+
 def _count(bin_counts) -> int:
     if isinstance(bin_counts, torch.Tensor):
         if bin_counts.is_cuda:
@@ -95,30 +148,30 @@ def _pinned_count() -> torch.Tensor:
     return slab[used:used + 1]
 
 
+_SLOTS = 1024
+
+
 def scratch_for(device, stream: int) -> tuple:
-    """Per (device, stream) reduce_mask scratch, zero-filled once; later calls pass SCRATCH_CLEAN."""
+    """A fresh, zero-filled reduce_mask scratch slot (4 int32, 16-byte aligned) for ``(device, stream)``
+    and the flag that says so.  Slots come from a slab of 1,024 that is zero-filled once on that stream;
+    every slot is handed out once, so word 0 -- where the kernel publishes the count -- stays an
+    independent device-side count for as long as the caller keeps the returned view (two results in
+    flight on one stream never alias).  A slab is released when the last view of it is gone."""
     key = (device.index if isinstance(device, torch.device) else torch.device(device).index, stream)
     hit = _scratch.get(key)
-    if hit is None:
-        buf = torch.zeros(_lib.SBNET_REDUCE_MASK_SCRATCH_INTS, dtype=torch.int32, device=device)
-        _scratch[key] = buf
-        return buf, 0
-    return hit, _lib.SBNET_SCRATCH_CLEAN
+    if hit is None or hit[1] >= _SLOTS:
+        hit = [torch.zeros(_SLOTS * _lib.SBNET_REDUCE_MASK_SCRATCH_INTS, dtype=torch.int32, device=device), 0]
+        _scratch[key] = hit
+    k = hit[1]
+    hit[1] = k + 1
+    n = _lib.SBNET_REDUCE_MASK_SCRATCH_INTS
+    return hit[0][k * n:(k + 1) * n], _lib.SBNET_SCRATCH_CLEAN
 
 
-def reduce_mask(mask: torch.Tensor, dynamic_bcount: Sequence[int], dynamic_bsize: Sequence[int],
-                dynamic_bstride: Sequence[int], dynamic_boffset: Sequence[int], tol: float,
-                avgpool: bool = False) -> ReduceMaskResult:
-    """``ReduceMask``: pools ``mask`` ([N,H,W,1] or [N,H,W] fp32) per block and lists the active blocks.
-
-    Returns ``(active_block_indices, bin_counts)``; ``bin_counts`` is a pinned host tensor whose value
-    is final when the call returns (the op interface requires the count on the host)."""
+def _reduce_mask_call(mask, dynamic_bcount, dynamic_bsize, dynamic_bstride, dynamic_boffset, tol, avgpool,
+                      counts, flags):
     _require_cuda(mask, "mask")
-    if mask.dtype != torch.float32:
-        raise ValueError("mask must be float32")
-    if mask.dim() == 4 and mask.shape[3] != 1 or mask.dim() not in (3, 4):
-        raise ValueError("mask must be [N,H,W,1]")
-    N, H, W = mask.shape[0], mask.shape[1], mask.shape[2]
+    N, H, W = _check_mask(mask)
     bch, bcw = _pair(dynamic_bcount, "dynamic_bcount")
     bsh, bsw = _pair(dynamic_bsize, "dynamic_bsize")
     bth, btw = _pair(dynamic_bstride, "dynamic_bstride")
@@ -126,33 +179,55 @@ def reduce_mask(mask: torch.Tensor, dynamic_bcount: Sequence[int], dynamic_bsize
     with _on(mask.device):
         stream = _stream(mask.device)
         idx = torch.empty((max(N * bch * bcw, 0), 3), dtype=torch.int16, device=mask.device)
-        counts = _pinned_count()
-        scratch, flags = scratch_for(mask.device, stream)
+        scratch, clean = scratch_for(mask.device, stream)
         _lib.check(_lib.load().sbnet_reduce_mask(
             mask.data_ptr(), N, H, W, float(tol), int(bool(avgpool)), boh, bow, bsh, bsw, bth, btw,
-            bch, bcw, idx.data_ptr(), scratch.data_ptr(), counts.data_ptr(), flags | _lib.SBNET_COUNT_POLL, stream))
+            bch, bcw, idx.data_ptr(), scratch.data_ptr(), None if counts is None else counts.data_ptr(),
+            flags | clean, stream))
+    return idx, scratch[:1]
+
+
+def reduce_mask(mask: torch.Tensor, dynamic_bcount: Sequence[int], dynamic_bsize: Sequence[int],
+                dynamic_bstride: Sequence[int], dynamic_boffset: Sequence[int], tol: float,
+                avgpool: bool = False, mask_stable: bool = False, yield_core: bool = False) -> ReduceMaskResult:
+    """``ReduceMask``: pools ``mask`` ([N,H,W,1] or [N,H,W] fp32) per block and lists the active blocks.
+
+    Returns ``(active_block_indices, bin_counts)``; ``bin_counts`` is a pinned host tensor whose value
+    is final when the call returns (the op interface requires the count on the host).
+    ``mask_stable=True`` promises that the mask is not written by the operation queued just before this
+    call on the current stream, which lets the kernel read it while that operation drains
+    (``SBNET_MASK_STABLE``); ``yield_core=True`` makes the wait for the count give its core away between
+    looks (``SBNET_COUNT_YIELD``: one process per GPU on shared cores)."""
+    _require_cuda(mask, "mask")   # before the pinned slot: a host mask must fail as an argument error
+    counts = _pinned_count()
+    flags = _lib.SBNET_COUNT_POLL | (_lib.SBNET_MASK_STABLE if mask_stable else 0) \
+        | (_lib.SBNET_COUNT_YIELD if yield_core else 0)
+    idx, _ = _reduce_mask_call(mask, dynamic_bcount, dynamic_bsize, dynamic_bstride, dynamic_boffset, tol,
+                               avgpool, counts, flags)
     return ReduceMaskResult(idx, counts)
 
 
+def reduce_mask_with_device_count(mask, dynamic_bcount, dynamic_bsize, dynamic_bstride, dynamic_boffset, tol,
+                                  avgpool=False, mask_stable=False, yield_core=False):
+    """:func:`reduce_mask` that also returns the count as a one-element device tensor (for a count
+    exchange between ranks, or for the ``*_dyn`` calls): ``(active_block_indices, bin_counts, count_dev)``."""
+    _require_cuda(mask, "mask")   # before the pinned slot: a host mask must fail as an argument error
+    counts = _pinned_count()
+    flags = _lib.SBNET_COUNT_POLL | (_lib.SBNET_MASK_STABLE if mask_stable else 0) \
+        | (_lib.SBNET_COUNT_YIELD if yield_core else 0)
+    idx, count_dev = _reduce_mask_call(mask, dynamic_bcount, dynamic_bsize, dynamic_bstride, dynamic_boffset,
+                                       tol, avgpool, counts, flags)
+    return idx, counts, count_dev
+
+
 def reduce_mask_async(mask, dynamic_bcount, dynamic_bsize, dynamic_bstride, dynamic_boffset, tol,
-                      avgpool=False):
+                      avgpool=False, mask_stable=False):
     """Same as :func:`reduce_mask` but never touches the host: returns ``(active_block_indices,
-    count_dev)`` where ``count_dev`` is a device int32 view holding the count in stream order, for
-    the ``*_dyn`` gather / scatter calls."""
-    _require_cuda(mask, "mask")
-    N, H, W = mask.shape[0], mask.shape[1], mask.shape[2]
-    bch, bcw = _pair(dynamic_bcount, "dynamic_bcount")
-    bsh, bsw = _pair(dynamic_bsize, "dynamic_bsize")
-    bth, btw = _pair(dynamic_bstride, "dynamic_bstride")
-    boh, bow = _pair(dynamic_boffset, "dynamic_boffset")
-    with _on(mask.device):
-        stream = _stream(mask.device)
-        idx = torch.empty((N * bch * bcw, 3), dtype=torch.int16, device=mask.device)
-        scratch, flags = scratch_for(mask.device, stream)
-        _lib.check(_lib.load().sbnet_reduce_mask(
-            mask.data_ptr(), N, H, W, float(tol), int(bool(avgpool)), boh, bow, bsh, bsw, bth, btw,
-            bch, bcw, idx.data_ptr(), scratch.data_ptr(), None, flags, stream))
-    return idx, scratch[:1]
+    count_dev)`` where ``count_dev`` is a one-element device int32 tensor that holds the count in stream
+    order, for the ``*_dyn`` gather / scatter calls.  Every call gets a count word of its own, so results
+    of several calls may be outstanding at once."""
+    return _reduce_mask_call(mask, dynamic_bcount, dynamic_bsize, dynamic_bstride, dynamic_boffset, tol,
+                             avgpool, None, _lib.SBNET_MASK_STABLE if mask_stable else 0)
 
 
 def _geom(dynamic_bsize, dynamic_bstride, dynamic_boffset):
@@ -167,15 +242,15 @@ def sparse_gather(x: torch.Tensor, bin_counts, active_block_indices: torch.Tenso
     """``SparseGather``: ``[bin_counts[0], bSzH, bSzW, C]``, or ``[bin_counts[0], C, bSzH, bSzW]`` when
     ``transpose``; pixels outside ``x`` read as zero."""
     _require_cuda(x, "x")
-    if x.dim() != 4:  # sparse_gather.cc:164
-        raise ValueError("x must be rank 4")
-    if x.dtype not in _DTYPES:
-        raise ValueError(f"unsupported dtype {x.dtype}")
     _require_cuda(active_block_indices, "active_block_indices")
-    N, H, W, Cc = x.shape
+    N, H, W, Cc = _check_image(x, "x")
     g = _geom(dynamic_bsize, dynamic_bstride, dynamic_boffset)
     nb = _count(bin_counts)
+    _check_indices(active_block_indices, nb)
     shape = (nb, Cc, g[2], g[3]) if transpose else (nb, g[2], g[3], Cc)
+    if out is not None:
+        _require_cuda(out, "out")
+        _check_stack(out, "out", nb, g[2] * g[3] * Cc, x)
     with _on(x.device):
         y = out if out is not None else torch.empty(shape, dtype=x.dtype, device=x.device)
         _lib.check(_lib.load().sbnet_sparse_gather(
@@ -192,13 +267,11 @@ def sparse_scatter_var(x: torch.Tensor, bin_counts, active_block_indices: torch.
     _require_cuda(x, "x")
     _require_cuda(ybase, "ybase")
     _require_cuda(active_block_indices, "active_block_indices")
-    if ybase.dim() != 4:  # sparse_gather.cc:327
-        raise ValueError("ybase must be rank 4")
-    if ybase.dtype not in _DTYPES or x.dtype != ybase.dtype:
-        raise ValueError("x and ybase must share a supported dtype")
-    N, H, W, Cc = ybase.shape
+    N, H, W, Cc = _check_image(ybase, "ybase")
     g = _geom(dynamic_bsize, dynamic_bstride, dynamic_boffset)
     nb = _count(bin_counts)
+    _check_indices(active_block_indices, nb)
+    _check_stack(x, "x", nb, g[2] * g[3] * Cc, ybase)
     if x.numel() != nb * g[2] * g[3] * Cc:
         raise ValueError("x must hold bin_counts[0]*bsize[0]*bsize[1]*C elements")
     with _on(ybase.device):
@@ -241,9 +314,16 @@ def sparse_gather_dyn(x, count_dev: torch.Tensor, max_blocks: int, active_block_
     """Gather with the block count read on the device (no host synchronisation).  The result has
     room for ``max_blocks`` blocks; only the first ``count_dev[0]`` are written."""
     _require_cuda(x, "x")
-    N, H, W, Cc = x.shape
+    _require_cuda(active_block_indices, "active_block_indices")
+    N, H, W, Cc = _check_image(x, "x")
     g = _geom(dynamic_bsize, dynamic_bstride, dynamic_boffset)
+    max_blocks = int(max_blocks)
+    _check_count_dev(count_dev, x)
+    _check_indices(active_block_indices, max_blocks)
     shape = (max_blocks, Cc, g[2], g[3]) if transpose else (max_blocks, g[2], g[3], Cc)
+    if out is not None:
+        _require_cuda(out, "out")
+        _check_stack(out, "out", max_blocks, g[2] * g[3] * Cc, x)
     with _on(x.device):
         y = out if out is not None else torch.empty(shape, dtype=x.dtype, device=x.device)
         _lib.check(_lib.load().sbnet_sparse_gather_dyn(
@@ -256,9 +336,16 @@ def sparse_gather_dyn(x, count_dev: torch.Tensor, max_blocks: int, active_block_
 def sparse_scatter_var_dyn(x, count_dev: torch.Tensor, max_blocks: int, active_block_indices, ybase,
                            dynamic_bsize, dynamic_bstride, dynamic_boffset, add, atomic=False,
                            transpose=False):
+    """Scatter with the block count read on the device; ``x`` has room for ``max_blocks`` blocks."""
     _require_cuda(ybase, "ybase")
-    N, H, W, Cc = ybase.shape
+    _require_cuda(x, "x")
+    _require_cuda(active_block_indices, "active_block_indices")
+    N, H, W, Cc = _check_image(ybase, "ybase")
     g = _geom(dynamic_bsize, dynamic_bstride, dynamic_boffset)
+    max_blocks = int(max_blocks)
+    _check_count_dev(count_dev, ybase)
+    _check_indices(active_block_indices, max_blocks)
+    _check_stack(x, "x", max_blocks, g[2] * g[3] * Cc, ybase)
     with _on(ybase.device):
         _lib.check(_lib.load().sbnet_sparse_scatter_dyn(
             x.data_ptr(), _DTYPES[ybase.dtype], N, H, W, Cc, ybase.data_ptr(), *g, int(max_blocks),

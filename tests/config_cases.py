@@ -4,7 +4,9 @@ Same generators, geometries, dtypes and flag combinations as the full-size confi
 (sbnet_b200/configs.py), smaller tensors.  ``run(ops, name)`` pushes one case through any
 implementation of the reference op interface (numpy in, numpy out) and returns the arrays to compare
 plus their digests.  Arrays listed in ``tol`` come from atomic adds over overlapping halos, whose
-floating-point add order is schedule dependent; every other array must match bit for bit.
+floating-point add order is schedule dependent: they are held to the fp64 exact-sum bars
+(``tests/atomic_check.py``) from the inputs returned under ``atomic``; every other array must match
+bit for bit.
 """
 from __future__ import annotations
 
@@ -72,7 +74,8 @@ def _c4a(ops, density):
     yv = base.copy()
     yv = ops.sparse_scatter_var(stack, cnt, idx, yv, g.bsize, g.bstride, g.boffset, add=True,
                                 atomic=True, transpose=False)
-    return dict(y=y, y_var=yv), ("y", "y_var")
+    # the inputs of the accumulation, for the exact-sum check of the order-dependent arrays
+    return dict(y=y, y_var=yv), ("y", "y_var"), dict(stack=stack, count=cnt, indices=idx, base=base, geom=g)
 
 
 def _c4b(ops, density):
@@ -118,6 +121,7 @@ NAMES = list(_CASES)
 
 
 def run(ops, name):
-    arrays, tol = _CASES[name](ops)
-    return dict(arrays=arrays, tol=tuple(tol),
+    res = _CASES[name](ops)
+    arrays, tol = res[0], res[1]
+    return dict(arrays=arrays, tol=tuple(tol), atomic=res[2] if len(res) > 2 else None,
                 digests={k: pipeline.digest(v) for k, v in arrays.items()})

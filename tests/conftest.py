@@ -8,6 +8,24 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 
+import contextlib
+
+
+@contextlib.contextmanager
+def library_options(**values):
+    """Sets process-wide switches of the CUDA library (``sbnet_set_option``) for the duration of a
+    block and puts the previous values back."""
+    from sbnet_b200 import lib
+    saved = {k: lib.get_option(k) for k in values}
+    try:
+        for k, v in values.items():
+            lib.set_option(k, v)
+        yield
+    finally:
+        for k, v in saved.items():
+            lib.set_option(k, v)
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
 

@@ -2,7 +2,7 @@
 
 Run in a container where the reference tree is mounted:
 
-    make -C oracle ref && python tests/golden/make_golden.py
+    python -c "from oracle import oracle; oracle.build(ref=True)" && python tests/golden/make_golden.py
 
 For every case of tests/ref_cases.py that is not marked ``big`` it runs
 reduce_mask -> sparse_gather -> sparse_scatter[_var] through oracle/_ref/libsbnet_ref.so (the

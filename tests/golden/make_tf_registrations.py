@@ -1,7 +1,7 @@
 """Extracts the op and GPU-kernel registrations from the reference's sources into
 tests/golden/tf_registrations.json (op name -> attrs / inputs / outputs / GPU host-memory arguments).
 
-    python tests/golden/make_tf_registrations.py [reference sbnet_ops directory]
+    python tests/golden/make_tf_registrations.py <reference tree>/sbnet_tensorflow/sbnet_ops
 
 The TensorFlow binding of this repository must register exactly these interfaces
 (tests/test_tf_shim.py); the one deliberate difference, `half` added to T, is applied by the test."""
@@ -32,7 +32,9 @@ def parse(src_dir):
 
 
 if __name__ == "__main__":
-    src = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/sbnet_tensorflow/sbnet_ops"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_tf_registrations.py <reference tree>/sbnet_tensorflow/sbnet_ops")
+    src = sys.argv[1]
     out = parse(src)
     with open(os.path.join(HERE, "tf_registrations.json"), "w") as f:
         json.dump(out, f, indent=1, sort_keys=True)

@@ -60,14 +60,10 @@ def test_bf16_gather_and_scatter(cuda_ops, oracle_port, shape, transpose):
                                        transpose=transpose)
     o = cuda_ops.sparse_scatter_var(stack, cnt, idx, base.copy(), bsize, bstride, boffset, add=True, atomic=True,
                                     transpose=transpose)
-    # tolerance: bfloat16 keeps 8 significant bits, so one add rounds by at most 2^-8 (3.9e-3) of
-    # the partial sum; per addend, relative to |base| + sum of |addends| (which bounds every
-    # partial sum whatever the arrival order), doubled because the checker rounds as well
-    cover = -(-bsize[0] // bstride[0]) * -(-bsize[1] // bstride[1])
-    mag = oracle_port.sparse_scatter_var(np.abs(stack.astype(np.float32)), cnt, idx, np.abs(base.astype(np.float32)),
-                                         bsize, bstride, boffset, add=True, atomic=True, transpose=transpose)
-    err = np.abs(o.astype(np.float64) - e.astype(np.float64)) / np.maximum(mag.astype(np.float64), 1.0)
-    assert err.max() <= 2.0 ** -7 * cover, err.max()
+    # bfloat16 keeps 8 significant bits: one add rounds by at most 2^-8 of the partial sum; both results
+    # within k such roundings of the fp64 sum
+    from atomic_check import check_atomic_add
+    check_atomic_add({"cuda": o, "cpu checker": e}, stack, cnt, idx, base, bsize, bstride, boffset, transpose)
 
 
 def test_bf16_subnormal_addends_are_not_flushed(cuda_ops, oracle_port):

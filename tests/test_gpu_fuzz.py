@@ -8,6 +8,7 @@ import numpy as np
 import pytest
 
 from sbnet_b200 import configs as cfg
+from atomic_check import check_atomic_add
 
 pytestmark = pytest.mark.gpu
 
@@ -44,7 +45,6 @@ def test_random_geometry(cuda_ops, oracle_port, seed):
     base = cfg.normal((N, H, W, C), seed + 1, dtype)
     disjoint = bstride[0] >= bsize[0] and bstride[1] >= bsize[1]
     cover = -(-bsize[0] // bstride[0]) * -(-bsize[1] // bstride[1])
-    rtol = (1e-6 if dtype == np.float32 else 1e-3) * (1 + cover)
     for transpose in (False, True):
         exp = oracle_port.sparse_gather(x, cnt, idx, bsize, bstride, boffset, transpose=transpose)
         got = cuda_ops.sparse_gather(x, cnt, idx, bsize, bstride, boffset, transpose=transpose)
@@ -58,12 +58,7 @@ def test_random_geometry(cuda_ops, oracle_port, seed):
                                            atomic=True, transpose=transpose)
         o = cuda_ops.sparse_scatter_var(stack, cnt, idx, base.copy(), bsize, bstride, boffset, add=True,
                                         atomic=True, transpose=transpose)
-        # relative to |base| + sum of |addends|, which bounds every partial sum whatever the arrival order
-        mag = oracle_port.sparse_scatter_var(np.abs(stack).astype(np.float32), cnt, idx,
-                                             np.abs(base).astype(np.float32), bsize, bstride, boffset, add=True,
-                                             atomic=True, transpose=transpose)
-        err = np.abs(o.astype(np.float64) - e.astype(np.float64)) / np.maximum(mag.astype(np.float64), 1.0)
-        assert err.max() <= rtol, (err.max(), rtol)
+        check_atomic_add({"cuda": o, "cpu checker": e}, stack, cnt, idx, base, bsize, bstride, boffset, transpose)
         if disjoint:
             e = oracle_port.sparse_scatter_var(stack, cnt, idx, base.copy(), bsize, bstride, boffset, add=True,
                                                transpose=transpose)
@@ -91,7 +86,6 @@ def _draw_tile(seed):
 
 @pytest.mark.parametrize("seed", range(60))
 def test_random_tile_shapes(cuda_ops, oracle_port, seed):
-    import os
     N, H, W, C, bsize, bstride, boffset, kind, pack = _draw_tile(seed)
     if kind == 2:
         ml_dtypes = pytest.importorskip("ml_dtypes")
@@ -107,9 +101,8 @@ def test_random_tile_shapes(cuda_ops, oracle_port, seed):
     stack = cfg.normal((nb, C, *bsize), seed + 2, dtype)
     disjoint = bstride[0] >= bsize[0] and bstride[1] >= bsize[1]
     cover = -(-bsize[0] // bstride[0]) * -(-bsize[1] // bstride[1])
-    saved = os.environ.get("SBNET_TILE_BLOCKS")
-    os.environ["SBNET_TILE_BLOCKS"] = pack
-    try:
+    from conftest import library_options
+    with library_options(tile_blocks=int(pack)):
         exp = oracle_port.sparse_gather(x, cnt, idx, bsize, bstride, boffset, transpose=True)
         got = cuda_ops.sparse_gather(x, cnt, idx, bsize, bstride, boffset, transpose=True)
         np.testing.assert_array_equal(got.view(bits), exp.view(bits))
@@ -126,13 +119,4 @@ def test_random_tile_shapes(cuda_ops, oracle_port, seed):
                                            transpose=True)
         o = cuda_ops.sparse_scatter_var(stack, cnt, idx, base.copy(), bsize, bstride, boffset, add=True, atomic=True,
                                         transpose=True)
-        mag = oracle_port.sparse_scatter_var(np.abs(stack.astype(np.float32)), cnt, idx,
-                                             np.abs(base.astype(np.float32)), bsize, bstride, boffset, add=True,
-                                             atomic=True, transpose=True)
-        err = np.abs(o.astype(np.float64) - e.astype(np.float64)) / np.maximum(mag.astype(np.float64), 1.0)
-        assert err.max() <= rtol1 * (1 + cover), (err.max(), rtol1, cover)
-    finally:
-        if saved is None:
-            os.environ.pop("SBNET_TILE_BLOCKS", None)
-        else:
-            os.environ["SBNET_TILE_BLOCKS"] = saved
+        check_atomic_add({"cuda": o, "cpu checker": e}, stack, cnt, idx, base, bsize, bstride, boffset, True)

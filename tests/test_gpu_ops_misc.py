@@ -8,11 +8,7 @@ from sbnet_b200 import configs as cfg
 pytestmark = pytest.mark.gpu
 
 
-def _tol_check(got, exp, dtype, addends):
-    rtol = (1e-6 if dtype == np.float32 else 1e-3) * addends
-    g, e = got.astype(np.float64), exp.astype(np.float64)
-    err = np.abs(g - e) / np.maximum(np.abs(e), 1.0)
-    assert err.max() <= rtol, err.max()
+from atomic_check import check_atomic_add
 
 
 # channel counts chosen to hit every vector width: C*sizeof(T) in {2,4,6,8,12,14,16,30,48,...}
@@ -38,7 +34,7 @@ def test_mode_matrix(cuda_ops, oracle_port, dtype, C, transpose):
                                        atomic=True, transpose=transpose)
     o = cuda_ops.sparse_scatter_var(stack, cnt, idx, base.copy(), bsize, bstride, boffset, add=True,
                                     atomic=True, transpose=transpose)
-    _tol_check(o, e, dtype, 3)
+    check_atomic_add({"cuda": o, "cpu checker": e}, stack, cnt, idx, base, bsize, bstride, boffset, transpose)
     # overwrite with equal values on shared pixels (a gathered stack)
     e = oracle_port.sparse_scatter(exp, cnt, idx, base, bsize, bstride, boffset, add=False, transpose=transpose)
     o = cuda_ops.sparse_scatter(exp, cnt, idx, base, bsize, bstride, boffset, add=False, transpose=transpose)

@@ -2,12 +2,12 @@
 multiple of 128 bytes, blocks of at most 384 pixels), the wider set the tile CTAs take (partial
 channel chunks, blocks of any size cut into pixel chunks) and shapes outside both, against the CPU
 checker; the general kernels are run on the same inputs by switching the others off."""
-import os
 
 import numpy as np
 import pytest
 
 from sbnet_b200 import configs as cfg
+from atomic_check import check_atomic_add
 
 pytestmark = pytest.mark.gpu
 
@@ -64,21 +64,10 @@ def tma_off(request):
     """Selects which plane-layout implementation takes the call: the default dispatch (tile CTAs,
     gathers fed by TMA), the tile CTAs with plain loads, the persistent TMA pipeline, or the general
     kernel."""
-    saved = {k: os.environ.get(k) for k in ("SBNET_DISABLE_TMA", "SBNET_PLANES")}
-    os.environ.pop("SBNET_DISABLE_TMA", None)
-    os.environ.pop("SBNET_PLANES", None)
-    if request.param == "general":
-        os.environ["SBNET_DISABLE_TMA"] = "1"
-    elif request.param == "tma_pipeline":
-        os.environ["SBNET_PLANES"] = "tma"
-    elif request.param == "tile_ctas":
-        os.environ["SBNET_PLANES"] = "tile"
-    yield request.param
-    for k, v in saved.items():
-        if v is None:
-            os.environ.pop(k, None)
-        else:
-            os.environ[k] = v
+    from conftest import library_options
+    planes = {"default": 0, "general": 0, "tma_pipeline": 1, "tile_ctas": 2}[request.param]
+    with library_options(planes=planes, disable_tma=int(request.param == "general"), tile_blocks=0):
+        yield request.param
 
 
 @pytest.mark.parametrize("shape", SHAPES, ids=_ids())
@@ -117,15 +106,8 @@ def _run_shape(cuda_ops, oracle_port, shape):
                                        atomic=True, transpose=True)
     o = cuda_ops.sparse_scatter_var(stack, cnt, idx, base.copy(), bsize, bstride, boffset, add=True,
                                     atomic=True, transpose=True)
-    # tolerance: 1e-6 (fp32) / 1e-3 (fp16) per addend, relative to the magnitude of what is summed
-    # (|base| + sum of |addends|: every partial sum, whose rounding the arrival order decides, is
-    # bounded by it even when the final value cancels); a pixel receives one addend per covering block
-    cover = -(-bsize[0] // bstride[0]) * -(-bsize[1] // bstride[1])
-    rtol = (1e-6 if dtype == np.float32 else 1e-3) * (1 + cover)
-    mag = oracle_port.sparse_scatter_var(np.abs(stack).astype(np.float32), cnt, idx, np.abs(base).astype(np.float32),
-                                         bsize, bstride, boffset, add=True, atomic=True, transpose=True)
-    err = np.abs(o.astype(np.float64) - e.astype(np.float64)) / np.maximum(mag.astype(np.float64), 1.0)
-    assert err.max() <= rtol, err.max()
+    # both results within k rounded additions of the fp64 sum; relative bars where nothing cancels
+    check_atomic_add({"cuda": o, "cpu checker": e}, stack, cnt, idx, base, bsize, bstride, boffset, True)
 
 
 @pytest.mark.parametrize("dtype", [np.float32, np.float16])
@@ -159,9 +141,7 @@ def test_device_count_calls_on_blocks_above_384_pixels(cuda_ops, dtype):
                                     transpose=True)
         torch.cuda.synchronize()
         if add:   # overlapping halos: arrival order differs between the two runs
-            tol = (1e-6 if dtype == np.float32 else 1e-3) * 5
-            err = ((y1.double() - y2.double()).abs() / y2.double().abs().clamp(min=1.0)).max().item()
-            assert err <= tol, err
+            check_atomic_add({"device count": y1, "host count": y2}, src, cnt_h, idx_h, base, bsize, bstride, boffset, True)
         else:
             assert torch.equal(y1, y2)
 
@@ -191,21 +171,9 @@ SMALL_BLOCKS = [
 def test_several_blocks_per_tile(cuda_ops, oracle_port, shape, blocks_per_tile, gather_loads):
     """``plain``: the plain-load kernels of the tile CTAs; ``tma``: the default dispatch, whose gather
     feeds the shared tile with one TMA load per block where it can."""
-    saved = {k: os.environ.get(k) for k in ("SBNET_TILE_BLOCKS", "SBNET_PLANES", "SBNET_DISABLE_TMA")}
-    os.environ["SBNET_TILE_BLOCKS"] = blocks_per_tile
-    if gather_loads == "plain":
-        os.environ["SBNET_PLANES"] = "tile"
-    else:
-        os.environ.pop("SBNET_PLANES", None)
-    os.environ.pop("SBNET_DISABLE_TMA", None)
-    try:
+    from conftest import library_options
+    with library_options(tile_blocks=int(blocks_per_tile), planes=2 if gather_loads == "plain" else 0, disable_tma=0):
         _run_shape(cuda_ops, oracle_port, shape)
-    finally:
-        for k, v in saved.items():
-            if v is None:
-                os.environ.pop(k, None)
-            else:
-                os.environ[k] = v
 
 
 def test_several_blocks_per_tile_chosen_by_launch_size(cuda_ops, oracle_port):
@@ -265,10 +233,7 @@ def test_device_count_gather_outside_the_pipeline(cuda_ops, case):
 
 
 def test_no_bounded_wait_gave_up(cuda_ops):
-    import ctypes as C
     import torch
     from sbnet_b200 import lib
     torch.cuda.synchronize()
-    n = C.c_uint(99)
-    lib.check(lib.load().sbnet_wait_timeouts(C.byref(n)))
-    assert n.value == 0
+    assert lib.wait_timeouts() == 0

@@ -7,6 +7,21 @@ from sbnet_b200 import configs as cfg
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True, params=["tile", "tile_many_ctas", "tile_few_ctas", "tile_no_pdl", "band", "per_block"])
+def rm_kernel(request):
+    """Every case runs through each reduce_mask kernel: the TMA-fed tile kernel (default column
+    tiling, the narrowest and the widest tiles, and without programmatic serialization), the
+    register-fed band kernel, and the one-thread-per-block kernel."""
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from conftest import library_options
+    opts = {"tile": {}, "tile_many_ctas": {"rm_ctas_per_sm": 10000}, "tile_few_ctas": {"rm_ctas_per_sm": 1},
+            "tile_no_pdl": {"rm_pdl": 0}, "band": {"rm_kernel": 1}, "per_block": {"rm_kernel": 2}}[request.param]
+    with library_options(**{"rm_kernel": 0, "rm_ctas_per_sm": 8, "rm_pdl": 1, **opts}):
+        yield request.param
+
+
 def _sets_equal(cuda_ops, oracle_port, mask, g, tol, avg):
     gi, gc = cuda_ops.reduce_mask(mask, *g.as_lists(), tol=tol, avgpool=avg)
     oi, oc = oracle_port.reduce_mask(mask, *g.as_lists(), tol=tol, avgpool=avg)
@@ -128,11 +143,13 @@ def test_pageable_count_host(cuda_ops):
     assert scratch.cpu().tolist() == [32, 0, 0, 0]
 
 
-def test_two_thousand_calls_on_one_self_resetting_scratch(cuda_ops):
-    """The scratch word is zero-filled once and then only reset by the kernel itself; alternate
-    masks of different counts for many calls (polled and device-side counts) and check each one."""
+def test_two_thousand_calls_on_self_resetting_scratch(cuda_ops):
+    """A scratch slot is zero-filled once and then only reset by the kernel itself.  Alternate masks
+    of different counts for many calls: through the op wrappers (polled and device-side counts, each
+    call on a fresh slot of a slab) and through the raw entry point on ONE slot for every call."""
+    import ctypes as C
     import torch
-    from sbnet_b200 import ops
+    from sbnet_b200 import lib, ops
     g = cfg.halo_geom(160, 176)
     masks_h = [cfg.rect_union_mask(2, 160, 176, seed=s, n_rects=k) for s, k in ((1, 3), (2, 12), (3, 0), (4, 30))]
     masks = [torch.from_numpy(m).cuda() for m in masks_h]
@@ -152,7 +169,44 @@ def test_two_thousand_calls_on_one_self_resetting_scratch(cuda_ops):
         assert got == expect[k], (i, k, got, expect[k])
     torch.cuda.synchronize()
     stream = torch.cuda.current_stream().cuda_stream
-    assert ops.scratch_for(masks[0].device, stream)[0].cpu().tolist()[2:] == [0, 0]
+    slab = ops._scratch[(masks[0].device.index, stream)][0].cpu().view(-1, 4)
+    assert int(slab[:, 2:].abs().sum()) == 0          # every cursor word was left at zero
+    # the raw entry point, one caller-owned slot reused by every call
+    scratch = torch.zeros(4, dtype=torch.int32, device="cuda")
+    idx = torch.zeros((2 * g.bcount[0] * g.bcount[1], 3), dtype=torch.int16, device="cuda")
+    out = C.c_int32(0)
+    for i in range(600):
+        k = (i * 5 + i // 7) % 4
+        rc = lib.load().sbnet_reduce_mask(masks[k].data_ptr(), 2, 160, 176, 0.5, 0, g.boffset[0], g.boffset[1],
+                                          g.bsize[0], g.bsize[1], g.bstride[0], g.bstride[1], g.bcount[0],
+                                          g.bcount[1], idx.data_ptr(), scratch.data_ptr(), C.addressof(out),
+                                          lib.SBNET_SCRATCH_CLEAN | (lib.SBNET_MASK_STABLE if i % 2 else 0), stream)
+        assert rc == 0 and out.value == expect[k], (i, k, rc, out.value)
+    assert scratch.cpu().tolist() == [expect[k], 0, 0, 0]
+
+
+def test_results_of_several_calls_may_be_outstanding(cuda_ops):
+    """Every asynchronous call owns its count word: two results in flight on one stream do not alias,
+    and a synchronous call in between does not disturb them."""
+    import torch
+    from sbnet_b200 import ops
+    g = cfg.halo_geom(160, 176)
+    a = torch.from_numpy(cfg.rect_union_mask(2, 160, 176, seed=5, n_rects=5)).cuda()
+    b = torch.from_numpy(cfg.rect_union_mask(2, 160, 176, seed=6, n_rects=25)).cuda()
+    na = int(ops.reduce_mask(a, *g.as_lists(), tol=0.5)[1][0])
+    nb = int(ops.reduce_mask(b, *g.as_lists(), tol=0.5)[1][0])
+    assert na != nb
+    ia, ca = ops.reduce_mask_async(a, *g.as_lists(), tol=0.5)
+    ib, cb = ops.reduce_mask_async(b, *g.as_lists(), tol=0.5, mask_stable=True)
+    _, cs = ops.reduce_mask(a, *g.as_lists(), tol=0.5)
+    x = torch.randn((2, 160, 176, 16), device="cuda")
+    max_blocks = ia.shape[0]
+    ya = ops.sparse_gather_dyn(x, ca, max_blocks, ia, g.bsize, g.bstride, g.boffset)
+    yb = ops.sparse_gather_dyn(x, cb, max_blocks, ib, g.bsize, g.bstride, g.boffset)
+    torch.cuda.synchronize()
+    assert int(ca[0]) == na and int(cb[0]) == nb and int(cs[0]) == na
+    assert torch.equal(ya[:na], ops.sparse_gather(x, [na], ia, g.bsize, g.bstride, g.boffset))
+    assert torch.equal(yb[:nb], ops.sparse_gather(x, [nb], ib, g.bsize, g.bstride, g.boffset))
 
 
 def test_two_streams_with_their_own_scratch_do_not_interfere(cuda_ops):
@@ -167,8 +221,8 @@ def test_two_streams_with_their_own_scratch_do_not_interfere(cuda_ops):
     outs = []
     for i in range(200):
         with torch.cuda.stream(s1):
-            outs.append((ops.reduce_mask_async(a, *g.as_lists(), tol=0.5)[1].clone(), na))
+            outs.append((ops.reduce_mask_async(a, *g.as_lists(), tol=0.5)[1], na))
         with torch.cuda.stream(s2):
-            outs.append((ops.reduce_mask_async(b, *g.as_lists(), tol=0.5)[1].clone(), nb))
+            outs.append((ops.reduce_mask_async(b, *g.as_lists(), tol=0.5)[1], nb))
     torch.cuda.synchronize()
     assert all(int(c[0]) == n for c, n in outs)

@@ -70,4 +70,43 @@ def test_static_scratch_rejects_more_blocks_than_its_limit(cuda_ops):
                                     None, None)
     assert rc == -1
     msg = h.sbnet_last_error().decode()
-    assert "candidate blocks" in msg and str(1 << 24) in msg
+    assert "product" in msg and str(1 << 24) in msg
+    # factors past the int16 range are refused one by one, before their product is formed
+    rc = h.sbnet_reduce_mask_static(None, 2 ** 31 - 1, 8, 8, 0.5, 0, 0, 0, 1, 1, 1, 1, 2 ** 31 - 1, 2 ** 31 - 1,
+                                    None, None, None, None)
+    assert rc == -1 and "32767" in h.sbnet_last_error().decode()
+
+
+def test_static_scratch_count_stays_on_the_device_and_feeds_a_gather(cuda_ops):
+    """The stream-ordered use: no host count at all (count_host NULL), the count lands in the caller's
+    device word and is read there by the device-count gather -- on a stream of the caller's own, twice
+    in a row, against the ordinary entry point followed by the host-count gather."""
+    import torch
+    from sbnet_b200 import lib, ops
+    dev = "cuda"
+    g = cfg.halo_geom(160, 176)
+    N, H, W, Cc = 2, 160, 176, 32
+    x = torch.randn((N, H, W, Cc), device=dev)
+    geom = (g.boffset[0], g.boffset[1], g.bsize[0], g.bsize[1], g.bstride[0], g.bstride[1], g.bcount[0], g.bcount[1])
+    total = N * g.bcount[0] * g.bcount[1]
+    side = torch.cuda.Stream()
+    for seed, rects in ((11, 9), (12, 0), (13, 21)):
+        mask = torch.from_numpy(cfg.rect_union_mask(N, H, W, seed=seed, n_rects=rects)).to(dev)
+        idx_ref, cnt_ref = ops.reduce_mask(mask, *g.as_lists(), tol=0.5)
+        n = int(cnt_ref[0])
+        ref = ops.sparse_gather(x, cnt_ref, idx_ref, g.bsize, g.bstride, g.boffset, transpose=True)
+        key = lambda t: (t[:, 0].long() * g.bcount[0] + t[:, 1].long()) * g.bcount[1] + t[:, 2].long()  # noqa: E731
+        ref_sorted = ref[torch.argsort(key(idx_ref[:n]))]
+        torch.cuda.synchronize()
+        for _ in range(2):
+            with torch.cuda.stream(side):
+                idx = torch.full((total, 3), -1, dtype=torch.int16, device=dev)
+                count_dev = torch.full((1,), -9, dtype=torch.int32, device=dev)
+                out = torch.full((total, Cc, 18, 18), 7.0, device=dev)
+                lib.check(lib.load().sbnet_reduce_mask_static(mask.data_ptr(), N, H, W, 0.5, 0, *geom, idx.data_ptr(),
+                                                              count_dev.data_ptr(), None, side.cuda_stream))
+                ops.sparse_gather_dyn(x, count_dev, total, idx, g.bsize, g.bstride, g.boffset, transpose=True, out=out)
+            side.synchronize()
+            assert int(count_dev[0]) == n
+            assert torch.equal(out[torch.argsort(key(idx[:n]))], ref_sorted)
+            assert bool((out[n:] == 7.0).all())
