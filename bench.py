@@ -2,7 +2,7 @@
 """Benchmark of the block-op hot path: reduce_mask -> sparse_gather -> sparse_scatter_var.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--occupancy 0.1] [--scaling weak|strong] [--suite ops]
+                    [--occupancy 0.1] [--scaling strong|weak] [--suite ops|one|resblock|topleft|cpu|refgpu]
 
 Workload (one "step" = one pass of the three ops over one batch): the sparse ResNet-bottleneck
 configuration -- x fp16 [32,400,352,256], a rectangle-union mask, 18x18 windows on a 16 pixel pitch
@@ -12,9 +12,13 @@ x.  The dense convolutions between gather and scatter belong to the host framewo
 of this library, so they are not in the step.  Data is synthetic and seeded (sbnet_b200/configs.py).
 
 One JSON line is printed by rank 0.  `value` is blocks/s over all ranks with inputs resident in HBM;
+with N GPUs ONE batch of 32 images is sharded 32/N per rank (`"scaling": "strong"`, the configured
+split) and the weak-scaling figure -- a full batch per rank -- is reported beside it under `weak`;
 `e2e` is the same pipeline fed from pinned host buffers with the copies inside the timed region;
-`roofline` describes the kernel that takes the largest share of the step; `cpu_baseline` is the
-reference's CPU functors timed on this machine's cores on a bounded sample.
+`roofline` describes the kernel that takes the largest share of the step; `suite` (1 GPU) is the
+op-level table of the other configurations (reduce_mask at bird's-eye-view scale with its yardsticks,
+every gather and scatter cell at 5 / 20 / 50 %, the pipeline at 30 % occupancy); `cpu_baseline` is
+the reference's CPU functors timed on this machine's cores on a bounded sample.
 
 `--impl reference` times the reference's own CPU implementation (oracle/_ref when it was compiled
 from the reference tree, else the C restatement) on bounded samples of the same workload.
@@ -158,14 +162,156 @@ def per_image_blocks(mask, g_in, N, H, W):
 
 # ---- our arm -------------------------------------------------------------------------------------
 
-def run_ours(args):
-    import torch
-    import torch.distributed as dist
-    from sbnet_b200 import build, lib, ops
+TRAFFIC_PROFILES = {
+    # dominant kernel -> the committed profiler summary its DRAM traffic per block is read from
+    "gather": "planes_gather_tma_tile_f16_c256_d20.txt",
+    "scatter": "planes_scatter_simt_f16_add_c256_d20.txt",
+}
 
+
+def traffic_per_block(op):
+    """DRAM bytes per active block of the dominant kernel, read from the committed summary of one
+    profiler capture of that kernel on a smaller case of the same shape (``DRAM read`` + ``DRAM write``
+    divided by ``blocks in this launch``).  Every block moves the same tile, so traffic is proportional
+    to the block count.  Returns (bytes per block, file name) or (None, file name)."""
+    import re
+    name = TRAFFIC_PROFILES[op]
+    try:
+        text = open(os.path.join(ROOT, "profiles", name)).read()
+        unit = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}
+        rd = re.search(r"DRAM read\s+([0-9.]+)\s+(\w+)", text)
+        wr = re.search(r"DRAM write\s+([0-9.]+)\s+(\w+)", text)
+        nb = re.search(r"blocks in this launch\s+(\d+)", text)
+        total = float(rd.group(1)) * unit[rd.group(2)] + float(wr.group(1)) * unit[wr.group(2)]
+        return total / int(nb.group(1)), name
+    except Exception:
+        return None, name
+
+
+def bind_cores(local, per_node):
+    """Gives this rank its own slice of the cores the process may run on, before any pinned buffer is
+    allocated (first touch then lands near those cores).  Returns the cores, or None when unsupported."""
+    try:
+        allowed = sorted(os.sched_getaffinity(0))
+        per = len(allowed) // max(per_node, 1)
+        if per_node <= 1 or per < 1:
+            return allowed
+        mine = allowed[local * per:(local + 1) * per]
+        os.sched_setaffinity(0, mine)
+        return mine
+    except Exception:
+        return None
+
+
+class Workload:
+    """Device-resident inputs of one rank for `n_images` images at one mask occupancy."""
+
+    def __init__(self, torch, dev, args, first_image, n_images, occupancy, x_all, gen):
+        H, W, C = args.height, args.width, args.channels
+        self.N, self.H, self.W, self.C = n_images, H, W, C
+        self.g_in, self.g_out = cfg.halo_geom(H, W), cfg.inner_geom(H, W)
+        # image n of the global batch always gets seed 7 + n, whichever rank owns it
+        self.mask_h = cfg.rect_union_mask(n_images, H, W, seed=7 + first_image, occupancy=occupancy)
+        self.nB, self.U_in, self.U_out, _ = union_stats(self.mask_h, self.g_in, self.g_out, n_images, H, W)
+        self.x = x_all[:n_images]
+        # conv-output-shaped stack [nB,C,16,16]; small magnitudes so K accumulations stay far from fp16 max
+        self.q = (torch.randn((self.nB, C, 16, 16), generator=gen, device=dev, dtype=torch.float32) * 0.01).half()
+        self.stack = torch.empty((self.nB, C, 18, 18), dtype=torch.float16, device=dev)
+        # masks rotate through enough copies to exceed L2 on their own
+        n_masks = max(2, int(L2_BYTES // self.mask_h.nbytes) + 2)
+        self.masks = [torch.from_numpy(self.mask_h).to(dev) for _ in range(min(n_masks, 8))]
+        sz = 2
+        self.bytes = {
+            "reduce_mask": cfg.algorithmic_bytes("reduce_mask", nB=self.nB, geom=self.g_in, C=1, itemsize=4, U=0,
+                                                 N=n_images, H=H, W=W, count=self.nB),
+            "gather": cfg.algorithmic_bytes("gather", nB=self.nB, geom=self.g_in, C=C, itemsize=sz, U=self.U_in),
+            "scatter": cfg.algorithmic_bytes("scatter_add", nB=self.nB, geom=self.g_out, C=C, itemsize=sz, U=self.U_out),
+        }
+
+
+def run_pipeline(torch, dist, ops, w, steps, warmup, world, exchange=None, marks=False, common_start=True):
+    """`warmup` untimed and `steps` timed passes of reduce_mask -> gather -> scatter over workload `w`.
+    Returns (ms of the timed region on this rank, blocks processed, per-op event times or None, wall-clock
+    window).  The timed steps carry no per-op events (they cost host time between the launches); a
+    separate call with marks=True takes those."""
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+    g_in, g_out = w.g_in, w.g_out
+    yield_core = world > 1
+
+    def step(i, mk=None, ex=None):
+        m = w.masks[i % len(w.masks)]
+        slot = ex.slot(i) if ex is not None else None
+        if mk is not None:
+            mk[0].record()
+        # the mask has been resident since start-up and the kernel queued before this one is the previous
+        # step's scatter, which does not touch it: its loads may overlap that kernel's tail
+        idx, cnt, _ = ops.reduce_mask_with_device_count(m, *g_in.as_lists(), tol=0.5, avgpool=False, mask_stable=True,
+                                                        yield_core=yield_core, scratch=slot)
+        if mk is not None:
+            mk[1].record()
+        nb = int(cnt[0])
+        assert nb == w.nB, (nb, w.nB)
+        if mk is not None:
+            mk[2].record()
+        ops.sparse_gather(w.x, cnt, idx, g_in.bsize, g_in.bstride, g_in.boffset, transpose=True, out=w.stack)
+        if mk is not None:
+            mk[3].record()
+        ops.sparse_scatter_var(w.q, cnt, idx, w.x, g_out.bsize, g_out.bstride, g_out.boffset, add=True, transpose=True)
+        if mk is not None:
+            mk[4].record()
+        if ex is not None:
+            ex.step_done(i, warmup + steps)
+        return nb
+
+    def fence():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for i in range(warmup):
+        step(i, ex=exchange)
+    fence()
+    mks = [[ev() for _ in range(5)] for _ in range(steps)] if marks else None
+    t0, t1 = ev(), ev()
+    if world > 1 and common_start:
+        # every rank enters the timed region at the same wall-clock instant (one node, one clock), so
+        # the barrier's exit skew is not part of a region that lasts only milliseconds
+        go = torch.zeros(1, dtype=torch.float64, device=w.x.device)
+        if dist.get_rank() == 0:
+            go[0] = time.time() + 0.01
+        dist.broadcast(go, 0)
+        t_go = float(go.item())
+        while time.time() < t_go:
+            pass
+    wall0 = time.time()
+    t0.record()
+    blocks = 0
+    for i in range(steps):
+        blocks += step(warmup + i, mks[i] if marks else None, exchange)
+    t1.record()
+    torch.cuda.synchronize()
+    wall1 = time.time()
+    fence()
+    ms = t0.elapsed_time(t1)
+    op_ms = None
+    if marks:
+        op_ms = {"reduce_mask": [m[0].elapsed_time(m[1]) for m in mks], "gather": [m[2].elapsed_time(m[3]) for m in mks],
+                 "scatter": [m[3].elapsed_time(m[4]) for m in mks]}
+    return ms, blocks, op_ms, (wall0, wall1)
+
+
+def run_ours(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    cores = bind_cores(local, int(os.environ.get("LOCAL_WORLD_SIZE", str(world))))
+    import torch
+    import torch.distributed as dist
+    from sbnet_b200 import build, lib, ops
+    from sbnet_b200 import dist as sbdist
+    from sbnet_b200.dist import shard_bounds
+
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path in the product)")
     torch.cuda.set_device(local)
@@ -178,261 +324,118 @@ def run_ours(args):
         dist.barrier()
     lib.load()
 
-    N, H, W, C, mask_h = make_host_inputs(args, rank, world)
-    g_in, g_out = cfg.halo_geom(H, W), cfg.inner_geom(H, W)
-    nB, U_in, U_out, _ = union_stats(mask_h, g_in, g_out, N, H, W)
-    sz = 2
+    H, W, C = args.height, args.width, args.channels
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
-    x = torch.empty((N, H, W, C), dtype=torch.float16, device=dev)
-    for n in range(N):  # generated in slices: a one-shot fp32 randn of this size would double the footprint
-        x[n] = torch.randn((H, W, C), generator=gen, device=dev, dtype=torch.float32).half()
-    # conv-output-shaped stack [nB,C,16,16]; small magnitudes so K accumulations stay far from fp16 max
-    q = (torch.randn((nB, C, 16, 16), generator=gen, device=dev, dtype=torch.float32) * 0.01).half()
-    stack = torch.empty((nB, C, 18, 18), dtype=torch.float16, device=dev)
-    # masks rotate through enough copies to exceed L2 on their own
-    n_masks = max(2, int(L2_BYTES // mask_h.nbytes) + 2)
-    masks = [torch.from_numpy(mask_h).to(dev) for _ in range(min(n_masks, 8))]
+    # the configured split: ONE batch of `--batch` images sharded over the ranks (strong scaling); the
+    # weak-scaling figure (every rank a full batch of its own) is measured beside it when there are peers
+    lo, hi = shard_bounds(args.batch, world, rank)
+    n_strong = max(hi - lo, 1)
+    n_alloc = args.batch if (world > 1 and not args.no_weak) or args.scaling == "weak" else n_strong
+    x_all = torch.empty((n_alloc, H, W, C), dtype=torch.float16, device=dev)
+    for n in range(n_alloc):  # generated in slices: a one-shot fp32 randn of this size would double the footprint
+        x_all[n] = torch.randn((H, W, C), generator=gen, device=dev, dtype=torch.float32).half()
+    if args.scaling == "strong":
+        main_w = Workload(torch, dev, args, lo, n_strong, args.occupancy, x_all, gen)
+    else:
+        main_w = Workload(torch, dev, args, rank * args.batch, args.batch, args.occupancy, x_all, gen)
     torch.cuda.synchronize()
 
-    bytes_mask = cfg.algorithmic_bytes("reduce_mask", nB=nB, geom=g_in, C=1, itemsize=4, U=0, N=N,
-                                       H=H, W=W, count=nB)
-    bytes_gather = cfg.algorithmic_bytes("gather", nB=nB, geom=g_in, C=C, itemsize=sz, U=U_in)
-    bytes_scatter = cfg.algorithmic_bytes("scatter_add", nB=nB, geom=g_out, C=C, itemsize=sz, U=U_out)
-
-    from sbnet_b200 import dist as sbdist
-    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
-
-    last_counts = [None]
-    pending = [None]
-    side = torch.cuda.Stream() if world > 1 else None
-
-    def step(i, marks=None, exchange=True):
-        m = masks[i % len(masks)]
-        if pending[0] is not None:   # the previous step's all-gather has read the device count by now
-            pending[0].wait()
-            pending[0] = None
-        if marks is not None:
-            marks[0].record()
-        idx, cnt = ops.reduce_mask(m, *g_in.as_lists(), tol=0.5, avgpool=False)
-        if marks is not None:
-            marks[1].record()
-        nb = int(cnt[0])
-        assert nb == nB, (nb, nB)
-        if marks is not None:
-            marks[2].record()
-        ops.sparse_gather(x, cnt, idx, g_in.bsize, g_in.bstride, g_in.boffset, transpose=True, out=stack)
-        if marks is not None:
-            marks[3].record()
-        ops.sparse_scatter_var(q, cnt, idx, x, g_out.bsize, g_out.bstride, g_out.boffset, add=True,
-                               transpose=True)
-        if marks is not None:
-            marks[4].record()
-        if world > 1 and exchange:
-            # The only exchange of the path: every rank's block count, read from device memory.  It is
-            # issued after gather and scatter are queued, on a side stream (the count is final: the op
-            # interface already synchronised for it), so it overlaps them and nothing waits for it
-            # until the next reduce_mask is about to overwrite the count.
-            count_dev = ops.scratch_for(dev, torch.cuda.current_stream(dev).cuda_stream)[0][:1]
-            with torch.cuda.stream(side):
-                counts_all, pending[0] = sbdist.all_gather_counts(count_dev, async_op=True)
-            last_counts[0] = counts_all
-        return nb
-
-    def fence():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
+    def exchange():
+        # The only exchange of the path: every rank's block count per step, read from device memory.
+        return sbdist.CountExchange(dev, depth=8, timeout_s=60.0) if world > 1 else None
 
     clocks = ClockSampler(local).start()
-    for i in range(args.warmup):
-        step(i)
-    fence()
-    marks = [[ev() for _ in range(5)] for _ in range(args.steps)]
-    t0, t1 = ev(), ev()
-    fence()
-    wall0 = time.time()
-    t0.record()
-    blocks = 0
-    for i in range(args.steps):
-        blocks += step(args.warmup + i, marks[i])
-    t1.record()
-    if pending[0] is not None:
-        pending[0].wait()
-        pending[0] = None
-    fence()
-    ms_total = t0.elapsed_time(t1)
+    ex = exchange()
+    ms_total, blocks, _, (wall0, _) = run_pipeline(torch, dist, ops, main_w, args.steps, args.warmup, world, ex)
+    global_counts = ex.finish() if ex is not None else None
     # a short timed region may fall between two clock samples: keep the same load running (untimed)
-    # until at least half a second of it has been sampled
-    extra = 0
-    while time.time() - wall0 < 0.5:
-        step(extra, exchange=False)   # ranks may run different numbers of these: no collective here
-        extra += 1
-    torch.cuda.synchronize()
-    wall1 = time.time()
-    if pending[0] is not None:
-        pending[0].wait()
-        pending[0] = None
-    fence()
-    clocks.stop()
+    # until at least half a second of it has been sampled; the per-op event times come from these passes
     op_ms = {"reduce_mask": [], "gather": [], "scatter": []}
-    for mk in marks:
-        op_ms["reduce_mask"].append(mk[0].elapsed_time(mk[1]))
-        op_ms["gather"].append(mk[2].elapsed_time(mk[3]))
-        op_ms["scatter"].append(mk[3].elapsed_time(mk[4]))
+    while True:
+        _, _, more, _ = run_pipeline(torch, dist, ops, main_w, min(args.steps, 25), 1, 1, None, marks=True)
+        for k in op_ms:
+            op_ms[k] += more[k]
+        if time.time() - wall0 >= 0.5:
+            break
+    wall1 = time.time()
+    clocks.stop()
+    if world > 1:
+        dist.barrier()
+
+    # ---- the other scaling mode beside it (per-rank batch fixed / one batch split), N > 1 only ----
+    other = None
+    if world > 1 and not args.no_weak:
+        if args.scaling == "strong":
+            ow = Workload(torch, dev, args, rank * args.batch, args.batch, args.occupancy, x_all, gen)
+        else:
+            ow = Workload(torch, dev, args, lo, n_strong, args.occupancy, x_all, gen)
+        oex = exchange()
+        oms, oblocks, _, _ = run_pipeline(torch, dist, ops, ow, args.steps, args.warmup, world, oex)
+        oex.finish()
+        other = (oms, oblocks, ow.N)
+        del ow
 
     # ---- end to end: host buffers in, host result out, copies inside the timed region ----
-    # The batch is cut into image groups; three streams (host->device, compute, device->host) are
-    # chained with events so that the upload of group g+1, the ops on group g and the download of
-    # group g-1 overlap.  PCIe is full duplex, so a step costs about max(upload, download) instead of
-    # their sum.  Every byte of mask, x and the conv-output stack goes up and every byte of the
-    # updated x comes down inside the timed region, every step.
-    e2e = None
-    if not args.no_e2e:
-        e2e_steps = max(1, min(args.steps, args.e2e_steps))
-        G = max(1, min(args.e2e_groups, N))
-        bounds = [(N * g) // G for g in range(G + 1)]
-        per_image = per_image_blocks(mask_h, g_in, N, H, W)
-        qoff = [0]
-        for g in range(G):
-            qoff.append(qoff[-1] + int(per_image[bounds[g]:bounds[g + 1]].sum()))
-        hx = torch.empty((N, H, W, C), dtype=torch.float16, pin_memory=True)
-        hx.copy_(x)
-        hq = torch.empty(q.shape, dtype=torch.float16, pin_memory=True)
-        hq.copy_(q)
-        hm = torch.from_numpy(mask_h).pin_memory()
-        hy = torch.empty((N, H, W, C), dtype=torch.float16, pin_memory=True)
-        dm = masks[0]
-        s_in, s_c, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
-        out_done = [None] * G
-        fence()
+    e2e = run_e2e(torch, dist, ops, args, main_w, world) if not args.no_e2e else None
+    sync_free = run_sync_free(torch, ops, args, main_w) if world == 1 and not args.no_sync_free else None
 
-        def e2e_step():
-            in_done = []
-            with torch.cuda.stream(s_in):
-                for g in range(G):
-                    lo, hi = bounds[g], bounds[g + 1]
-                    if out_done[g] is not None:      # x[lo:hi] of the previous step must be downloaded first
-                        s_in.wait_event(out_done[g])
-                    dm[lo:hi].copy_(hm[lo:hi], non_blocking=True)
-                    x[lo:hi].copy_(hx[lo:hi], non_blocking=True)
-                    q[qoff[g]:qoff[g + 1]].copy_(hq[qoff[g]:qoff[g + 1]], non_blocking=True)
-                    e = torch.cuda.Event()
-                    e.record(s_in)
-                    in_done.append(e)
-            total = 0
-            for g in range(G):
-                lo, hi = bounds[g], bounds[g + 1]
-                with torch.cuda.stream(s_c):
-                    s_c.wait_event(in_done[g])
-                    idx, cnt = ops.reduce_mask(dm[lo:hi], *g_in.as_lists(), tol=0.5, avgpool=False)
-                    nb = int(cnt[0])
-                    assert nb == qoff[g + 1] - qoff[g] or qoff[g + 1] == qoff[g], (nb, g)
-                    if qoff[g + 1] > qoff[g]:
-                        ops.sparse_gather(x[lo:hi], cnt, idx, g_in.bsize, g_in.bstride, g_in.boffset,
-                                          transpose=True, out=stack[:nb])
-                        ops.sparse_scatter_var(q[qoff[g]:qoff[g + 1]], cnt, idx, x[lo:hi], g_out.bsize,
-                                               g_out.bstride, g_out.boffset, add=True, transpose=True)
-                        total += nb
-                    e = torch.cuda.Event()
-                    e.record(s_c)
-                with torch.cuda.stream(s_out):
-                    s_out.wait_event(e)
-                    hy[lo:hi].copy_(x[lo:hi], non_blocking=True)
-                    d = torch.cuda.Event()
-                    d.record(s_out)
-                    out_done[g] = d
-            return total
+    # ---- the configured op-level cells and the 30 % pipeline, single GPU only ----
+    suite = None
+    if world == 1 and not args.no_suite:
+        import bench_ops
+        suite = {}
+        w30 = Workload(torch, dev, args, 0, main_w.N, 0.30, x_all, gen)
+        ms30, b30, op30, _ = run_pipeline(torch, dist, ops, w30, 20, 5, 1, None, marks=True)
+        peak, peak_kind = measured_peak()
+        for k in ("reduce_mask", "gather", "scatter"):
+            med = statistics.median(op30[k])
+            gbs = w30.bytes[k] / (med * 1e-3) / 1e9
+            suite[f"c5_occ30_{k}"] = {"us": round(med * 1e3, 2), "us_min": round(min(op30[k]) * 1e3, 2),
+                                      "algorithmic_bytes": int(w30.bytes[k]), "GB/s": round(gbs, 1),
+                                      "frac_of_" + peak_kind: round(gbs / peak, 4), "blocks": w30.nB}
+        suite["c5_occ30_step"] = {"us": round(ms30 / 20 * 1e3, 2), "blocks": w30.nB, "blocks/s": round(b30 / (ms30 * 1e-3))}
+        del w30
+        torch.cuda.empty_cache()
+        suite.update(bench_ops.suite_table(torch, dev, steps=20, warmup=5, quiet=True))
 
-        def e2e_fence():
-            for st in (s_in, s_c, s_out):
-                st.synchronize()
-            fence()
-
-        e2e_step()
-        e2e_fence()
-        a, b = ev(), ev()
-        a.record()
-        s_in.wait_event(a)
-        eb = 0
-        for _ in range(e2e_steps):
-            eb += e2e_step()
-        for st in (s_in, s_c, s_out):
-            torch.cuda.current_stream().wait_stream(st)
-        b.record()
-        e2e_fence()
-        e2e_ms = a.elapsed_time(b)
-        e2e = dict(ms=e2e_ms, blocks=eb, steps=e2e_steps, groups=G,
-                   h2d=hx.numel() * 2 + hq.numel() * 2 + hm.numel() * 4, d2h=hy.numel() * 2)
-        del hx, hq, hy
-
-    # ---- the same three ops with the block count kept on the device, replayed from a CUDA graph ----
-    # (outside the op interface, which needs bin_counts on the host; offered by the *_dyn entry points)
-    sync_free = None
-    if world == 1 and not args.no_sync_free:
-        max_blocks = N * g_in.bcount[0] * g_in.bcount[1]
-        big_stack = torch.empty((max_blocks, C, 18, 18), dtype=torch.float16, device=dev)
-        big_q = torch.empty((max_blocks, C, 16, 16), dtype=torch.float16, device=dev)
-        big_q[:nB] = q
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-
-        def dyn_step(m):
-            idx, cnt_dev = ops.reduce_mask_async(m, *g_in.as_lists(), tol=0.5, avgpool=False)
-            ops.sparse_gather_dyn(x, cnt_dev, max_blocks, idx, g_in.bsize, g_in.bstride, g_in.boffset,
-                                  transpose=True, out=big_stack)
-            ops.sparse_scatter_var_dyn(big_q, cnt_dev, max_blocks, idx, x, g_out.bsize, g_out.bstride,
-                                       g_out.boffset, add=True, transpose=True)
-            return idx
-
-        with torch.cuda.stream(side):
-            dyn_step(masks[0])
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
-        graph, keep = torch.cuda.CUDAGraph(), []
-        with torch.cuda.graph(graph, stream=side):
-            for m in masks[:4]:
-                keep.append(dyn_step(m))
-        for _ in range(2):
-            graph.replay()
-        fence()
-        a, b = ev(), ev()
-        reps = max(1, args.steps // 4)
-        a.record()
-        for _ in range(reps):
-            graph.replay()
-        b.record()
-        fence()
-        ms = a.elapsed_time(b) / (reps * 4)
-        sync_free = {"value": nB / (ms * 1e-3), "unit": "blocks/s", "ms_per_step": ms,
-                     "how": "reduce_mask -> gather_dyn -> scatter_dyn, count read on the device, 4 steps per CUDA graph replay"}
-        del big_stack, big_q, graph, keep
-
-    # ---- reduce over ranks: max time, summed blocks ----
-    stats = torch.tensor([ms_total, e2e["ms"] if e2e else 0.0], dtype=torch.float64, device=dev)
-    sums = torch.tensor([blocks, e2e["blocks"] if e2e else 0], dtype=torch.float64, device=dev)
+    # ---- reduce over ranks: max time, summed blocks; per-op medians of the slowest rank ----
+    med_local = [statistics.median(op_ms[k]) for k in ("reduce_mask", "gather", "scatter")]
+    stats = torch.tensor([ms_total, e2e["ms"] if e2e else 0.0, other[0] if other else 0.0] + med_local,
+                         dtype=torch.float64, device=dev)
+    sums = torch.tensor([blocks, e2e["blocks"] if e2e else 0, other[1] if other else 0], dtype=torch.float64, device=dev)
+    per_rank = None
     if world > 1:
+        gathered = [torch.zeros_like(stats) for _ in range(world)]
+        dist.all_gather(gathered, stats)
+        per_rank = torch.stack(gathered).cpu().tolist()
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
         dist.all_reduce(sums, op=dist.ReduceOp.SUM)
-    ms_total, e2e_ms = stats.tolist()
-    blocks_all, e2e_blocks_all = sums.tolist()
+    ms_total, e2e_ms, other_ms = stats.tolist()[:3]
+    med_slowest = dict(zip(("reduce_mask", "gather", "scatter"), stats.tolist()[3:]))
+    blocks_all, e2e_blocks_all, other_blocks_all = sums.tolist()
+    e2e_rates = None
+    if e2e and world > 1:
+        t = torch.tensor([e2e["h2d"] / (e2e["ms"] / e2e["steps"] * 1e-3) / 1e9, e2e["d2h"] / (e2e["ms"] / e2e["steps"] * 1e-3) / 1e9],
+                         dtype=torch.float64, device=dev)
+        g = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(g, t)
+        e2e_rates = [[round(v, 2) for v in r] for r in torch.stack(g).cpu().tolist()]
 
     global_blocks = None
-    if world > 1 and last_counts[0] is not None:
-        global_blocks = int(last_counts[0].sum().item())   # from the all-gathered device counts
-        assert global_blocks * args.steps == int(blocks_all), (global_blocks, blocks_all)
+    if global_counts:
+        per_step = [sum(v) for k, v in sorted(global_counts.items()) if k >= args.warmup]
+        global_blocks = per_step[0]
+        assert all(p == global_blocks for p in per_step) and global_blocks * args.steps == int(blocks_all), \
+            (per_step[:4], blocks_all)
     if rank == 0:
         peak, peak_kind = measured_peak()
-        med = {k: statistics.median(v) for k, v in op_ms.items()}
-        alg = {"reduce_mask": bytes_mask, "gather": bytes_gather, "scatter": bytes_scatter}
-        gbs = {k: alg[k] / (med[k] * 1e-3) / 1e9 for k in med}
-        dom = max(("gather", "scatter"), key=lambda k: med[k])
+        w = main_w
+        med0 = dict(zip(("reduce_mask", "gather", "scatter"), med_local))
+        gbs = {k: w.bytes[k] / (med_slowest[k] * 1e-3) / 1e9 for k in med_slowest}
+        dom = max(("gather", "scatter"), key=lambda k: med_slowest[k])
         kernel_name = {"gather": "planes_gather_tma_tile<__half> (sparse_gather transpose=True)",
                        "scatter": "planes_scatter_simt<atomic,__half,4> (sparse_scatter_var add=True transpose=True)"}[dom]
-        # DRAM bytes per active block from one ncu capture of each kernel on a smaller case of the same
-        # shape (1,641 blocks; profiles/planes_*_c256_d20.txt), scaled by the blocks of this launch
-        # (traffic is proportional to the block count: every block moves the same tile)
-        traffic = {"gather": 295860, "scatter": 357910}[dom] * nB
+        per_block, source = traffic_per_block(dom)
         line = {
             "metric": "sparse block pipeline throughput (reduce_mask -> sparse_gather -> sparse_scatter_var)",
             "value": blocks_all / (ms_total * 1e-3),
@@ -442,23 +445,38 @@ def run_ours(args):
             "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
             "dtype": "f16", "data": "synthetic",
             "config": {
-                "workload": "sparse ResNet bottleneck block ops, batch-sharded (BASELINE config 5 without the framework's convs)",
-                "x": [N, H, W, C], "per_rank_batch": N, "global_batch": N * world,
+                "workload": "sparse ResNet bottleneck block ops, one batch sharded over the GPUs (BASELINE config 5 without the framework's convs)"
+                            if args.scaling == "strong" else
+                            "sparse ResNet bottleneck block ops, one full batch per GPU (BASELINE config 5 without the framework's convs)",
+                "x": [w.N, H, W, C], "per_rank_batch": w.N,
+                "global_batch": args.batch if args.scaling == "strong" else args.batch * world,
                 "mask": f"rectangle union, {args.occupancy:.0%} pixel occupancy",
                 "bsize": [18, 18], "bstride": [16, 16], "boffset": [-1, -1],
-                "active_blocks_per_rank": nB, "candidate_blocks_per_rank": N * g_in.bcount[0] * g_in.bcount[1],
-                "l2": "x (2.3 GB per rank) exceeds L2; masks rotate through copies and are evicted by the x traffic between uses",
-                "parallelism": f"dp{world}", "global_blocks_per_step": global_blocks if world > 1 else nB,
-                "collective": "all-gather of one int32 block count per rank per step (NCCL), off the critical path",
+                "active_blocks_per_rank": w.nB, "candidate_blocks_per_rank": w.N * w.g_in.bcount[0] * w.g_in.bcount[1],
+                "l2": "x (72 MB per image) exceeds L2 from two images on; masks rotate through copies and are evicted by the x traffic between uses",
+                "parallelism": f"dp{world}", "global_blocks_per_step": global_blocks if world > 1 else w.nB,
+                "collective": "all-gather of the ranks' int32 block counts, eight steps per call (NCCL), off the critical path",
             },
-            "ops": {k: {"us": med[k] * 1e3, "algorithmic_bytes": alg[k], "GB/s": gbs[k],
-                        "frac_of_" + peak_kind: gbs[k] / peak} for k in med},
+            "ops": {k: {"us": med_slowest[k] * 1e3, "us_rank0": med0[k] * 1e3, "algorithmic_bytes": w.bytes[k], "GB/s": gbs[k],
+                        "frac_of_" + peak_kind: gbs[k] / peak} for k in med_slowest},
+            "ops_note": "median CUDA-event time per op on the slowest rank, from instrumented passes of the same steps",
             "roofline": {"bound": "hbm", "kernel": kernel_name, "achieved": gbs[dom], "peak": peak,
                          "peak_source": peak_kind, "unit": "GB/s", "frac": gbs[dom] / peak,
-                         "traffic": traffic, "algorithmic_bytes": alg[dom]},
+                         "traffic": per_block * w.nB if per_block else None, "traffic_source": "profiles/" + source,
+                         "algorithmic_bytes": w.bytes[dom]},
             "gpu_launches": 3 * args.steps,
             "clocks": clocks.summary(wall0, wall1),
+            "host_cores_per_rank": len(cores) if cores else None,
         }
+        if other:
+            mode = "weak" if args.scaling == "strong" else "strong"
+            line[mode] = {"value": other_blocks_all / (other_ms * 1e-3), "unit": "blocks/s", "ms_per_step": other_ms / args.steps,
+                          "per_rank_batch": other[2],
+                          "global_batch": args.batch * world if mode == "weak" else args.batch}
+        if per_rank:
+            line["per_rank"] = {"ms_per_step": [r[0] / args.steps for r in per_rank],
+                                "reduce_mask_us": [r[3] * 1e3 for r in per_rank],
+                                "gather_us": [r[4] * 1e3 for r in per_rank], "scatter_us": [r[5] * 1e3 for r in per_rank]}
         if sync_free:
             line["sync_free"] = sync_free
         if e2e:
@@ -466,12 +484,151 @@ def run_ours(args):
                            "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
                            "steps": e2e["steps"], "ms_per_step": e2e_ms / e2e["steps"],
                            "pipelining": f"{e2e['groups']} image groups on 3 streams (upload / ops / download overlap)"}
+            if e2e_rates:
+                line["e2e"]["per_rank_h2d_d2h_GB/s"] = e2e_rates
+        if suite:
+            line["suite"] = suite
         if world == 1 and not args.no_cpu:
-            line["cpu_baseline"] = cpu_pipeline(args, mask_h, N, H, W, C, budget_s=args.cpu_budget)
+            line["cpu_baseline"] = cpu_pipeline(args, w.mask_h, w.N, H, W, C, budget_s=args.cpu_budget)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def run_e2e(torch, dist, ops, args, w, world):
+    """The same pipeline fed from pinned host buffers.  The batch is cut into image groups; three streams
+    (host->device, compute, device->host) are chained with events so that the upload of group g+1, the
+    ops on group g and the download of group g-1 overlap.  PCIe is full duplex, so a step costs about
+    max(upload, download) instead of their sum.  Every byte of mask, x and the conv-output stack goes up
+    and every byte of the updated x comes down inside the timed region, every step."""
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+    N, H, W, C = w.N, w.H, w.W, w.C
+    g_in, g_out, x, q, stack = w.g_in, w.g_out, w.x, w.q, w.stack
+    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+    G = max(1, min(args.e2e_groups, N))
+    bounds = [(N * g) // G for g in range(G + 1)]
+    per_image = per_image_blocks(w.mask_h, g_in, N, H, W)
+    qoff = [0]
+    for g in range(G):
+        qoff.append(qoff[-1] + int(per_image[bounds[g]:bounds[g + 1]].sum()))
+    hx = torch.empty((N, H, W, C), dtype=torch.float16, pin_memory=True)
+    hx.copy_(x)
+    hq = torch.empty(q.shape, dtype=torch.float16, pin_memory=True)
+    hq.copy_(q)
+    hm = torch.from_numpy(w.mask_h).pin_memory()
+    hy = torch.empty((N, H, W, C), dtype=torch.float16, pin_memory=True)
+    dm = w.masks[0]
+    s_in, s_c, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    out_done = [None] * G
+
+    def fence():
+        for st in (s_in, s_c, s_out):
+            st.synchronize()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def e2e_step():
+        in_done = []
+        with torch.cuda.stream(s_in):
+            for g in range(G):
+                lo, hi = bounds[g], bounds[g + 1]
+                if out_done[g] is not None:      # x[lo:hi] of the previous step must be downloaded first
+                    s_in.wait_event(out_done[g])
+                dm[lo:hi].copy_(hm[lo:hi], non_blocking=True)
+                x[lo:hi].copy_(hx[lo:hi], non_blocking=True)
+                q[qoff[g]:qoff[g + 1]].copy_(hq[qoff[g]:qoff[g + 1]], non_blocking=True)
+                e = torch.cuda.Event()
+                e.record(s_in)
+                in_done.append(e)
+        total = 0
+        for g in range(G):
+            lo, hi = bounds[g], bounds[g + 1]
+            with torch.cuda.stream(s_c):
+                s_c.wait_event(in_done[g])
+                idx, cnt = ops.reduce_mask(dm[lo:hi], *g_in.as_lists(), tol=0.5, avgpool=False, yield_core=world > 1)
+                nb = int(cnt[0])
+                assert nb == qoff[g + 1] - qoff[g] or qoff[g + 1] == qoff[g], (nb, g)
+                if qoff[g + 1] > qoff[g]:
+                    ops.sparse_gather(x[lo:hi], cnt, idx, g_in.bsize, g_in.bstride, g_in.boffset,
+                                      transpose=True, out=stack[:nb])
+                    ops.sparse_scatter_var(q[qoff[g]:qoff[g + 1]], cnt, idx, x[lo:hi], g_out.bsize,
+                                           g_out.bstride, g_out.boffset, add=True, transpose=True)
+                    total += nb
+                e = torch.cuda.Event()
+                e.record(s_c)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(e)
+                hy[lo:hi].copy_(x[lo:hi], non_blocking=True)
+                d = torch.cuda.Event()
+                d.record(s_out)
+                out_done[g] = d
+        return total
+
+    fence()
+    e2e_step()
+    fence()
+    a, b = ev(), ev()
+    a.record()
+    s_in.wait_event(a)
+    eb = 0
+    for _ in range(e2e_steps):
+        eb += e2e_step()
+    for st in (s_in, s_c, s_out):
+        torch.cuda.current_stream().wait_stream(st)
+    b.record()
+    fence()
+    res = dict(ms=a.elapsed_time(b), blocks=eb, steps=e2e_steps, groups=G,
+               h2d=hx.numel() * 2 + hq.numel() * 2 + hm.numel() * 4, d2h=hy.numel() * 2)
+    del hx, hq, hy
+    return res
+
+
+def run_sync_free(torch, ops, args, w):
+    """The same three ops with the block count kept on the device, replayed from a CUDA graph (outside
+    the op interface, which needs bin_counts on the host; offered by the *_dyn entry points)."""
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+    dev = w.x.device
+    g_in, g_out, x = w.g_in, w.g_out, w.x
+    max_blocks = w.N * g_in.bcount[0] * g_in.bcount[1]
+    big_stack = torch.empty((max_blocks, w.C, 18, 18), dtype=torch.float16, device=dev)
+    big_q = torch.empty((max_blocks, w.C, 16, 16), dtype=torch.float16, device=dev)
+    big_q[:w.nB] = w.q
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+
+    def dyn_step(m):
+        idx, cnt_dev = ops.reduce_mask_async(m, *g_in.as_lists(), tol=0.5, avgpool=False, mask_stable=True)
+        ops.sparse_gather_dyn(x, cnt_dev, max_blocks, idx, g_in.bsize, g_in.bstride, g_in.boffset,
+                              transpose=True, out=big_stack)
+        ops.sparse_scatter_var_dyn(big_q, cnt_dev, max_blocks, idx, x, g_out.bsize, g_out.bstride,
+                                   g_out.boffset, add=True, transpose=True)
+        return idx, cnt_dev
+
+    with torch.cuda.stream(side):
+        dyn_step(w.masks[0])
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph, keep = torch.cuda.CUDAGraph(), []
+    with torch.cuda.graph(graph, stream=side):
+        for m in w.masks[:4]:
+            keep.append(dyn_step(m))
+    for _ in range(2):
+        graph.replay()
+    torch.cuda.synchronize()
+    a, b = ev(), ev()
+    reps = max(1, args.steps // 4)
+    a.record()
+    for _ in range(reps):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / (reps * 4)
+    del big_stack, big_q, graph, keep
+    return {"value": w.nB / (ms * 1e-3), "unit": "blocks/s", "ms_per_step": ms,
+            "how": "reduce_mask -> gather_dyn -> scatter_dyn, count read on the device, 4 steps per CUDA graph replay"}
 
 
 # ---- CPU legs ------------------------------------------------------------------------------------
@@ -592,7 +749,7 @@ def refgpu_suite(args):
     import torch
     from oracle import refgpu   # test / benchmark infrastructure, never used by the product
     from sbnet_b200 import build, ops
-    from sbnet_b200.opbench import Timer, _peak
+    from bench_ops import Timer, _peak
     if not refgpu.available():
         try:
             refgpu.build()
@@ -778,7 +935,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="strong")
     ap.add_argument("--occupancy", type=float, default=0.10)
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--height", type=int, default=400)
@@ -789,8 +946,15 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-sync-free", action="store_true")
+    ap.add_argument("--no-suite", action="store_true", help="skip the op-level table of configurations 2-4 and 5 at 30 percent")
+    ap.add_argument("--no-weak", action="store_true", help="N > 1: skip the second pass in the other scaling mode")
     ap.add_argument("--cpu-budget", type=float, default=12.0)
-    ap.add_argument("--suite", choices=["ops", "one", "resblock", "cpu", "refgpu"], default=None)
+    ap.add_argument("--suite", choices=["ops", "one", "resblock", "topleft", "cpu", "refgpu"], default=None)
+    ap.add_argument("--arch", choices=["resnet-50", "resnet-v2"], default="resnet-v2", help="--suite topleft: size table")
+    ap.add_argument("--topleft-test", choices=["conv", "res"], default="res")
+    ap.add_argument("--topleft-dtype", choices=["f16", "f32"], default="f16")
+    ap.add_argument("--topleft-stage", type=int, default=None, help="--suite topleft: one stage (0-3) instead of all")
+    ap.add_argument("--topleft-sparsity", type=float, default=None, help="--suite topleft: one sparsity instead of the list")
     ap.add_argument("--case", default="gather_f16_t1")
     ap.add_argument("--density", type=float, default=0.2)
     ap.add_argument("--one-channels", type=int, default=None)
@@ -801,9 +965,9 @@ def main():
         refgpu_suite(args)
     elif args.suite == "cpu":
         cpu_suite(args)
-    elif args.suite in ("ops", "one", "resblock"):
-        from sbnet_b200 import opbench
-        opbench.main(args)
+    elif args.suite in ("ops", "one", "resblock", "topleft"):
+        import bench_ops
+        bench_ops.main(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -10,10 +10,18 @@ for device tensors, gloo for CPU tests).
 """
 from __future__ import annotations
 
-from typing import List, Sequence, Tuple
+import datetime
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
+
+
+class RankFailure(RuntimeError):
+    """A peer did not take part in the count exchange within the time allowed (it never joined, died,
+    or is stuck).  The reference has one process and no such case; its convention for any failure is to
+    print and ``exit()`` (``sbnet_ops/op_utils.h:27-37``).  Here the survivors get an exception they can act on
+    between steps, with nothing of theirs in flight on the GPU."""
 
 
 def shard_bounds(n_items: int, world: int, rank: int) -> Tuple[int, int]:
@@ -26,15 +34,110 @@ def shard_bounds(n_items: int, world: int, rank: int) -> Tuple[int, int]:
     return start, start + base + (1 if rank < extra else 0)
 
 
-def all_gather_counts(count: torch.Tensor, group=None, async_op: bool = False):
+def wait_for(work, timeout_s: Optional[float] = None, what: str = "count exchange") -> None:
+    """Waits for an asynchronous collective.  With ``timeout_s`` a peer that does not show up turns into
+    :class:`RankFailure` after that many seconds instead of a wait without end (host-side collectives
+    honour the timeout directly; NCCL work is additionally bounded by the process group's own timeout,
+    given to ``init_process_group``)."""
+    if work is None:
+        return
+    try:
+        if timeout_s is None:
+            work.wait()
+        else:
+            ok = work.wait(datetime.timedelta(seconds=float(timeout_s)))
+            if ok is False:
+                raise RankFailure(f"{what}: not complete after {timeout_s} s")
+    except RankFailure:
+        raise
+    except RuntimeError as e:   # gloo / NCCL report a timeout or a lost peer as RuntimeError
+        raise RankFailure(f"{what}: {e}") from e
+
+
+def all_gather_counts(count: torch.Tensor, group=None, async_op: bool = False, timeout_s: Optional[float] = None):
     """All-gathers one int32 per rank.  ``count`` is a 1-element int32 tensor (device tensor for NCCL,
     e.g. the device count published by reduce_mask; CPU tensor for gloo).  Returns ``(counts, work)``:
     ``counts`` is an int32 tensor of ``world`` entries, valid once ``work`` (None if synchronous) is
-    waited for."""
+    waited for (:func:`wait_for`).  A synchronous call with ``timeout_s`` raises :class:`RankFailure` when a
+    peer does not join in time."""
     world = dist.get_world_size(group)
     out = torch.empty(world, dtype=torch.int32, device=count.device)
-    work = dist.all_gather_into_tensor(out, count.reshape(1).to(torch.int32), group=group, async_op=async_op)
-    return out, (work if async_op else None)
+    work = dist.all_gather_into_tensor(out, count.reshape(1).to(torch.int32), group=group, async_op=True)
+    if async_op:
+        return out, work
+    wait_for(work, timeout_s)
+    return out, None
+
+
+class CountExchange:
+    """Exchange of the per-step block counts of a pipelined loop, batched so that no step waits for it.
+
+    Every step's reduce_mask publishes its count into a scratch slot of its own (``slot(step)``, to be
+    passed as the op's scratch); slots form rings of ``depth`` steps, and after the last step of a ring
+    ONE all-gather moves the whole ring (``16 * depth`` bytes per rank).  Two rings alternate, so the
+    wait for a ring's all-gather happens ``depth`` steps later, just before its slots are reused --
+    by then it has long finished, and no rank ever waits for a slower peer inside a step.  On a CUDA
+    device the collective is issued on a side stream behind an event recorded after the step's last
+    launch, so its kernel does not run beside the step's own kernels.
+    """
+
+    SLOT = 4   # int32 words of one reduce_mask scratch slot; word 0 is the count
+
+    def __init__(self, device, depth: int = 8, group=None, timeout_s: Optional[float] = None):
+        self.device, self.depth, self.group, self.timeout_s = torch.device(device), int(depth), group, timeout_s
+        self.world = dist.get_world_size(group)
+        n = self.depth * self.SLOT
+        self.rings = [torch.zeros(n, dtype=torch.int32, device=self.device) for _ in range(2)]
+        self.gathered = [torch.zeros(self.world * n, dtype=torch.int32, device=self.device) for _ in range(2)]
+        self.work = [None, None]
+        self.first_step = [None, None]
+        self.history: List[torch.Tensor] = []    # [world, depth] count tables of finished rings
+        self.side = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
+
+    def slot(self, step: int) -> torch.Tensor:
+        """The 4-word scratch slot of ``step``; waits (in stream order on a GPU) for the exchange that
+        last read this slot's ring."""
+        b, k = (step // self.depth) % 2, step % self.depth
+        if k == 0:
+            self._collect(b)
+        return self.rings[b][k * self.SLOT:(k + 1) * self.SLOT]
+
+    def step_done(self, step: int, steps_total: Optional[int] = None) -> None:
+        """Call after the step's last launch.  Starts the ring's all-gather when the ring is full (or
+        when ``step`` is the last of ``steps_total``)."""
+        b, k = (step // self.depth) % 2, step % self.depth
+        last = steps_total is not None and step == steps_total - 1
+        if k != self.depth - 1 and not last:
+            return
+        self.first_step[b] = step - k
+        if self.side is not None:
+            ev = torch.cuda.Event()
+            ev.record()
+            with torch.cuda.stream(self.side):
+                self.side.wait_event(ev)
+                self.work[b] = dist.all_gather_into_tensor(self.gathered[b], self.rings[b], group=self.group, async_op=True)
+        else:
+            self.work[b] = dist.all_gather_into_tensor(self.gathered[b], self.rings[b], group=self.group, async_op=True)
+
+    def _collect(self, b: int) -> None:
+        if self.work[b] is None:
+            return
+        wait_for(self.work[b], self.timeout_s)
+        self.work[b] = None
+        table = self.gathered[b].view(self.world, self.depth, self.SLOT)[:, :, 0].clone()
+        self.history.append((self.first_step[b], table))
+
+    def finish(self):
+        """Waits for what is outstanding and returns ``{step: [count of rank 0, count of rank 1, ...]}``
+        for every step exchanged so far (a partly filled last ring reports its unused slots as 0)."""
+        for b in range(2):
+            self._collect(b)
+        out = {}
+        for first, table in self.history:
+            t = table.cpu().tolist()
+            for k in range(self.depth):
+                out[first + k] = [t[r][k] for r in range(self.world)]
+        return out
 
 
 def block_offsets(counts: Sequence[int]) -> List[int]:

@@ -156,11 +156,14 @@ def scratch_for(device, stream: int) -> tuple:
     and the flag that says so.  Slots come from a slab of 1,024 that is zero-filled once on that stream;
     every slot is handed out once, so word 0 -- where the kernel publishes the count -- stays an
     independent device-side count for as long as the caller keeps the returned view (two results in
-    flight on one stream never alias).  A slab is released when the last view of it is gone."""
+    flight on one stream never alias).  A slab is released when the last view of it is gone.  A slab
+    that had to be created while the stream was being captured into a CUDA graph belongs to that graph
+    (its zero fill is a node of the graph) and is not reused by later calls outside the capture."""
     key = (device.index if isinstance(device, torch.device) else torch.device(device).index, stream)
+    capturing = torch.cuda.is_current_stream_capturing()
     hit = _scratch.get(key)
-    if hit is None or hit[1] >= _SLOTS:
-        hit = [torch.zeros(_SLOTS * _lib.SBNET_REDUCE_MASK_SCRATCH_INTS, dtype=torch.int32, device=device), 0]
+    if hit is None or hit[1] >= _SLOTS or (hit[2] and not capturing):
+        hit = [torch.zeros(_SLOTS * _lib.SBNET_REDUCE_MASK_SCRATCH_INTS, dtype=torch.int32, device=device), 0, capturing]
         _scratch[key] = hit
     k = hit[1]
     hit[1] = k + 1
@@ -169,7 +172,7 @@ def scratch_for(device, stream: int) -> tuple:
 
 
 def _reduce_mask_call(mask, dynamic_bcount, dynamic_bsize, dynamic_bstride, dynamic_boffset, tol, avgpool,
-                      counts, flags):
+                      counts, flags, scratch=None):
     _require_cuda(mask, "mask")
     N, H, W = _check_mask(mask)
     bch, bcw = _pair(dynamic_bcount, "dynamic_bcount")
@@ -179,7 +182,13 @@ def _reduce_mask_call(mask, dynamic_bcount, dynamic_bsize, dynamic_bstride, dyna
     with _on(mask.device):
         stream = _stream(mask.device)
         idx = torch.empty((max(N * bch * bcw, 0), 3), dtype=torch.int16, device=mask.device)
-        scratch, clean = scratch_for(mask.device, stream)
+        if scratch is None:
+            scratch, clean = scratch_for(mask.device, stream)
+        else:   # a slot of the caller's (e.g. one of a ring that is exchanged between ranks): zero-filled once
+            if scratch.dtype != torch.int32 or scratch.numel() < _lib.SBNET_REDUCE_MASK_SCRATCH_INTS or \
+                    scratch.device != mask.device or not scratch.is_contiguous():
+                raise ValueError("scratch must be a contiguous int32 device tensor of at least 4 elements")
+            clean = _lib.SBNET_SCRATCH_CLEAN
         _lib.check(_lib.load().sbnet_reduce_mask(
             mask.data_ptr(), N, H, W, float(tol), int(bool(avgpool)), boh, bow, bsh, bsw, bth, btw,
             bch, bcw, idx.data_ptr(), scratch.data_ptr(), None if counts is None else counts.data_ptr(),
@@ -208,15 +217,18 @@ def reduce_mask(mask: torch.Tensor, dynamic_bcount: Sequence[int], dynamic_bsize
 
 
 def reduce_mask_with_device_count(mask, dynamic_bcount, dynamic_bsize, dynamic_bstride, dynamic_boffset, tol,
-                                  avgpool=False, mask_stable=False, yield_core=False):
+                                  avgpool=False, mask_stable=False, yield_core=False, scratch=None):
     """:func:`reduce_mask` that also returns the count as a one-element device tensor (for a count
-    exchange between ranks, or for the ``*_dyn`` calls): ``(active_block_indices, bin_counts, count_dev)``."""
+    exchange between ranks, or for the ``*_dyn`` calls): ``(active_block_indices, bin_counts, count_dev)``.
+    ``scratch``: a 16-byte aligned, zero-filled int32 device tensor of 4 elements owned by the caller,
+    whose word 0 then receives the count (words 2..3 are left at zero, so the slot can be used again by
+    a later call on the same stream)."""
     _require_cuda(mask, "mask")   # before the pinned slot: a host mask must fail as an argument error
     counts = _pinned_count()
     flags = _lib.SBNET_COUNT_POLL | (_lib.SBNET_MASK_STABLE if mask_stable else 0) \
         | (_lib.SBNET_COUNT_YIELD if yield_core else 0)
     idx, count_dev = _reduce_mask_call(mask, dynamic_bcount, dynamic_bsize, dynamic_bstride, dynamic_boffset,
-                                       tol, avgpool, counts, flags)
+                                       tol, avgpool, counts, flags, scratch)
     return idx, counts, count_dev
 
 
