@@ -92,12 +92,13 @@ const char* sbnet_last_error(void);
  *                         sched_yield() between looks (for hosts that run one such thread per GPU on
  *                         shared cores).  An empty result is reported as ONE block with index (0,0,0),
  *                         as the reference does.
- *   SBNET_MASK_STABLE     the kernel is launched with programmatic stream serialization: its prologue
- *                         overlaps the tail of the kernel queued before it on `stream`, and everything
- *                         that touches scratch_dev or active_block_indices waits for that kernel.  With
- *                         this flag the MASK is read before that wait as well, which is only correct when
- *                         the mask is not produced by that preceding kernel (e.g. the previous layer's
- *                         scatter precedes, and the mask has been resident for longer).
+ *   SBNET_MASK_STABLE     every kernel of the library is launched with programmatic stream serialization:
+ *                         its CTAs may become resident while the kernel queued before it on `stream`
+ *                         drains, and touch global memory only once that kernel has completed.  With this
+ *                         flag reduce_mask reads the MASK before that point as well (scratch_dev and
+ *                         active_block_indices still wait), which is only correct when the mask is not
+ *                         produced by that preceding kernel (e.g. the previous layer's scatter precedes,
+ *                         and the mask has been resident for longer).
  *   Limits                N, bCntH, bCntW <= 32767 (int16 triples); N*bCntH*bCntW < 2^31 (int32 count),
  *                         larger products are rejected with SBNET_ERR_UNSUPPORTED.
  */
@@ -188,8 +189,9 @@ int sbnet_wait_timeouts(unsigned int* count);
  *   "tile_blocks"     > 0: small blocks sharing one tile, whatever the launch size               [SBNET_TILE_BLOCKS]
  *   "rm_kernel"       reduce_mask: 0 default, 1 register-fed band kernel, 2 one thread per block  [SBNET_RM_KERNEL]
  *   "rm_ctas_per_sm"  reduce_mask: CTAs per SM the column tiling aims at (default 8)             [SBNET_RM_CTAS_PER_SM]
- *   "rm_pdl"          reduce_mask: 0 launches without programmatic serialization (default 1)     [SBNET_RM_PDL]
- *   "tail_waves"      plane tiles: launches under this many resident waves get finer work items  [SBNET_TAIL_WAVES]
+ *   "rm_resident"     reduce_mask: at most this many CTAs resident per SM, 0 = no cap            [SBNET_RM_RESIDENT]
+ *   "pdl"             0: launch kernels without programmatic stream serialization (default 1)    [SBNET_PDL]
+ *   "tma_l2"          L2 promotion of image tensor maps: 0 none, 1 64 B, 2 128 B (default), 3 256 B [SBNET_TMA_L2]
  */
 int sbnet_set_option(const char* name, int value);
 int sbnet_get_option(const char* name, int* value);

@@ -125,8 +125,9 @@ Options& options()
         opt.tileBlocks = env_number("SBNET_TILE_BLOCKS", 0);
         opt.rmKernel = env_number("SBNET_RM_KERNEL", 0);
         opt.rmCtasPerSm = env_number("SBNET_RM_CTAS_PER_SM", 8);
-        opt.rmPdl = env_number("SBNET_RM_PDL", 1);
-        opt.tailSplit = env_number("SBNET_TAIL_WAVES", 4);
+        opt.rmResident = env_number("SBNET_RM_RESIDENT", 0);
+        opt.pdl = env_number("SBNET_PDL", 1);
+        opt.tmaL2 = env_number("SBNET_TMA_L2", 2);
     });
     return opt;
 }
@@ -140,8 +141,9 @@ struct OptionName {
 const OptionName kOptionNames[] = {
     {"planes", &sbnet::Options::planes},          {"disable_tma", &sbnet::Options::disableTma},
     {"tile_blocks", &sbnet::Options::tileBlocks}, {"rm_kernel", &sbnet::Options::rmKernel},
-    {"rm_ctas_per_sm", &sbnet::Options::rmCtasPerSm}, {"rm_pdl", &sbnet::Options::rmPdl},
-    {"tail_waves", &sbnet::Options::tailSplit},
+    {"rm_ctas_per_sm", &sbnet::Options::rmCtasPerSm}, {"pdl", &sbnet::Options::pdl},
+    {"rm_resident", &sbnet::Options::rmResident},
+    {"tma_l2", &sbnet::Options::tmaL2},
 };
 } // namespace
 

@@ -7,7 +7,30 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
+#include "options.h"
+
 namespace sbnet {
+
+// Every kernel of the library is launched with programmatic stream serialization: its CTAs may become
+// resident while the kernel queued before it on the stream drains, and they start their first global
+// memory access only behind griddepcontrol.wait (pdl_wait(), async_ptx.cuh), i.e. once that kernel has
+// completed and its writes are visible -- stream order as seen through memory is unchanged, the launch
+// latency and the prologue are hidden.  The `pdl` option set to 0 launches the ordinary way.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = options().pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 // ---- exact unsigned division by a runtime constant ----------------------------------------------
 // q = n / d for 0 <= n < 2^31, 1 <= d < 2^31, with one mul.hi, one add and one shift.

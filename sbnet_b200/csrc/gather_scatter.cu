@@ -107,22 +107,24 @@ __device__ __forceinline__ void rows_item(const BlockArgs& a, const RowPlan& p, 
 template <int VB, int MODE, typename T>
 __global__ void __launch_bounds__(kThreads) rows_kernel(const BlockArgs a, const RowPlan p)
 {
-    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
+    pdl_wait();   // nothing is read or written before the kernel queued ahead of this one is done
     uint32_t ib, chunk;
     p.chunksPerBlock.divmod(blockIdx.x, ib, chunk);
     rows_item<VB, MODE, T>(a, p, ib, chunk);
+    pdl_launch_dependents();
 }
 
 template <int VB, int MODE, typename T>
 __global__ void __launch_bounds__(kThreads) rows_kernel_dyn(const BlockArgs a, const RowPlan p)
 {
-    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
+    pdl_wait();   // nothing is read or written before the kernel queued ahead of this one is done
     const long long nItems = (long long)active_count(a) * p.chunksPerBlock.div;
     for (long long item = blockIdx.x; item < nItems; item += gridDim.x) {
         uint32_t ib, chunk;
         p.chunksPerBlock.divmod((uint32_t)item, ib, chunk);
         rows_item<VB, MODE, T>(a, p, ib, chunk);
     }
+    pdl_launch_dependents();
 }
 
 // ---- [nB,C,R,S] layout ---------------------------------------------------------------------------
@@ -169,7 +171,7 @@ template <int VB, typename T> __device__ __forceinline__ typename Vec<VB>::type 
 template <int VB, int MODE, typename T>
 __global__ void __launch_bounds__(kThreads, 4) planes_kernel(const BlockArgs a, const PlanePlan p)
 {
-    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
+    pdl_wait();   // nothing is read or written before the kernel queued ahead of this one is done
     typedef typename Vec<VB>::type V;
     constexpr int EPV = VB / (int)sizeof(T);   // elements per vector
     __shared__ __align__(16) unsigned char tileRaw[kTileBytes];
@@ -267,6 +269,7 @@ __global__ void __launch_bounds__(kThreads, 4) planes_kernel(const BlockArgs a, 
             __syncthreads();
         }
     }
+    pdl_launch_dependents();
 }
 
 // ---- host side -----------------------------------------------------------------------------------
@@ -323,12 +326,12 @@ static void launch_rows(const BlockArgs& a, cudaStream_t stream)
     p.chunksPerBlock = FastDiv((uint32_t)nChunks);
     const long long nItems = (long long)a.numActive * nChunks;
     if (a.num_active_dev == nullptr && nItems <= 0x7fffffffll) {
-        rows_kernel<VB, MODE, T><<<(unsigned)nItems, kThreads, 0, stream>>>(a, p);
+        launch_pdl(rows_kernel<VB, MODE, T>, dim3((unsigned)nItems), dim3(kThreads), 0, stream, a, p);
     } else {
         static const int perSm = ctas_per_sm(rows_kernel_dyn<VB, MODE, T>, kThreads);
         const int wave = perSm * sm_count();
         const int grid = (int)(nItems < wave ? nItems : wave);
-        rows_kernel_dyn<VB, MODE, T><<<grid, kThreads, 0, stream>>>(a, p);
+        launch_pdl(rows_kernel_dyn<VB, MODE, T>, dim3(grid), dim3(kThreads), 0, stream, a, p);
     }
 }
 
@@ -367,7 +370,7 @@ static void launch_planes(const BlockArgs& a, cudaStream_t stream)
     const int wave = perSm * sm_count();
     const bool perItem = a.num_active_dev == nullptr && nItems <= 0x7fffffffll;
     const unsigned grid = (unsigned)(perItem ? nItems : (nItems < wave ? nItems : wave));
-    planes_kernel<VB, MODE, T><<<grid, kThreads, 0, stream>>>(a, p);
+    launch_pdl(planes_kernel<VB, MODE, T>, dim3(grid), dim3(kThreads), 0, stream, a, p);
 }
 
 template <int MODE, typename T>
@@ -458,7 +461,7 @@ __global__ void __launch_bounds__(kThreads) copy_kernel(uint4* __restrict__ dst,
                                                         unsigned char* dstTail,
                                                         const unsigned char* srcTail, int tailBytes)
 {
-    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
+    pdl_wait();   // nothing is read or written before the kernel queued ahead of this one is done
     const size_t base = (size_t)blockIdx.x * (kThreads * kCopyUnroll) + threadIdx.x;
     uint4 v[kCopyUnroll];
 #pragma unroll
@@ -471,14 +474,16 @@ __global__ void __launch_bounds__(kThreads) copy_kernel(uint4* __restrict__ dst,
             dst[base + u * kThreads] = v[u];
     if (blockIdx.x == 0 && (int)threadIdx.x < tailBytes)
         dstTail[threadIdx.x] = srcTail[threadIdx.x];
+    pdl_launch_dependents();
 }
 
 __global__ void copy_bytes_kernel(unsigned char* dst, const unsigned char* src, size_t n)
 {
-    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
+    pdl_wait();   // nothing is read or written before the kernel queued ahead of this one is done
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
         dst[i] = src[i];
+    pdl_launch_dependents();
 }
 
 cudaError_t launch_copy(void* dst, const void* src, size_t bytes, cudaStream_t stream)
@@ -492,16 +497,14 @@ cudaError_t launch_copy(void* dst, const void* src, size_t bytes, cudaStream_t s
         const int tail = (int)(bytes - nVec * 16);
         const size_t want = (nVec + kThreads * kCopyUnroll - 1) / (kThreads * kCopyUnroll);
         const unsigned grid = (unsigned)(want < 1 ? 1 : want);
-        copy_kernel<<<grid, kThreads, 0, stream>>>(
-            reinterpret_cast<uint4*>(dst), reinterpret_cast<const uint4*>(src), nVec,
-            reinterpret_cast<unsigned char*>(dst) + nVec * 16,
-            reinterpret_cast<const unsigned char*>(src) + nVec * 16, tail);
+        launch_pdl(copy_kernel, dim3(grid), dim3(kThreads), 0, stream, reinterpret_cast<uint4*>(dst),
+                   reinterpret_cast<const uint4*>(src), nVec, reinterpret_cast<unsigned char*>(dst) + nVec * 16,
+                   reinterpret_cast<const unsigned char*>(src) + nVec * 16, tail);
     } else {
         long long want = (long long)((bytes + kThreads - 1) / kThreads);
         const int grid = (int)(want < cap ? want : cap);
-        copy_bytes_kernel<<<grid, kThreads, 0, stream>>>(reinterpret_cast<unsigned char*>(dst),
-                                                         reinterpret_cast<const unsigned char*>(src),
-                                                         bytes);
+        launch_pdl(copy_bytes_kernel, dim3(grid), dim3(kThreads), 0, stream, reinterpret_cast<unsigned char*>(dst),
+                   reinterpret_cast<const unsigned char*>(src), bytes);
     }
     return cudaGetLastError();
 }

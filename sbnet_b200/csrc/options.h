@@ -13,8 +13,9 @@ struct Options {
     int tileBlocks;    // > 0: blocks per shared tile regardless of the launch size (SBNET_TILE_BLOCKS)
     int rmKernel;      // reduce_mask: 0 default, 1 band kernel, 2 one thread per block (SBNET_RM_KERNEL)
     int rmCtasPerSm;   // reduce_mask tile kernel: CTAs per SM the column tiling aims at (SBNET_RM_CTAS_PER_SM)
-    int rmPdl;         // reduce_mask tile kernel: launch with programmatic serialization (SBNET_RM_PDL)
-    int tailSplit;     // plane tiles: cut the tiles of launches under this many resident waves (SBNET_TAIL_WAVES)
+    int rmResident;    // reduce_mask tile kernel: at most this many CTAs resident per SM, 0 = no cap (SBNET_RM_RESIDENT)
+    int pdl;           // launch every kernel with programmatic stream serialization (SBNET_PDL, default 1)
+    int tmaL2;         // L2 promotion of the image tensor maps: 0 none, 1 64 B, 2 128 B, 3 256 B (SBNET_TMA_L2, default 2)
 };
 
 Options& options();

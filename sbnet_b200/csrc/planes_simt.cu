@@ -75,7 +75,7 @@ constexpr int kTileMulti = 2;    // blocks of at most 192 pixels: as many whole 
 template <typename T, int SHAPE, bool ODD = false>
 __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gather_simt(const BlockArgs a, const SimtPlan p)
 {
-    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
+    pdl_wait();   // nothing global is read or written before the kernel queued ahead of this one is done
     constexpr bool PCH = SHAPE == kTileChunked, MB = SHAPE == kTileMulti;
     static_assert(!ODD || (sizeof(T) == 2 && !PCH), "odd rows: fp16, whole blocks only");
     __shared__ __align__(1024) unsigned char tileRaw[kPsTileBytes];
@@ -145,6 +145,7 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
                 sts128(dst + (uint32_t)(px0 + 32 * k) * 128u, v[k]);
     }
     __syncthreads();
+    pdl_launch_dependents();   // this CTA's loads have landed: the next kernel's CTAs may take the slots that free up
 
     // ---- tile -> registers (16-byte channel groups), then registers -> tile in [channel][pixel] order
     const int nTasks = ((U + 15) >> 4) * 128;
@@ -311,7 +312,7 @@ template <int MODE, typename T, int GW, int SHAPE>
 __global__ void __launch_bounds__(kPsThreads, MODE == kScatterAdd ? 2 : 3)
 planes_scatter_simt(const BlockArgs a, const SimtPlan p)
 {
-    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
+    pdl_wait();   // nothing global is read or written before the kernel queued ahead of this one is done
     constexpr bool PCH = SHAPE == kTileChunked, MB = SHAPE == kTileMulti;
     static_assert(!PCH || GW > 1, "pixel chunks copy in whole 8- or 16-byte units");
     static_assert(GW != 0 || sizeof(T) == 2, "odd rows of halves: fp16 only");
@@ -606,6 +607,7 @@ planes_scatter_simt(const BlockArgs a, const SimtPlan p)
     }
     __syncthreads();   // the tile is reused by the next item
     }
+    pdl_launch_dependents();
 }
 
 // Pixels of a multiple of 16 bytes (the last 128-byte chunk may be partial), 16-byte aligned buffers.
@@ -704,7 +706,7 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
         const long long wave = (long long)sm_count() * 3;
         grid = (unsigned)(nItems < wave ? nItems : wave);
     }
-#define SBNET_PS(KERNEL) KERNEL<<<grid, kPsThreads, 0, stream>>>(a, p)
+#define SBNET_PS(KERNEL) launch_pdl(KERNEL, dim3(grid), dim3(kPsThreads), 0, stream, a, p)
     const int shape = pch ? kTileChunked : (multi ? kTileMulti : kTileSingle);
 #define SBNET_PS_G(T_)                                                \
     do {                                                              \

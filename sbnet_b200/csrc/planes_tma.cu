@@ -137,13 +137,13 @@ template <typename T>
 __global__ void __launch_bounds__(kTmaThreads, 1)
 planes_gather_tma(const __grid_constant__ CUtensorMap imageMap, const BlockArgs a, const TmaPlan p)
 {
-    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
     extern __shared__ unsigned char dynSmem[];
     __shared__ int abortFlag;
     constexpr int EPW = 4 / (int)sizeof(T);        // pixels per 32-bit word of a channel plane
     constexpr int CPG = 16 / (int)sizeof(T);       // channels per 16-byte group
     const Ring ring = carve(dynSmem, p);
     ring_init(ring, p, &abortFlag);
+    pdl_wait();   // nothing global is read or written before the kernel queued ahead of this one is done
 
     const long long nItems = (long long)device_count(a) * p.cChunks.div;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -168,6 +168,7 @@ planes_gather_tma(const __grid_constant__ CUtensorMap imageMap, const BlockArgs 
             }
             drain_loads(ring, p, k);
         }
+        pdl_launch_dependents();
         return;
     }
 
@@ -229,6 +230,7 @@ planes_gather_tma(const __grid_constant__ CUtensorMap imageMap, const BlockArgs 
         }
         __syncwarp();
     }
+    pdl_launch_dependents();
     if (threadIdx.x == 0)
         bulk_wait_all();
 }
@@ -237,7 +239,6 @@ planes_gather_tma(const __grid_constant__ CUtensorMap imageMap, const BlockArgs 
 template <int MODE, typename T>
 __global__ void __launch_bounds__(kTmaThreads, 1) planes_scatter_tma(const BlockArgs a, const TmaPlan p)
 {
-    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
     extern __shared__ unsigned char dynSmem[];
     __shared__ int abortFlag;
     constexpr int EPW = 4 / (int)sizeof(T);
@@ -246,6 +247,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) planes_scatter_tma(const Block
     constexpr int kMaxTasks = ((kMaxPixels / EPW + 15) / 16 + 1) / 2;
     const Ring ring = carve(dynSmem, p);
     ring_init(ring, p, &abortFlag);
+    pdl_wait();   // nothing global is read or written before the kernel queued ahead of this one is done
 
     const long long nItems = (long long)device_count(a) * p.cChunks.div;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -268,6 +270,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) planes_scatter_tma(const Block
             }
             drain_loads(ring, p, k);
         }
+        pdl_launch_dependents();
         return;
     }
 
@@ -355,6 +358,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) planes_scatter_tma(const Block
         if (lane == 0)
             mbar_arrive(ring.empty0 + 8u * s);
     }
+    pdl_launch_dependents();
 }
 
 // ---- gather, one short CTA per tile, fed by TMA ---------------------------------------------------
@@ -403,7 +407,6 @@ template <typename T, bool ODD = false>
 __global__ void __launch_bounds__(kTileThreads, 4)
 planes_gather_tma_tile(const __grid_constant__ CUtensorMap imageMap, const BlockArgs a, const TmaTilePlan p)
 {
-    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
     static_assert(!ODD || sizeof(T) == 2, "odd rows of halves: 16-bit types only");
     extern __shared__ unsigned char dynSmem[];
     __shared__ __align__(8) unsigned long long barStorage;
@@ -417,6 +420,14 @@ planes_gather_tma_tile(const __grid_constant__ CUtensorMap imageMap, const Block
     uint32_t grp, cc;
     p.cChunks.divmod(blockIdx.x, grp, cc);
     const uint32_t ib = grp * (uint32_t)p.blocksPerItem;
+    if (threadIdx.x == 0) {
+        abortFlag = 0;
+        mbar_init(bar, 1);
+        mbar_init_fence();
+        fence_async_smem();
+    }
+    __syncthreads();
+    pdl_wait();   // nothing global is read or written before the kernel queued ahead of this one is done
     // With the block count on the device the grid covers the largest possible count and the CTAs
     // past the actual one leave at once.
     const int nActive = device_count(a);
@@ -425,14 +436,6 @@ planes_gather_tma_tile(const __grid_constant__ CUtensorMap imageMap, const Block
     const int nBlk = min(p.blocksPerItem, nActive - (int)ib);
     const int nG = min(8, p.groups - 8 * (int)cc);
     const uint32_t regionBytes = (uint32_t)p.regionPixels * 128u;
-
-    if (threadIdx.x == 0) {
-        abortFlag = 0;
-        mbar_init(bar, 1);
-        mbar_init_fence();
-        fence_async_smem();
-    }
-    __syncthreads();
     if (threadIdx.x == 0) {
         mbar_expect_tx(bar, (uint32_t)nBlk * (uint32_t)p.pixels * 128u);
         for (int b = 0; b < nBlk; ++b) {
@@ -443,6 +446,7 @@ planes_gather_tma_tile(const __grid_constant__ CUtensorMap imageMap, const Block
     }
     if (!tile_arrived(bar, &abortFlag))
         return;
+    pdl_launch_dependents();   // this CTA's loads have landed: the next kernel's CTAs may take the slots that free up
 
     // ---- tile -> registers (16-byte channel groups), then registers -> tile in [channel][pixel] order
     const int U = nBlk * p.units;
@@ -545,7 +549,6 @@ __global__ void __launch_bounds__(kTileThreads, 4)
 planes_gather_tma_rows(const __grid_constant__ CUtensorMap mapFull, const __grid_constant__ CUtensorMap mapLast,
                        const BlockArgs a, const TmaRowsPlan p)
 {
-    pdl_launch_dependents();   // a kernel queued behind this one with programmatic serialization may start its prologue
     extern __shared__ unsigned char dynSmem[];
     __shared__ __align__(8) unsigned long long barStorage;
     __shared__ int abortFlag;
@@ -558,6 +561,7 @@ planes_gather_tma_rows(const __grid_constant__ CUtensorMap mapFull, const __grid
     uint32_t rest, cc, ib, kc;
     p.cChunks.divmod(blockIdx.x, rest, cc);
     p.rChunks.divmod(rest, ib, kc);
+    pdl_wait();   // nothing global is read or written before the kernel queued ahead of this one is done
     if ((int)ib >= device_count(a))   // count on the device: the grid covers the largest possible count
         return;
     const bool last = kc + 1 == p.rChunks.div;
@@ -582,6 +586,7 @@ planes_gather_tma_rows(const __grid_constant__ CUtensorMap mapFull, const __grid
     }
     if (!tile_arrived(bar, &abortFlag))
         return;
+    pdl_launch_dependents();
 
     // ---- tile -> registers (16-byte channel groups), then registers -> tile in [channel][pixel] order
     const int nTasks = ((U + 15) >> 4) * 128;
@@ -711,7 +716,7 @@ static bool image_map(const BlockArgs& a, int itemsize, int boxW, int boxH, CUte
 {
     struct Entry {
         const void* base;
-        int N, H, W, C, itemsize, boxW, boxH;
+        int N, H, W, C, itemsize, boxW, boxH, l2;
         CUtensorMap map;
     };
     constexpr int kEntries = 8;
@@ -720,7 +725,7 @@ static bool image_map(const BlockArgs& a, int itemsize, int boxW, int boxH, CUte
     for (int i = 0; i < used; ++i) {
         const Entry& e = cache[i];
         if (e.base == a.image && e.N == a.N && e.H == a.H && e.W == a.W && e.C == a.C && e.itemsize == itemsize &&
-            e.boxW == boxW && e.boxH == boxH) {
+            e.boxW == boxW && e.boxH == boxH && e.l2 == options().tmaL2) {
             *out = e.map;
             return true;
         }
@@ -733,12 +738,16 @@ static bool image_map(const BlockArgs& a, int itemsize, int boxW, int boxH, CUte
                                    (cuuint64_t)a.H * a.W * a.C * itemsize};
     const cuuint32_t box[4] = {(cuuint32_t)(128 / itemsize), (cuuint32_t)boxW, (cuuint32_t)boxH, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
+    // how much of a line the L2 fetches from DRAM around every 128-byte piece the box touches
+    static const CUtensorMapL2promotion promotion[4] = {CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_64B,
+                                                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B};
     if (enc(out, itemsize == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, a.image, dims,
-            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promotion[options().tmaL2 & 3],
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
     Entry& e = cache[next];
     e.base = a.image, e.N = a.N, e.H = a.H, e.W = a.W, e.C = a.C, e.itemsize = itemsize, e.boxW = boxW, e.boxH = boxH;
+    e.l2 = options().tmaL2;
     e.map = *out;
     next = (next + 1) % kEntries;
     if (used < kEntries)
@@ -818,11 +827,11 @@ cudaError_t launch_planes_tma(const BlockArgs& a, int dtype, int mode, cudaStrea
         if (dtype == 0) {
             if (cudaError_t e = set_smem((const void*)planes_gather_tma<float>, smem))
                 return e;
-            planes_gather_tma<float><<<grid, kTmaThreads, smem, stream>>>(map, a, p);
+            launch_pdl(planes_gather_tma<float>, dim3(grid), dim3(kTmaThreads), smem, stream, map, a, p);
         } else {
             if (cudaError_t e = set_smem((const void*)planes_gather_tma<__half>, smem))
                 return e;
-            planes_gather_tma<__half><<<grid, kTmaThreads, smem, stream>>>(map, a, p);
+            launch_pdl(planes_gather_tma<__half>, dim3(grid), dim3(kTmaThreads), smem, stream, map, a, p);
         }
         *taken = true;
         return cudaGetLastError();
@@ -836,7 +845,7 @@ cudaError_t launch_planes_tma(const BlockArgs& a, int dtype, int mode, cudaStrea
     do {                                                                                          \
         if (cudaError_t e = set_smem((const void*)planes_scatter_tma<MODE_, T_>, smem))       \
             return e;                                                                             \
-        planes_scatter_tma<MODE_, T_><<<grid, kTmaThreads, smem, stream>>>(a, p);                 \
+        launch_pdl(planes_scatter_tma<MODE_, T_>, dim3(grid), dim3(kTmaThreads), smem, stream, a, p); \
     } while (0)
     if (dtype == 0) {
         if (mode == kScatterSet)
@@ -891,15 +900,15 @@ cudaError_t launch_gather_tma_tile(const BlockArgs& a, int dtype, int blocksPerI
     if (dtype == 0) {
         if (cudaError_t e = set_smem((const void*)planes_gather_tma_tile<float>, smem))
             return e;
-        planes_gather_tma_tile<float><<<(unsigned)nItems, kTileThreads, smem, stream>>>(map, a, p);
+        launch_pdl(planes_gather_tma_tile<float>, dim3((unsigned)nItems), dim3(kTileThreads), smem, stream, map, a, p);
     } else if (odd) {
         if (cudaError_t e = set_smem((const void*)planes_gather_tma_tile<__half, true>, smem))
             return e;
-        planes_gather_tma_tile<__half, true><<<(unsigned)nItems, kTileThreads, smem, stream>>>(map, a, p);
+        launch_pdl(planes_gather_tma_tile<__half, true>, dim3((unsigned)nItems), dim3(kTileThreads), smem, stream, map, a, p);
     } else {
         if (cudaError_t e = set_smem((const void*)planes_gather_tma_tile<__half>, smem))
             return e;
-        planes_gather_tma_tile<__half><<<(unsigned)nItems, kTileThreads, smem, stream>>>(map, a, p);
+        launch_pdl(planes_gather_tma_tile<__half>, dim3((unsigned)nItems), dim3(kTileThreads), smem, stream, map, a, p);
     }
     *taken = true;
     return cudaGetLastError();
@@ -935,11 +944,11 @@ cudaError_t launch_gather_tma_rows(const BlockArgs& a, int dtype, cudaStream_t s
     if (dtype == 0) {
         if (cudaError_t e = set_smem((const void*)planes_gather_tma_rows<float>, smem))
             return e;
-        planes_gather_tma_rows<float><<<(unsigned)nItems, kTileThreads, smem, stream>>>(maps[0], maps[1], a, p);
+        launch_pdl(planes_gather_tma_rows<float>, dim3((unsigned)nItems), dim3(kTileThreads), smem, stream, maps[0], maps[1], a, p);
     } else {
         if (cudaError_t e = set_smem((const void*)planes_gather_tma_rows<__half>, smem))
             return e;
-        planes_gather_tma_rows<__half><<<(unsigned)nItems, kTileThreads, smem, stream>>>(maps[0], maps[1], a, p);
+        launch_pdl(planes_gather_tma_rows<__half>, dim3((unsigned)nItems), dim3(kTileThreads), smem, stream, maps[0], maps[1], a, p);
     }
     *taken = true;
     return cudaGetLastError();

@@ -15,9 +15,9 @@
 //    mbarrier, so the load phase costs no registers and no load instructions.  Eight lanes then sum
 //    (or test) the window of one block straight out of shared memory, combine by shuffles, and the
 //    first warp ballots the verdicts, reserves the tile's run of the index list with ONE 64-bit atomic
-//    and writes the triples.  The kernel is launched with the programmatic-serialization attribute:
-//    its prologue (and, when the caller vouches for the mask, its loads) overlap the tail of the
-//    kernel queued before it.
+//    and writes the triples.  Like every kernel of the library it is launched with programmatic stream
+//    serialization; when the caller vouches for the mask, not only its prologue but its loads too
+//    overlap the tail of the kernel queued before it.
 //  * reduce_mask_band (any other shape): threads own image columns (four at a time, one 128-bit load
 //    per row) and run down the band's rows keeping all loads of a batch in flight; per-column partial
 //    results go to shared memory, then one thread per block combines the columns of its window.
@@ -52,6 +52,8 @@ struct RmArgs {
     int bOffsH, bOffsW, bSzH, bSzW, bStrH, bStrW, bCntH, bCntW;
     int tileBlocks;        // block columns per CTA
     int earlyLoads;        // tile kernel: the mask may be read before the preceding kernel has finished
+    int tileFloats;        // tile kernel: floats of shared memory reserved for the tile itself
+    int tileCols;          // tile kernel: columns reserved per partial-result array behind the tile
     float area;            // (float)(bSzH*bSzW)
 };
 
@@ -204,47 +206,71 @@ __global__ void __launch_bounds__(kRmTileMaxThreads) reduce_mask_tile(const RmAr
         }
     }
 
-    // ---- window of block b: eight lanes stride over its columns, each running down the rows
-    const float* tileF = reinterpret_cast<const float*>(rmSmem);
+    pdl_launch_dependents();   // the tile is here: the next kernel's CTAs may take the slots that free up
+    // ---- columns: a thread owns four neighbouring columns and runs down the tile's rows with 128-bit
+    // shared-memory loads (a warp reads 512 contiguous bytes per instruction: no bank conflicts), leaving
+    // one partial result per column behind the tile
+    float* colVal = reinterpret_cast<float*>(rmSmem) + (size_t)a.tileFloats;   // [nCols] sum / any-flag
+    float* colMag = colVal + a.tileCols;                                        // [nCols] sum of magnitudes (AVG)
+    for (int c4 = threadIdx.x; c4 < (nCols >> 2); c4 += blockDim.x) {
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, mag[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const uint32_t at = tile + (uint32_t)c4 * 16u;
+#pragma unroll 6
+        for (int r = 0; r < nRows; ++r) {
+            const uint4 q = lds128(at + (uint32_t)(r * nCols) * 4u);
+            const float v[4] = {__uint_as_float(q.x), __uint_as_float(q.y), __uint_as_float(q.z), __uint_as_float(q.w)};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (AVG) {
+                    acc[j] = __fadd_rn(acc[j], v[j]);
+                    mag[j] = __fadd_rn(mag[j], fabsf(v[j]));
+                } else {
+                    acc[j] = (v[j] > a.tol) ? 1.0f : acc[j];
+                }
+            }
+        }
+        *reinterpret_cast<float4*>(colVal + 4 * c4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        if (AVG)
+            *reinterpret_cast<float4*>(colMag + 4 * c4) = make_float4(mag[0], mag[1], mag[2], mag[3]);
+    }
+    __syncthreads();
+
+    // ---- window of block b: eight lanes stride over its columns' partial results and combine by shuffles
     // (whole warps take every trip: lanes past the last block hold zeros and shuffle along)
     for (int t0 = warp * 32; t0 < nBlk * kRmLanesPerBlock; t0 += blockDim.x) {
         const int t = t0 + lane;
         const int b = t / kRmLanesPerBlock, g = t % kRmLanesPerBlock;
         const bool mine = b < nBlk;
         const int w0 = a.bOffsW + (bw0 + b) * a.bStrW;
-        const int wBeg = max(w0, 0), wEnd = mine ? min(w0 + a.bSzW, a.W) : 0;
+        const int wBeg = max(w0, 0), wEnd = (mine && haveTile) ? min(w0 + a.bSzW, a.W) : 0;
         float s = 0.0f, m = 0.0f;
-        bool any = false;
         for (int c = wBeg + g - cBeg; c < wEnd - cBeg; c += kRmLanesPerBlock) {
-            const float* col = tileF + c;
-#pragma unroll 6
-            for (int r = 0; r < nRows; ++r) {
-                const float v = col[r * nCols];
-                if (AVG) {
-                    s = __fadd_rn(s, v);
-                    m = __fadd_rn(m, fabsf(v));
-                } else {
-                    any |= v > a.tol;
-                }
+            if (AVG) {
+                s = __fadd_rn(s, colVal[c]);
+                m = __fadd_rn(m, colMag[c]);
+            } else {
+                s = fmaxf(s, colVal[c]);
             }
         }
-        bool active = false;
-        if (AVG) {
 #pragma unroll
-            for (int d = kRmLanesPerBlock / 2; d > 0; d >>= 1) {   // a block's lanes are neighbours in one warp
+        for (int d = kRmLanesPerBlock / 2; d > 0; d >>= 1) {   // a block's lanes are neighbours in one warp
+            if (AVG) {
                 s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, d));
                 m = __fadd_rn(m, __shfl_xor_sync(0xffffffffu, m, d));
+            } else {
+                s = fmaxf(s, __shfl_xor_sync(0xffffffffu, s, d));
             }
-            if (g == 0 && mine) {
-                const float terms = (float)nRows * (float)max(wEnd - wBeg, 0);
-                active = avg_verdict(a, s, m, terms, n, bh, bw0 + b);
-            }
-        } else {
-            const unsigned hits = __ballot_sync(0xffffffffu, any);
-            active = ((hits >> (lane & ~(kRmLanesPerBlock - 1))) & ((1u << kRmLanesPerBlock) - 1u)) != 0u;
         }
-        if (g == 0 && mine)
+        if (g == 0 && mine) {
+            bool active;
+            if (AVG) {
+                const float terms = (float)nRows * (float)max(min(w0 + a.bSzW, a.W) - wBeg, 0);
+                active = avg_verdict(a, s, m, terms, n, bh, bw0 + b);
+            } else {
+                active = s > 0.0f;
+            }
             verdict[b] = active ? 1 : 0;
+        }
     }
     __syncthreads();
 
@@ -280,6 +306,7 @@ __global__ void __launch_bounds__(kRmThreads, 3) reduce_mask_band(const RmArgs a
     __shared__ unsigned wordBase[kRmMaxCols / 32 + 1];  // exclusive prefix of popc(ballots)
     __shared__ unsigned ctaBase;
 
+    pdl_wait();   // nothing global is read or written before the kernel queued ahead of this one is done
     const int n = blockIdx.z, bh = blockIdx.y;
     const int bw0 = blockIdx.x * a.tileBlocks;
     const int bwEnd = min(bw0 + a.tileBlocks, a.bCntW);
@@ -406,6 +433,7 @@ __global__ void __launch_bounds__(kRmThreads, 3) reduce_mask_band(const RmArgs a
 template <bool AVG>
 __global__ void __launch_bounds__(kRmThreads) reduce_mask_naive(const RmArgs a)
 {
+    pdl_wait();   // nothing global is read or written before the kernel queued ahead of this one is done
     const long long total = (long long)a.N * a.bCntH * a.bCntW;
     const long long stride = (long long)gridDim.x * kRmThreads;
     const long long rounds = (total + stride - 1) / stride;
@@ -467,7 +495,7 @@ static int tile_blocks_for(int N, int H, int W, int bSzH, int bSzW, int bStrW, i
 {
     const long long rows = bSzH < H ? bSzH : H;
     // widest run of block columns whose pixel span (plus the rounding to 16-byte groups) fits
-    const long long maxCols = kRmTileSmemMax / 4 / rows;
+    const long long maxCols = kRmTileSmemMax / 4 / (rows + 2);
     long long fit = (maxCols - 9 - bSzW) >= 0 ? (maxCols - 9 - bSzW) / bStrW + 1 : 0;
     if (fit > kRmTileMaxBlocks)
         fit = kRmTileMaxBlocks;
@@ -509,27 +537,25 @@ cudaError_t launch_reduce_mask(const float* mask, int N, int H, int W, float tol
         long long cols = ((long long)(tb - 1) * bStrW + bSzW + 9) & ~3ll;
         if (cols > W)
             cols = W;
-        const size_t smem = (size_t)rows * (size_t)cols * 4;
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((bCntW + tb - 1) / tb, bCntH, N);
-        cfg.blockDim = dim3((unsigned)((tb * kRmLanesPerBlock + 31) & ~31));
-        cfg.dynamicSmemBytes = smem;
-        cfg.stream = stream;
-        // programmatic serialization: this kernel's prologue may overlap the tail of the kernel queued
-        // before it; everything that depends on that kernel sits behind griddepcontrol.wait
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = options().rmPdl ? 1 : 0;
+        a.tileFloats = (int)(rows * cols), a.tileCols = (int)cols;
+        size_t smem = ((size_t)rows + 2) * (size_t)cols * 4;   // the tile + two rows of per-column partial results
+        // fewer, larger shared-memory claims per SM keep that many CTAs from being resident at once: the
+        // CTAs of a later wave then load while those of an earlier one reduce
+        if (options().rmResident > 0) {
+            const size_t want = (size_t)(220 * 1024) / (size_t)options().rmResident - 1024;
+            if (want > smem && want <= (size_t)kRmTileSmemMax)
+                smem = want;
+        }
+        const dim3 grid((bCntW + tb - 1) / tb, bCntH, N);
+        const dim3 block((unsigned)((tb * kRmLanesPerBlock + 31) & ~31));
         if (avgpool) {
             if (cudaError_t e = tile_smem_limit<true>())
                 return e;
-            return cudaLaunchKernelEx(&cfg, reduce_mask_tile<true>, a);
+            return launch_pdl(reduce_mask_tile<true>, grid, block, smem, stream, a);
         }
         if (cudaError_t e = tile_smem_limit<false>())
             return e;
-        return cudaLaunchKernelEx(&cfg, reduce_mask_tile<false>, a);
+        return launch_pdl(reduce_mask_tile<false>, grid, block, smem, stream, a);
     }
 
     // widest run of block columns whose pixel span (plus 4-column rounding) fits the staging area
@@ -540,14 +566,14 @@ cudaError_t launch_reduce_mask(const float* mask, int N, int H, int W, float tol
         const dim3 grid((bCntW + a.tileBlocks - 1) / a.tileBlocks, bCntH, N);
         if (avgpool) {
             if (vec4)
-                reduce_mask_band<true, true><<<grid, kRmThreads, 0, stream>>>(a);
+                launch_pdl(reduce_mask_band<true, true>, grid, dim3(kRmThreads), 0, stream, a);
             else
-                reduce_mask_band<true, false><<<grid, kRmThreads, 0, stream>>>(a);
+                launch_pdl(reduce_mask_band<true, false>, grid, dim3(kRmThreads), 0, stream, a);
         } else {
             if (vec4)
-                reduce_mask_band<false, true><<<grid, kRmThreads, 0, stream>>>(a);
+                launch_pdl(reduce_mask_band<false, true>, grid, dim3(kRmThreads), 0, stream, a);
             else
-                reduce_mask_band<false, false><<<grid, kRmThreads, 0, stream>>>(a);
+                launch_pdl(reduce_mask_band<false, false>, grid, dim3(kRmThreads), 0, stream, a);
         }
     } else {
         a.tileBlocks = 1;
@@ -556,9 +582,9 @@ cudaError_t launch_reduce_mask(const float* mask, int N, int H, int W, float tol
                                    ? (total + kRmThreads - 1) / kRmThreads
                                    : 1184);
         if (avgpool)
-            reduce_mask_naive<true><<<grid, kRmThreads, 0, stream>>>(a);
+            launch_pdl(reduce_mask_naive<true>, dim3(grid), dim3(kRmThreads), 0, stream, a);
         else
-            reduce_mask_naive<false><<<grid, kRmThreads, 0, stream>>>(a);
+            launch_pdl(reduce_mask_naive<false>, dim3(grid), dim3(kRmThreads), 0, stream, a);
     }
     return cudaGetLastError();
 }

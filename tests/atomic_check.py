@@ -14,6 +14,8 @@ def cover_of(bsize, bstride):
 def to_numpy(t):
     if isinstance(t, np.ndarray):
         return t
+    if isinstance(t, (list, tuple, int)):
+        return np.asarray(t)
     from cuda_ops import to_numpy as torch_to_numpy
     return torch_to_numpy(t)
 

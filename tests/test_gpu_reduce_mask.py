@@ -7,18 +7,19 @@ from sbnet_b200 import configs as cfg
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True, params=["tile", "tile_many_ctas", "tile_few_ctas", "tile_no_pdl", "band", "per_block"])
+@pytest.fixture(autouse=True, params=["tile", "tile_many_ctas", "tile_few_ctas", "tile_no_pdl", "tile_two_resident", "band", "per_block"])
 def rm_kernel(request):
     """Every case runs through each reduce_mask kernel: the TMA-fed tile kernel (default column
-    tiling, the narrowest and the widest tiles, and without programmatic serialization), the
+    tiling, the narrowest and the widest tiles, without programmatic serialization, and with a cap on
+    the CTAs resident per SM), the
     register-fed band kernel, and the one-thread-per-block kernel."""
     import torch
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     from conftest import library_options
     opts = {"tile": {}, "tile_many_ctas": {"rm_ctas_per_sm": 10000}, "tile_few_ctas": {"rm_ctas_per_sm": 1},
-            "tile_no_pdl": {"rm_pdl": 0}, "band": {"rm_kernel": 1}, "per_block": {"rm_kernel": 2}}[request.param]
-    with library_options(**{"rm_kernel": 0, "rm_ctas_per_sm": 8, "rm_pdl": 1, **opts}):
+            "tile_no_pdl": {"pdl": 0}, "tile_two_resident": {"rm_resident": 2}, "band": {"rm_kernel": 1}, "per_block": {"rm_kernel": 2}}[request.param]
+    with library_options(**{"rm_kernel": 0, "rm_ctas_per_sm": 8, "pdl": 1, "rm_resident": 0, **opts}):
         yield request.param
 
 
