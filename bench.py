@@ -229,7 +229,8 @@ class Workload:
         }
 
 
-def run_pipeline(torch, dist, ops, w, steps, warmup, world, exchange=None, marks=False, common_start=True):
+def run_pipeline(torch, dist, ops, w, steps, warmup, world, exchange=None, marks=False, common_start=True,
+                 prefetch=False):
     """`warmup` untimed and `steps` timed passes of reduce_mask -> gather -> scatter over workload `w`.
     Returns (ms of the timed region on this rank, blocks processed, per-op event times or None, wall-clock
     window).  The timed steps carry no per-op events (they cost host time between the launches); a
@@ -238,17 +239,33 @@ def run_pipeline(torch, dist, ops, w, steps, warmup, world, exchange=None, marks
     g_in, g_out = w.g_in, w.g_out
     yield_core = world > 1
 
-    def step(i, mk=None, ex=None):
+    main = torch.cuda.current_stream()
+    side = torch.cuda.Stream(priority=-1) if prefetch else None
+    ahead = {}   # step -> (idx, cnt, event): reduce_mask results computed one step ahead on the side stream
+
+    def mask_call(i, ex, mk=None):
         m = w.masks[i % len(w.masks)]
         slot = ex.slot(i) if ex is not None else None
         if mk is not None:
             mk[0].record()
-        # the mask has been resident since start-up and the kernel queued before this one is the previous
-        # step's scatter, which does not touch it: its loads may overlap that kernel's tail
+        # the mask has been resident since start-up and the kernel queued before this one does not touch
+        # it: its loads may overlap that kernel's tail
         idx, cnt, _ = ops.reduce_mask_with_device_count(m, *g_in.as_lists(), tol=0.5, avgpool=False, mask_stable=True,
                                                         yield_core=yield_core, scratch=slot)
         if mk is not None:
             mk[1].record()
+        return idx, cnt
+
+    def step(i, mk=None, ex=None):
+        if side is None:
+            idx, cnt = mask_call(i, ex, mk)
+        else:
+            if i not in ahead:          # the very first step has nothing computed ahead
+                with torch.cuda.stream(side):
+                    ahead[i] = mask_call(i, ex) + (side.record_event(),)
+            idx, cnt, ready = ahead.pop(i)
+            main.wait_event(ready)      # the gather reads the index list written on the side stream
+            idx.record_stream(main)
         nb = int(cnt[0])
         assert nb == w.nB, (nb, w.nB)
         if mk is not None:
@@ -256,6 +273,13 @@ def run_pipeline(torch, dist, ops, w, steps, warmup, world, exchange=None, marks
         ops.sparse_gather(w.x, cnt, idx, g_in.bsize, g_in.bstride, g_in.boffset, transpose=True, out=w.stack)
         if mk is not None:
             mk[3].record()
+        if side is not None:
+            # software pipelining over steps: the next step's reduce_mask (it depends on nothing of this
+            # step) runs on a second stream beside this step's gather, so its kernel and the host's wait
+            # for its count are off the critical path.  Every step issues exactly one reduce_mask, one
+            # gather and one scatter (the last step's reduce_mask serves a step that is never run)
+            with torch.cuda.stream(side):
+                ahead[i + 1] = mask_call(i + 1, ex) + (side.record_event(),)
         ops.sparse_scatter_var(w.q, cnt, idx, w.x, g_out.bsize, g_out.bstride, g_out.boffset, add=True, transpose=True)
         if mk is not None:
             mk[4].record()
@@ -346,7 +370,8 @@ def run_ours(args):
 
     clocks = ClockSampler(local).start()
     ex = exchange()
-    ms_total, blocks, _, (wall0, _) = run_pipeline(torch, dist, ops, main_w, args.steps, args.warmup, world, ex)
+    ms_total, blocks, _, (wall0, _) = run_pipeline(torch, dist, ops, main_w, args.steps, args.warmup, world, ex,
+                                                   prefetch=not args.in_order)
     global_counts = ex.finish() if ex is not None else None
     # a short timed region may fall between two clock samples: keep the same load running (untimed)
     # until at least half a second of it has been sampled; the per-op event times come from these passes
@@ -370,7 +395,8 @@ def run_ours(args):
         else:
             ow = Workload(torch, dev, args, lo, n_strong, args.occupancy, x_all, gen)
         oex = exchange()
-        oms, oblocks, _, _ = run_pipeline(torch, dist, ops, ow, args.steps, args.warmup, world, oex)
+        oms, oblocks, _, _ = run_pipeline(torch, dist, ops, ow, args.steps, args.warmup, world, oex,
+                                          prefetch=not args.in_order)
         oex.finish()
         other = (oms, oblocks, ow.N)
         del ow
@@ -946,6 +972,9 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-sync-free", action="store_true")
+    ap.add_argument("--in-order", action="store_true",
+                    help="issue every step's reduce_mask behind the previous step's scatter on one stream "
+                         "(default: one step ahead on a second stream)")
     ap.add_argument("--no-suite", action="store_true", help="skip the op-level table of configurations 2-4 and 5 at 30 percent")
     ap.add_argument("--no-weak", action="store_true", help="N > 1: skip the second pass in the other scaling mode")
     ap.add_argument("--cpu-budget", type=float, default=12.0)

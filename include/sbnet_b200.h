@@ -191,7 +191,7 @@ int sbnet_wait_timeouts(unsigned int* count);
  *   "rm_ctas_per_sm"  reduce_mask: CTAs per SM the column tiling aims at (default 8)             [SBNET_RM_CTAS_PER_SM]
  *   "rm_resident"     reduce_mask: at most this many CTAs resident per SM, 0 = no cap            [SBNET_RM_RESIDENT]
  *   "pdl"             0: launch kernels without programmatic stream serialization (default 1)    [SBNET_PDL]
- *   "tma_l2"          L2 promotion of image tensor maps: 0 none, 1 64 B, 2 128 B (default), 3 256 B [SBNET_TMA_L2]
+ *   "tma_l2"          L2 promotion of image tensor maps: 0 none, 1 64 B, 2 128 B, 3 256 B (default) [SBNET_TMA_L2]
  */
 int sbnet_set_option(const char* name, int value);
 int sbnet_get_option(const char* name, int* value);

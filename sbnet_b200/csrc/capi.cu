@@ -127,7 +127,7 @@ Options& options()
         opt.rmCtasPerSm = env_number("SBNET_RM_CTAS_PER_SM", 8);
         opt.rmResident = env_number("SBNET_RM_RESIDENT", 0);
         opt.pdl = env_number("SBNET_PDL", 1);
-        opt.tmaL2 = env_number("SBNET_TMA_L2", 2);
+        opt.tmaL2 = env_number("SBNET_TMA_L2", 3);
     });
     return opt;
 }

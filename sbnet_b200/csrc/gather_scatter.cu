@@ -168,12 +168,18 @@ template <int VB, typename T> __device__ __forceinline__ typename Vec<VB>::type 
     return v;
 }
 
+// Narrow vectors need more of them in flight: the general kernel keeps 64 bytes of image loads (and 16
+// stack elements) per thread outstanding whatever the vector width.
+template <int VB> struct PlaneUnroll { static constexpr int image = VB >= 16 ? 4 : (VB == 8 ? 8 : 16); };
+constexpr int kStackUnroll = 16;
+
 template <int VB, int MODE, typename T>
 __global__ void __launch_bounds__(kThreads, 4) planes_kernel(const BlockArgs a, const PlanePlan p)
 {
     pdl_wait();   // nothing is read or written before the kernel queued ahead of this one is done
     typedef typename Vec<VB>::type V;
     constexpr int EPV = VB / (int)sizeof(T);   // elements per vector
+    constexpr int kUI = PlaneUnroll<VB>::image;
     __shared__ __align__(16) unsigned char tileRaw[kTileBytes];
     T* tile = reinterpret_cast<T*>(tileRaw);
 
@@ -204,26 +210,30 @@ __global__ void __launch_bounds__(kThreads, 4) planes_kernel(const BlockArgs a, 
         const int nElem = nPix * nChan;
 
         if constexpr (MODE == kGather) {
-            // image -> tile: one vector of channels per thread-step, kUnroll loads in flight
-            for (int v0 = threadIdx.x; v0 < nVec; v0 += kThreads * kUnroll) {
-                V val[kUnroll];
-                uint32_t px[kUnroll], j[kUnroll];
+            // image -> tile: one vector of channels per thread-step, kUI loads in flight
+            for (int v0 = threadIdx.x; v0 < nVec; v0 += kThreads * kUI) {
+                V val[kUI];
 #pragma unroll
-                for (int u = 0; u < kUnroll; ++u) {
+                for (int u = 0; u < kUI; ++u) {
                     const int v = v0 + u * kThreads;
-                    vpp.divmod((uint32_t)min(v, nVec - 1), px[u], j[u]);
-                    uint32_t r, s;
-                    p.blockW.divmod((uint32_t)p0 + px[u], r, s);
+                    uint32_t px, j, r, s;
+                    vpp.divmod((uint32_t)min(v, nVec - 1), px, j);
+                    p.blockW.divmod((uint32_t)p0 + px, r, s);
                     const int h = h0 + (int)r, w = w0 + (int)s;
                     const bool inr = v < nVec && h >= 0 && h < a.H && w >= 0 && w < a.W;
                     val[u] = inr ? ld_stream(reinterpret_cast<const V*>(
-                                       imgN + ((long long)h * a.W + w) * a.C + j[u] * EPV))
+                                       imgN + ((long long)h * a.W + w) * a.C + j * EPV))
                                  : vzero<VB>();
                 }
 #pragma unroll
-                for (int u = 0; u < kUnroll; ++u)
-                    if (v0 + u * kThreads < nVec)
-                        tile_store<VB, T>(tile + px[u] * p.pitch + j[u] * EPV, val[u]);
+                for (int u = 0; u < kUI; ++u) {
+                    const int v = v0 + u * kThreads;
+                    if (v < nVec) {
+                        uint32_t px, j;
+                        vpp.divmod((uint32_t)v, px, j);   // recomputed: cheaper than keeping it across the loads
+                        tile_store<VB, T>(tile + px * p.pitch + j * EPV, val[u]);
+                    }
+                }
             }
             __syncthreads();
             // tile -> stack: consecutive threads write consecutive pixels of one channel plane
@@ -235,19 +245,24 @@ __global__ void __launch_bounds__(kThreads, 4) planes_kernel(const BlockArgs a, 
             __syncthreads();
         } else {
             // stack -> tile
-            for (int o0 = threadIdx.x; o0 < nElem; o0 += kThreads * 8) {
-                T val[8];
-                uint32_t c[8], px[8];
+            for (int o0 = threadIdx.x; o0 < nElem; o0 += kThreads * kStackUnroll) {
+                T val[kStackUnroll];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
+                for (int u = 0; u < kStackUnroll; ++u) {
                     const int o = o0 + u * kThreads;
-                    pixDiv.divmod((uint32_t)min(o, nElem - 1), c[u], px[u]);
-                    val[u] = planes[(long long)c[u] * RS + px[u]];
+                    uint32_t c, px;
+                    pixDiv.divmod((uint32_t)min(o, nElem - 1), c, px);
+                    val[u] = planes[(long long)c * RS + px];
                 }
 #pragma unroll
-                for (int u = 0; u < 8; ++u)
-                    if (o0 + u * kThreads < nElem)
-                        tile[px[u] * p.pitch + c[u]] = val[u];
+                for (int u = 0; u < kStackUnroll; ++u) {
+                    const int o = o0 + u * kThreads;
+                    if (o < nElem) {
+                        uint32_t c, px;
+                        pixDiv.divmod((uint32_t)o, c, px);
+                        tile[px * p.pitch + c] = val[u];
+                    }
+                }
             }
             __syncthreads();
             // tile -> image
@@ -341,8 +356,13 @@ static void launch_planes(const BlockArgs& a, cudaStream_t stream)
     const int itemsize = (int)sizeof(T);
     PlanePlan p;
     const int RS = a.bSzH * a.bSzW;
-    const int chunkElems = 128 / itemsize;
-    p.chanPerChunk = a.C < chunkElems ? a.C : chunkElems;
+    // channel chunks of at most 128 bytes, as even as the vector width allows (33 fp32 channels run as
+    // 17 + 16, not as 32 + 1: a chunk of one channel would move 4 bytes per pixel)
+    const int chunkElems = 128 / itemsize, epv = VB / itemsize;
+    const int wantChunks = (a.C + chunkElems - 1) / chunkElems;
+    p.chanPerChunk = (((a.C + wantChunks - 1) / wantChunks + epv - 1) / epv) * epv;
+    if (p.chanPerChunk > chunkElems)
+        p.chanPerChunk = chunkElems;
     // pitch: an odd number of 32-bit words (2-byte elements with a 2-byte vector: any odd count)
     if (itemsize == 4 || VB == 2) {
         p.pitch = p.chanPerChunk | 1;

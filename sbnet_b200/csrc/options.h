@@ -15,7 +15,7 @@ struct Options {
     int rmCtasPerSm;   // reduce_mask tile kernel: CTAs per SM the column tiling aims at (SBNET_RM_CTAS_PER_SM)
     int rmResident;    // reduce_mask tile kernel: at most this many CTAs resident per SM, 0 = no cap (SBNET_RM_RESIDENT)
     int pdl;           // launch every kernel with programmatic stream serialization (SBNET_PDL, default 1)
-    int tmaL2;         // L2 promotion of the image tensor maps: 0 none, 1 64 B, 2 128 B, 3 256 B (SBNET_TMA_L2, default 2)
+    int tmaL2;         // L2 promotion of the image tensor maps: 0 none, 1 64 B, 2 128 B, 3 256 B (SBNET_TMA_L2, default 3)
 };
 
 Options& options();
