@@ -143,6 +143,24 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
         : "memory");
 }
 
+// ---- in-place transposition of a swizzled tile -----------------------------------------------------
+// Task t of a tile's transposition -> (16-byte channel group j, word column u); 128 tasks cover 16
+// word columns x 8 groups.  A quarter warp's eight 16-byte reads of the [pixel][128 B] tile (groups
+// XOR-swizzled by pixel & 7) are conflict-free when they hit eight different groups.  32-bit elements:
+// word column u is pixel u, so eight neighbouring columns of one group do.  16-bit elements: word
+// column u is the pixel pair (2u, 2u+1), whose swizzle phases are all even (or all odd) -- four
+// values only -- so every eight lanes pair two channel groups with four columns instead.
+template <int EPW> __device__ __forceinline__ void transpose_task(int t, int& j, int& u)
+{
+    if constexpr (EPW == 2) {
+        j = (t & 1) | (((t >> 5) & 3) << 1);
+        u = ((t >> 7) << 4) + ((t >> 1) & 15);
+    } else {
+        j = (t >> 4) & 7;
+        u = ((t >> 7) << 4) + (t & 15);
+    }
+}
+
 // ---- programmatic dependent launch ----------------------------------------------------------------
 // wait: blocks until the kernel this one was launched behind (with the programmatic-serialization
 // attribute) has completed and its writes are visible; a no-op for an ordinary launch.

@@ -153,8 +153,8 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
 #pragma unroll
     for (int q = 0; q < kMaxTasks; ++q) {
         const int t = threadIdx.x + q * kPsThreads;
-        const int uLocal = t & 15, grp = t >> 4;
-        const int j = grp & 7, u = ((grp >> 3) << 4) + uLocal;
+        int j, u;
+        transpose_task<EPW>(t, j, u);
         if (t < nTasks && u < U && j < nG) {
             if constexpr (ODD) {   // word u = word uIn of block b: pixels 2*uIn and (if it exists) 2*uIn+1
                 uint32_t b = 0, uIn = (uint32_t)u;
@@ -178,8 +178,8 @@ __global__ void __launch_bounds__(kPsThreads, sizeof(T) == 2 ? 4 : 3) planes_gat
 #pragma unroll
     for (int q = 0; q < kMaxTasks; ++q) {
         const int t = threadIdx.x + q * kPsThreads;
-        const int uLocal = t & 15, grp = t >> 4;
-        const int j = grp & 7, u = ((grp >> 3) << 4) + uLocal;
+        int j, u;
+        transpose_task<EPW>(t, j, u);
         if (t < nTasks && u < U && j < nG) {
             uint32_t base = tile + ((uint32_t)(CPG * j) * U + u) * 4u;
             uint32_t pitch = (uint32_t)U * 4u;

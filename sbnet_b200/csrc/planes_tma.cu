@@ -189,8 +189,8 @@ planes_gather_tma(const __grid_constant__ CUtensorMap imageMap, const BlockArgs 
         const uint32_t in = ring.in0 + (uint32_t)s * p.inStageBytes;
         const uint32_t out = ring.out0 + (uint32_t)o * p.outStageBytes;
         for (int t = threadIdx.x; t < nTasks; t += kConsumers) {
-            const int uLocal = t & 15, grp = t >> 4;
-            const int j = grp & 7, u = ((grp >> 3) << 4) + uLocal;
+            int j, u;
+            transpose_task<EPW>(t, j, u);
             if (u >= U)
                 continue;
             if constexpr (EPW == 2) {
@@ -455,8 +455,8 @@ planes_gather_tma_tile(const __grid_constant__ CUtensorMap imageMap, const Block
 #pragma unroll
     for (int q = 0; q < kMaxTasks; ++q) {
         const int t = threadIdx.x + q * kTileThreads;
-        const int uLocal = t & 15, g16 = t >> 4;
-        const int j = g16 & 7, u = ((g16 >> 3) << 4) + uLocal;
+        int j, u;
+        transpose_task<EPW>(t, j, u);
         if (t < nTasks && u < U && j < nG) {
             uint32_t b, uIn;
             p.unitsDiv.divmod((uint32_t)u, b, uIn);
@@ -474,8 +474,8 @@ planes_gather_tma_tile(const __grid_constant__ CUtensorMap imageMap, const Block
 #pragma unroll
     for (int q = 0; q < kMaxTasks; ++q) {
         const int t = threadIdx.x + q * kTileThreads;
-        const int uLocal = t & 15, g16 = t >> 4;
-        const int j = g16 & 7, u = ((g16 >> 3) << 4) + uLocal;
+        int j, u;
+        transpose_task<EPW>(t, j, u);
         if (t < nTasks && u < U && j < nG) {
             uint32_t b, uIn;
             p.unitsDiv.divmod((uint32_t)u, b, uIn);
@@ -594,8 +594,8 @@ planes_gather_tma_rows(const __grid_constant__ CUtensorMap mapFull, const __grid
 #pragma unroll
     for (int q = 0; q < kMaxTasks; ++q) {
         const int t = threadIdx.x + q * kTileThreads;
-        const int uLocal = t & 15, g16 = t >> 4;
-        const int j = g16 & 7, u = ((g16 >> 3) << 4) + uLocal;
+        int j, u;
+        transpose_task<EPW>(t, j, u);
         if (t < nTasks && u < U && j < nG) {
             const uint32_t r0 = EPW * u;
             A[q] = lds128(tile + r0 * 128u + ((j ^ (r0 & 7u)) << 4));
@@ -610,8 +610,8 @@ planes_gather_tma_rows(const __grid_constant__ CUtensorMap mapFull, const __grid
 #pragma unroll
     for (int q = 0; q < kMaxTasks; ++q) {
         const int t = threadIdx.x + q * kTileThreads;
-        const int uLocal = t & 15, g16 = t >> 4;
-        const int j = g16 & 7, u = ((g16 >> 3) << 4) + uLocal;
+        int j, u;
+        transpose_task<EPW>(t, j, u);
         if (t < nTasks && u < U && j < nG) {
             const uint32_t base = tile + ((uint32_t)(CPG * j) * U + u) * 4u;
             const uint32_t pitch = (uint32_t)U * 4u;
