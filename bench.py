@@ -203,6 +203,37 @@ def bind_cores(local, per_node):
         return None
 
 
+class FastEvents:
+    """cudaEventRecord / cudaStreamWaitEvent on torch's events and streams through ctypes: torch's own
+    methods cost 4-7 us of interpreter time per call, which is a tenth of a rank's step when eight GPUs
+    share one batch.  Falls back to the torch methods where the runtime library cannot be opened."""
+
+    def __init__(self, torch):
+        import ctypes
+        self.rt = None
+        for name in ("libcudart.so.12", "libcudart.so"):
+            try:
+                rt = ctypes.CDLL(name)
+                rt.cudaEventRecord.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+                rt.cudaStreamWaitEvent.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint]
+                self.rt = rt
+                break
+            except OSError:
+                continue
+
+    def record(self, event, stream):
+        if self.rt is None or not event.cuda_event:     # a torch event gets its handle at its first record
+            event.record(stream)
+        elif self.rt.cudaEventRecord(event.cuda_event, stream.cuda_stream) != 0:
+            raise RuntimeError("cudaEventRecord failed")
+
+    def wait(self, stream, event):
+        if self.rt is None:
+            stream.wait_event(event)
+        elif self.rt.cudaStreamWaitEvent(stream.cuda_stream, event.cuda_event, 0) != 0:
+            raise RuntimeError("cudaStreamWaitEvent failed")
+
+
 class Workload:
     """Device-resident inputs of one rank for `n_images` images at one mask occupancy."""
 
@@ -242,45 +273,64 @@ def run_pipeline(torch, dist, ops, w, steps, warmup, world, exchange=None, marks
     main = torch.cuda.current_stream()
     side = torch.cuda.Stream(priority=-1) if prefetch else None
     ahead = {}   # step -> (idx, cnt, event): reduce_mask results computed one step ahead on the side stream
+    # the same buffers and geometry every step: arguments are validated once (ops.bind_*), which takes
+    # about 7 us of interpreter time off each call -- it matters when a rank's step is only tens of us
+    # The mask has been resident since start-up and the kernel queued before a reduce_mask never writes
+    # it, so its loads may overlap that kernel's tail (mask_stable).
+    mask_fn = ops.bind_reduce_mask(w.masks[0], *g_in.as_lists(), tol=0.5, avgpool=False, mask_stable=True,
+                                   yield_core=yield_core, stream=side.cuda_stream if side is not None else None)
+    gather_fn = ops.bind_sparse_gather(w.x, w.stack, g_in.bsize, g_in.bstride, g_in.boffset, transpose=True)
+    scatter_fn = ops.bind_sparse_scatter_var(w.q, w.x, g_out.bsize, g_out.bstride, g_out.boffset, add=True, transpose=True)
+    fast = FastEvents(torch)
+    ready_ev = [torch.cuda.Event() for _ in range(4)]     # index list of step i written (side stream)
+    gathered_ev = [torch.cuda.Event() for _ in range(4)]  # gather of step i finished (main stream)
+    held = []   # index lists stay referenced until the final synchronisation (they were allocated under
+                # the main stream and written on the side stream, so their memory must not be recycled early)
 
     def mask_call(i, ex, mk=None):
-        m = w.masks[i % len(w.masks)]
         slot = ex.slot(i) if ex is not None else None
         if mk is not None:
             mk[0].record()
-        # the mask has been resident since start-up and the kernel queued before this one does not touch
-        # it: its loads may overlap that kernel's tail
-        idx, cnt, _ = ops.reduce_mask_with_device_count(m, *g_in.as_lists(), tol=0.5, avgpool=False, mask_stable=True,
-                                                        yield_core=yield_core, scratch=slot)
+        idx, cnt, _ = mask_fn(w.masks[i % len(w.masks)], slot)
         if mk is not None:
             mk[1].record()
         return idx, cnt
+
+    def mask_ahead(i, ex):
+        idx, cnt = mask_call(i, ex)      # launched on the side stream by handle; returns once the count is on the host
+        ev = ready_ev[i % len(ready_ev)]
+        fast.record(ev, side)
+        held.append(idx)
+        return idx, cnt, ev
 
     def step(i, mk=None, ex=None):
         if side is None:
             idx, cnt = mask_call(i, ex, mk)
         else:
             if i not in ahead:          # the very first step has nothing computed ahead
-                with torch.cuda.stream(side):
-                    ahead[i] = mask_call(i, ex) + (side.record_event(),)
+                ahead[i] = mask_ahead(i, ex)
             idx, cnt, ready = ahead.pop(i)
-            main.wait_event(ready)      # the gather reads the index list written on the side stream
-            idx.record_stream(main)
+            fast.wait(main, ready)      # the gather reads the index list written on the side stream
         nb = int(cnt[0])
         assert nb == w.nB, (nb, w.nB)
         if mk is not None:
             mk[2].record()
-        ops.sparse_gather(w.x, cnt, idx, g_in.bsize, g_in.bstride, g_in.boffset, transpose=True, out=w.stack)
+        gather_fn(cnt, idx)
         if mk is not None:
             mk[3].record()
         if side is not None:
             # software pipelining over steps: the next step's reduce_mask (it depends on nothing of this
-            # step) runs on a second stream beside this step's gather, so its kernel and the host's wait
-            # for its count are off the critical path.  Every step issues exactly one reduce_mask, one
-            # gather and one scatter (the last step's reduce_mask serves a step that is never run)
-            with torch.cuda.stream(side):
-                ahead[i + 1] = mask_call(i + 1, ex) + (side.record_event(),)
-        ops.sparse_scatter_var(w.q, cnt, idx, w.x, g_out.bsize, g_out.bstride, g_out.boffset, add=True, transpose=True)
+            # step) runs on a second stream beside this step's SCATTER -- it is queued behind this step's
+            # gather, which also keeps the host exactly one step ahead of the device -- so its kernel and the
+            # host's wait for its count are off the critical path.  Every step issues exactly one
+            # reduce_mask, one gather and one scatter (the last step's reduce_mask serves a step never run)
+            ge = gathered_ev[i % len(gathered_ev)]
+            fast.record(ge, main)
+            scatter_fn(cnt, idx)
+            fast.wait(side, ge)
+            ahead[i + 1] = mask_ahead(i + 1, ex)
+        else:
+            scatter_fn(cnt, idx)
         if mk is not None:
             mk[4].record()
         if ex is not None:

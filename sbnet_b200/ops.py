@@ -366,6 +366,103 @@ def sparse_scatter_var_dyn(x, count_dev: torch.Tensor, max_blocks: int, active_b
     return ybase
 
 
+# ---- pre-validated calls for hot loops ---------------------------------------------------------------
+# The wrappers above re-check every argument on every call (about 7 us of interpreter time each, beside
+# the ~5 us of the foreign call itself).  A loop that calls the same op on the same buffers with the
+# same geometry -- every layer of a network at inference time -- can bind those once: the returned
+# function takes only what changes from call to call.  Same library entry points, same results.
+
+def bind_reduce_mask(mask_like: torch.Tensor, dynamic_bcount, dynamic_bsize, dynamic_bstride, dynamic_boffset, tol,
+                     avgpool=False, mask_stable=False, yield_core=False, stream: int = None):
+    """Returns ``call(mask, scratch=None) -> (active_block_indices, bin_counts, count_dev)`` for masks of
+    ``mask_like``'s shape, dtype and device.  ``stream``: raw handle of the stream to launch on (default:
+    torch's current stream at call time).  Every call allocates its index list and takes a fresh pinned
+    count and (unless ``scratch`` is given) a fresh scratch slot, as :func:`reduce_mask` does."""
+    _require_cuda(mask_like, "mask")
+    N, H, W = _check_mask(mask_like)
+    bch, bcw = _pair(dynamic_bcount, "dynamic_bcount")
+    g = _geom(dynamic_bsize, dynamic_bstride, dynamic_boffset)
+    device, shape = mask_like.device, tuple(mask_like.shape)
+    rows = max(N * bch * bcw, 0)
+    flags = _lib.SBNET_COUNT_POLL | _lib.SBNET_SCRATCH_CLEAN | (_lib.SBNET_MASK_STABLE if mask_stable else 0) \
+        | (_lib.SBNET_COUNT_YIELD if yield_core else 0)
+    fn = _lib.load().sbnet_reduce_mask
+    head = (N, H, W, float(tol), int(bool(avgpool)), *g, bch, bcw)
+    n_scratch = _lib.SBNET_REDUCE_MASK_SCRATCH_INTS
+
+    def call(mask, scratch=None):
+        if tuple(mask.shape) != shape or mask.dtype != torch.float32 or mask.device != device or not mask.is_contiguous():
+            raise ValueError("mask differs from the one this call was bound for")
+        st = stream if stream is not None else _stream(device)
+        idx = torch.empty((rows, 3), dtype=torch.int16, device=device)
+        counts = _pinned_count()
+        if scratch is None:
+            scratch = scratch_for(device, st)[0]
+        elif scratch.dtype != torch.int32 or scratch.numel() < n_scratch or scratch.device != device:
+            raise ValueError("scratch must be an int32 device tensor of at least 4 elements")
+        _lib.check(fn(mask.data_ptr(), *head, idx.data_ptr(), scratch.data_ptr(), counts.data_ptr(), flags, st))
+        return idx, counts, scratch[:1]
+    return call
+
+
+def bind_sparse_gather(x: torch.Tensor, out: torch.Tensor, dynamic_bsize, dynamic_bstride, dynamic_boffset,
+                       transpose=False, stream: int = None):
+    """Returns ``call(bin_counts, active_block_indices) -> out`` gathering from ``x`` into ``out`` (room for
+    the largest count that will be passed; checked per call)."""
+    _require_cuda(x, "x")
+    _require_cuda(out, "out")
+    N, H, W, Cc = _check_image(x, "x")
+    g = _geom(dynamic_bsize, dynamic_bstride, dynamic_boffset)
+    block = g[2] * g[3] * Cc
+    _check_stack(out, "out", 0, block, x)
+    cap = out.numel() // block
+    device = x.device
+    fn = _lib.load().sbnet_sparse_gather
+    head = (x.data_ptr(), _DTYPES[x.dtype], N, H, W, Cc, out.data_ptr(), *g)
+    tr = int(bool(transpose))
+    keep = (x, out)   # the bound buffers stay alive as long as the call does
+
+    def call(bin_counts, active_block_indices):
+        nb = _count(bin_counts)
+        if nb > cap:
+            raise ValueError(f"out holds {cap} blocks, the call needs {nb}")
+        a = active_block_indices
+        if a.dtype != torch.int16 or a.device != device or a.shape[0] < nb or not a.is_contiguous():
+            raise ValueError("active_block_indices must be a contiguous int16 [>= count, 3] tensor on the image's device")
+        _lib.check(fn(*head, nb, a.data_ptr(), tr, stream if stream is not None else _stream(device)))
+        return keep[1]
+    return call
+
+
+def bind_sparse_scatter_var(x: torch.Tensor, ybase: torch.Tensor, dynamic_bsize, dynamic_bstride, dynamic_boffset,
+                            add: bool, atomic=False, transpose=False, stream: int = None):
+    """Returns ``call(bin_counts, active_block_indices) -> ybase`` scattering the first ``bin_counts[0]``
+    blocks of the stack ``x`` into ``ybase`` in place."""
+    _require_cuda(x, "x")
+    _require_cuda(ybase, "ybase")
+    N, H, W, Cc = _check_image(ybase, "ybase")
+    g = _geom(dynamic_bsize, dynamic_bstride, dynamic_boffset)
+    block = g[2] * g[3] * Cc
+    _check_stack(x, "x", 0, block, ybase)
+    cap = x.numel() // block
+    device = ybase.device
+    fn = _lib.load().sbnet_sparse_scatter
+    head = (x.data_ptr(), _DTYPES[ybase.dtype], N, H, W, Cc, ybase.data_ptr(), *g)
+    tail = (int(bool(add)), int(bool(transpose)), int(bool(atomic)))
+    keep = (x, ybase)
+
+    def call(bin_counts, active_block_indices):
+        nb = _count(bin_counts)
+        if nb > cap:
+            raise ValueError(f"x holds {cap} blocks, the call needs {nb}")
+        a = active_block_indices
+        if a.dtype != torch.int16 or a.device != device or a.shape[0] < nb or not a.is_contiguous():
+            raise ValueError("active_block_indices must be a contiguous int16 [>= count, 3] tensor on the image's device")
+        _lib.check(fn(*head, nb, a.data_ptr(), *tail, stream if stream is not None else _stream(device)))
+        return keep[1]
+    return call
+
+
 def cuda_timer_start() -> int:
     """``CudaTimerStart``: returns an event handle (``sbnet_ops/sparse_gather.cc:398-423``)."""
     h = C.c_int64(0)

@@ -211,3 +211,49 @@ def test_device_count_pipeline_replays_from_a_cuda_graph(cuda_ops, oracle_port):
                                              go.bsize, go.bstride, go.boffset, add=True, transpose=True)
         np.testing.assert_array_equal(y.cpu().numpy(), exp)
     assert counts[0] != counts[1]
+
+
+def test_bound_calls_match_the_ordinary_wrappers(cuda_ops):
+    """bind_reduce_mask / bind_sparse_gather / bind_sparse_scatter_var (arguments validated once) give the
+    results of the per-call wrappers, also on a stream passed by handle, and still reject what changes
+    shape under them."""
+    import torch
+    from sbnet_b200 import ops
+    dev = "cuda"
+    N, H, W, C = 2, 64, 48, 64
+    g, gi = cfg.halo_geom(H, W), cfg.inner_geom(H, W)
+    masks = [torch.from_numpy(cfg.rect_union_mask(N, H, W, seed=s, occupancy=0.3, side=(4, 16))).to(dev) for s in (1, 2)]
+    x = torch.randn((N, H, W, C), device=dev).half()
+    cap = N * g.bcount[0] * g.bcount[1]
+    stack = torch.empty((cap, C, 18, 18), dtype=torch.float16, device=dev)
+    q = (torch.randn((cap, C, 16, 16), device=dev) * 0.1).half()
+    side = torch.cuda.Stream()
+    for stream in (None, side.cuda_stream):
+        rm = ops.bind_reduce_mask(masks[0], *g.as_lists(), tol=0.5, mask_stable=True, stream=stream)
+        ga = ops.bind_sparse_gather(x, stack, g.bsize, g.bstride, g.boffset, transpose=True, stream=stream)
+        y = x.clone()
+        sc = ops.bind_sparse_scatter_var(q, y, gi.bsize, gi.bstride, gi.boffset, add=True, transpose=True, stream=stream)
+        torch.cuda.synchronize()
+        ref = x.clone()
+        for m in masks:
+            idx, cnt, cnt_dev = rm(m)
+            ridx, rcnt = ops.reduce_mask(m, *g.as_lists(), tol=0.5)
+            n = int(cnt[0])
+            assert n == int(rcnt[0])
+            ga(cnt, idx)
+            sc(cnt, idx)
+            torch.cuda.synchronize()
+            assert int(cnt_dev[0]) == n
+            assert sorted(map(tuple, idx[:n].tolist())) == sorted(map(tuple, ridx[:n].tolist()))
+            assert torch.equal(stack[:n], ops.sparse_gather(x, cnt, idx, g.bsize, g.bstride, g.boffset, transpose=True))
+            # the same stack rows onto the same block list through the ordinary wrapper
+            ops.sparse_scatter_var(q[:n].contiguous(), cnt, idx, ref, gi.bsize, gi.bstride, gi.boffset, add=True,
+                                   transpose=True)
+        torch.cuda.synchronize()
+        assert torch.equal(y, ref)
+    with pytest.raises(ValueError):
+        rm(masks[0][:1])
+    with pytest.raises(ValueError):
+        ga([cap + 1], idx)
+    with pytest.raises(ValueError):
+        sc([1], idx.to(torch.int32))
