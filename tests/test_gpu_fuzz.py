@@ -102,7 +102,7 @@ def test_random_tile_shapes(cuda_ops, oracle_port, seed):
     disjoint = bstride[0] >= bsize[0] and bstride[1] >= bsize[1]
     cover = -(-bsize[0] // bstride[0]) * -(-bsize[1] // bstride[1])
     from conftest import library_options
-    with library_options(tile_blocks=int(pack)):
+    with library_options(tile_blocks=int(pack), planes=3 if seed % 2 else 0):   # odd seeds: tile CTAs whatever the launch size
         exp = oracle_port.sparse_gather(x, cnt, idx, bsize, bstride, boffset, transpose=True)
         got = cuda_ops.sparse_gather(x, cnt, idx, bsize, bstride, boffset, transpose=True)
         np.testing.assert_array_equal(got.view(bits), exp.view(bits))

@@ -59,13 +59,14 @@ def _ids():
     return [f"{np.dtype(s[0]).name}_C{s[4]}_b{s[5][0]}x{s[5][1]}_s{s[6][0]}x{s[6][1]}" for s in SHAPES]
 
 
-@pytest.fixture(params=["default", "tile_ctas", "tma_pipeline", "general"])
+@pytest.fixture(params=["default", "tma_tile", "tile_ctas", "tma_pipeline", "general"])
 def tma_off(request):
-    """Selects which plane-layout implementation takes the call: the default dispatch (tile CTAs,
-    gathers fed by TMA), the tile CTAs with plain loads, the persistent TMA pipeline, or the general
-    kernel."""
+    """Selects which plane-layout implementation takes the call: the default dispatch (which sends
+    launches as small as these tests' gathers to the TMA pipeline where the shape allows), the tile CTAs
+    fed by TMA whatever the launch size, the tile CTAs with plain loads, the persistent TMA pipeline, or the
+    general kernel."""
     from conftest import library_options
-    planes = {"default": 0, "general": 0, "tma_pipeline": 1, "tile_ctas": 2}[request.param]
+    planes = {"default": 0, "general": 0, "tma_pipeline": 1, "tile_ctas": 2, "tma_tile": 3}[request.param]
     with library_options(planes=planes, disable_tma=int(request.param == "general"), tile_blocks=0):
         yield request.param
 
@@ -172,7 +173,7 @@ def test_several_blocks_per_tile(cuda_ops, oracle_port, shape, blocks_per_tile, 
     """``plain``: the plain-load kernels of the tile CTAs; ``tma``: the default dispatch, whose gather
     feeds the shared tile with one TMA load per block where it can."""
     from conftest import library_options
-    with library_options(tile_blocks=int(blocks_per_tile), planes=2 if gather_loads == "plain" else 0, disable_tma=0):
+    with library_options(tile_blocks=int(blocks_per_tile), planes=2 if gather_loads == "plain" else 3, disable_tma=0):
         _run_shape(cuda_ops, oracle_port, shape)
 
 
