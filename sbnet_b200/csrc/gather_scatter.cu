@@ -356,9 +356,10 @@ static void launch_planes(const BlockArgs& a, cudaStream_t stream)
     const int itemsize = (int)sizeof(T);
     PlanePlan p;
     const int RS = a.bSzH * a.bSzW;
-    // channel chunks of at most 128 bytes, as even as the vector width allows (33 fp32 channels run as
-    // 17 + 16, not as 32 + 1: a chunk of one channel would move 4 bytes per pixel)
-    const int chunkElems = 128 / itemsize, epv = VB / itemsize;
+    // channel chunks of at most 256 bytes (a pixel of up to 256 bytes is moved whole, so image rows stay
+    // contiguous runs), as even as the vector width allows: 100 fp16 channels run as one chunk, 160 as
+    // 80 + 80, never as 128 + 32
+    const int chunkElems = 256 / itemsize, epv = VB / itemsize;
     const int wantChunks = (a.C + chunkElems - 1) / chunkElems;
     p.chanPerChunk = (((a.C + wantChunks - 1) / wantChunks + epv - 1) / epv) * epv;
     if (p.chanPerChunk > chunkElems)
