@@ -282,8 +282,7 @@ def run_pipeline(torch, dist, ops, w, steps, warmup, world, exchange=None, marks
     gather_fn = ops.bind_sparse_gather(w.x, w.stack, g_in.bsize, g_in.bstride, g_in.boffset, transpose=True)
     scatter_fn = ops.bind_sparse_scatter_var(w.q, w.x, g_out.bsize, g_out.bstride, g_out.boffset, add=True, transpose=True)
     fast = FastEvents(torch)
-    ready_ev = [torch.cuda.Event() for _ in range(4)]     # index list of step i written (side stream)
-    gathered_ev = [torch.cuda.Event() for _ in range(4)]  # gather of step i finished (main stream)
+    ready_ev = [torch.cuda.Event() for _ in range(8)]     # index list of step i written (side stream)
     held = []   # index lists stay referenced until the final synchronisation (they were allocated under
                 # the main stream and written on the side stream, so their memory must not be recycled early)
 
@@ -320,17 +319,12 @@ def run_pipeline(torch, dist, ops, w, steps, warmup, world, exchange=None, marks
             mk[3].record()
         if side is not None:
             # software pipelining over steps: the next step's reduce_mask (it depends on nothing of this
-            # step) runs on a second stream beside this step's SCATTER -- it is queued behind this step's
-            # gather, which also keeps the host exactly one step ahead of the device -- so its kernel and the
-            # host's wait for its count are off the critical path.  Every step issues exactly one
-            # reduce_mask, one gather and one scatter (the last step's reduce_mask serves a step never run)
-            ge = gathered_ev[i % len(gathered_ev)]
-            fast.record(ge, main)
-            scatter_fn(cnt, idx)
-            fast.wait(side, ge)
+            # step) is issued on a second stream, so its kernel and the host's wait for its count are off
+            # the critical path; the host runs ahead of the device by as many steps as that lets it.  Every
+            # step issues exactly one reduce_mask, one gather and one scatter (the last step's reduce_mask
+            # serves a step that is never run)
             ahead[i + 1] = mask_ahead(i + 1, ex)
-        else:
-            scatter_fn(cnt, idx)
+        scatter_fn(cnt, idx)
         if mk is not None:
             mk[4].record()
         if ex is not None:

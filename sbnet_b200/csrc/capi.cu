@@ -21,6 +21,7 @@
 namespace {
 
 thread_local char g_err[320] = "";
+thread_local const char* g_site = "";
 constexpr int32_t kCountSentinel = INT32_MIN;
 
 int reject(int code, const char* fmt, ...)
@@ -35,7 +36,8 @@ int reject(int code, const char* fmt, ...)
 inline int cuda_status(cudaError_t e)
 {
     if (e != cudaSuccess)
-        snprintf(g_err, sizeof(g_err), "CUDA error %d: %s", (int)e, cudaGetErrorString(e));
+        snprintf(g_err, sizeof(g_err), "CUDA error %d: %s%s%s", (int)e, cudaGetErrorString(e), g_site[0] ? " at " : "",
+                 g_site);
     return (int)e;
 }
 
@@ -63,6 +65,7 @@ int blocks_call(const char* op, int mode, int dtype, int N, int H, int W, int C,
                 int bStrW, int numActive, const int32_t* numActiveDev, const int16_t* idx,
                 int transpose, void* stream)
 {
+    g_site = "";
     if (dtype != SBNET_F32 && dtype != SBNET_F16 && dtype != SBNET_BF16)
         return reject(SBNET_ERR_INVALID_ARGUMENT, "%s: unknown dtype %d", op, dtype);
     if (N < 1 || H < 1 || W < 1 || C < 1)
@@ -107,6 +110,7 @@ int scatter_mode(const char* op, int add, int atomic, int bSzH, int bSzW, int bS
 namespace sbnet {
 // Lets other translation units of the library report through sbnet_last_error().
 void set_last_error(const char* text) { snprintf(g_err, sizeof(g_err), "%s", text); }
+void note_site(const char* site) { g_site = site; }
 
 static int env_number(const char* name, int dflt)
 {

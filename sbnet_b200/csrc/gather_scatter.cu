@@ -465,6 +465,7 @@ cudaError_t launch_blocks(const BlockArgs& a, int dtype, int mode, bool transpos
             return cudaSuccess;
     }
     const int vb = pick_vector_bytes(a, itemsize);
+    note_site(transpose ? "launch of planes_kernel" : "launch of rows_kernel");
     if (dtype == 0)
         dispatch_mode<float>(a, mode, transpose, vb, stream);
     else if (dtype == 2)

@@ -39,4 +39,8 @@ int sm_count();
 // Sets the calling thread's sbnet_last_error() text.
 void set_last_error(const char* text);
 
+// Names the runtime call a launcher is about to make; a CUDA error reported by the C ABI carries the
+// last name noted on the calling thread.
+void note_site(const char* site);
+
 } // namespace sbnet

@@ -709,6 +709,7 @@ cudaError_t launch_planes_simt(const BlockArgs& a, int dtype, int mode, cudaStre
                                    : (long long)a.numActive * p.cChunks.div * p.pChunks.div;
     if (nItems > 0x7fffffffll)
         return cudaSuccess;
+    note_site("launch of a planes_simt kernel");
     unsigned grid = (unsigned)nItems;
     if (a.num_active_dev != nullptr) {   // count on the device: one resident wave strides over the items
         const long long wave = (long long)sm_count() * 3;

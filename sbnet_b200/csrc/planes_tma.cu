@@ -782,11 +782,13 @@ static cudaError_t set_smem(const void* fn, int bytes)
     thread_local Done done[kEntries];
     thread_local int used = 0, next = 0;
     int device = 0;
+    note_site("cudaGetDevice (shared-memory limit)");
     if (cudaError_t e = cudaGetDevice(&device))
         return e;
     for (int i = 0; i < used; ++i)
         if (done[i].fn == fn && done[i].device == device && done[i].bytes >= bytes)
             return cudaSuccess;
+    note_site("cudaFuncSetAttribute (shared-memory limit)");
     if (cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))
         return e;
     done[next] = Done{fn, device, bytes};
@@ -819,6 +821,7 @@ cudaError_t launch_planes_tma(const BlockArgs& a, int dtype, int mode, cudaStrea
         CUtensorMap map;
         if (!image_map(a, itemsize, a.bSzW, a.bSzH, &map))
             return cudaSuccess;   // no encoder, or a shape it rejects: the general kernel takes the call
+        note_site("launch of planes_gather_tma");
         p.outStages = 2;
         p.inStageBytes = (p.tileBytes + 1023) & ~1023;
         p.outStageBytes = (p.tileBytes + 127) & ~127;
@@ -837,6 +840,7 @@ cudaError_t launch_planes_tma(const BlockArgs& a, int dtype, int mode, cudaStrea
         return cudaGetLastError();
     }
 
+    note_site("launch of planes_scatter_tma");
     p.inStages = 4, p.outStages = 0;
     p.inStageBytes = (p.tileBytes + 127) & ~127;
     p.outStageBytes = 0;
@@ -897,6 +901,7 @@ cudaError_t launch_gather_tma_tile(const BlockArgs& a, int dtype, int blocksPerI
     if (nItems > 0x7fffffffll)
         return cudaSuccess;
     const int smem = kTileBytesMax + 1024;
+    note_site("launch of planes_gather_tma_tile");
     if (dtype == 0) {
         if (cudaError_t e = set_smem((const void*)planes_gather_tma_tile<float>, smem))
             return e;
@@ -941,6 +946,7 @@ cudaError_t launch_gather_tma_rows(const BlockArgs& a, int dtype, cudaStream_t s
     if (nItems > 0x7fffffffll)
         return cudaSuccess;
     const int smem = kTileBytesMax + 1024;
+    note_site("launch of planes_gather_tma_rows");
     if (dtype == 0) {
         if (cudaError_t e = set_smem((const void*)planes_gather_tma_rows<float>, smem))
             return e;
