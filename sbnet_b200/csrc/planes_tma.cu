@@ -34,6 +34,7 @@
 #include <stdlib.h>
 
 #include <algorithm>
+#include <mutex>
 
 #include "async_ptx.cuh"
 #include "common.cuh"
@@ -770,31 +771,40 @@ bool planes_tma_eligible(const BlockArgs& a, int itemsize)
     return true;
 }
 
-// Raises a kernel's dynamic shared memory limit; remembers the last few (kernel, device, size)
-// triples per thread so that repeated launches skip the runtime call.
+// Raises a kernel's dynamic shared memory limit.  The limit is a property of the function (of the
+// context), shared by every host thread, so what has been set is remembered process-wide -- frameworks
+// call from several threads (an autograd engine runs backward passes on its own) -- and it is only ever
+// raised: a smaller request after a larger one leaves the larger limit in place.
 static cudaError_t set_smem(const void* fn, int bytes)
 {
     struct Done {
         const void* fn;
         int device, bytes;
     };
-    constexpr int kEntries = 16;
-    thread_local Done done[kEntries];
-    thread_local int used = 0, next = 0;
+    constexpr int kEntries = 64;
+    static Done done[kEntries];
+    static int used = 0;
+    static std::mutex lock;
     int device = 0;
     note_site("cudaGetDevice (shared-memory limit)");
     if (cudaError_t e = cudaGetDevice(&device))
         return e;
+    std::lock_guard<std::mutex> guard(lock);
+    int slot = -1;
     for (int i = 0; i < used; ++i)
-        if (done[i].fn == fn && done[i].device == device && done[i].bytes >= bytes)
-            return cudaSuccess;
+        if (done[i].fn == fn && done[i].device == device) {
+            if (done[i].bytes >= bytes)
+                return cudaSuccess;
+            slot = i;
+            break;
+        }
     note_site("cudaFuncSetAttribute (shared-memory limit)");
     if (cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))
         return e;
-    done[next] = Done{fn, device, bytes};
-    next = (next + 1) % kEntries;
-    if (used < kEntries)
-        ++used;
+    if (slot < 0 && used < kEntries)
+        slot = used++;
+    if (slot >= 0)   // a full table only costs the repeated runtime call
+        done[slot] = Done{fn, device, bytes};
     return cudaSuccess;
 }
 

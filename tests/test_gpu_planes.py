@@ -238,3 +238,35 @@ def test_no_bounded_wait_gave_up(cuda_ops):
     from sbnet_b200 import lib
     torch.cuda.synchronize()
     assert lib.wait_timeouts() == 0
+
+
+def test_shared_memory_limit_is_consistent_across_host_threads(cuda_ops):
+    """A kernel's dynamic shared-memory limit belongs to the function, not to the calling thread: a small
+    launch of the same kernel from a second host thread (as an autograd engine's backward pass makes)
+    must not lower the limit under a later large launch from the first."""
+    import threading
+    import torch
+    from conftest import library_options
+    from sbnet_b200 import ops
+    dev = "cuda"
+    x = torch.randn((2, 64, 64, 32), device=dev)            # fp32, 128-byte pixels: the TMA pipeline's shape
+    big = cfg.halo_geom(64, 64)                             # 18x18 blocks: ~205 KB of stages
+    small = cfg.geom_for(64, 64, (3, 3), (3, 3), (0, 0))    # 3x3 blocks: a few KB
+    lists = {k: cfg.random_block_list(2, g.bcount, 0.6, seed=3) for k, g in (("big", big), ("small", small))}
+
+    def gather(kind):
+        g = big if kind == "big" else small
+        idx_h, cnt_h = lists[kind]
+        out = ops.sparse_gather(x, torch.from_numpy(cnt_h), torch.from_numpy(idx_h).to(dev), g.bsize, g.bstride,
+                                g.boffset, transpose=True)
+        torch.cuda.synchronize()
+        return out
+
+    with library_options(planes=1):                         # the persistent pipeline, whatever the launch size
+        ref_big, ref_small = gather("big").clone(), gather("small").clone()
+        result = {}
+        t = threading.Thread(target=lambda: result.update(small=gather("small")))
+        t.start()
+        t.join()
+        assert torch.equal(result["small"], ref_small)
+        assert torch.equal(gather("big"), ref_big)          # failed with "invalid argument" when limits were cached per thread
