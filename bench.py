@@ -272,45 +272,49 @@ def run_pipeline(torch, dist, ops, w, steps, warmup, world, exchange=None, marks
 
     main = torch.cuda.current_stream()
     side = torch.cuda.Stream(priority=-1) if prefetch else None
-    ahead = {}   # step -> (idx, cnt, event): reduce_mask results computed one step ahead on the side stream
     # the same buffers and geometry every step: arguments are validated once (ops.bind_*), which takes
-    # about 7 us of interpreter time off each call -- it matters when a rank's step is only tens of us
+    # about 7 us of interpreter time off each call -- it matters when a rank's step is only tens of us.
     # The mask has been resident since start-up and the kernel queued before a reduce_mask never writes
     # it, so its loads may overlap that kernel's tail (mask_stable).
     mask_fn = ops.bind_reduce_mask(w.masks[0], *g_in.as_lists(), tol=0.5, avgpool=False, mask_stable=True,
-                                   yield_core=yield_core, stream=side.cuda_stream if side is not None else None)
+                                   yield_core=yield_core, stream=side.cuda_stream if side is not None else None,
+                                   wait=side is None)
     gather_fn = ops.bind_sparse_gather(w.x, w.stack, g_in.bsize, g_in.bstride, g_in.boffset, transpose=True)
     scatter_fn = ops.bind_sparse_scatter_var(w.q, w.x, g_out.bsize, g_out.bstride, g_out.boffset, add=True, transpose=True)
     fast = FastEvents(torch)
-    ready_ev = [torch.cuda.Event() for _ in range(8)]     # index list of step i written (side stream)
-    held = []   # index lists stay referenced until the final synchronisation (they were allocated under
-                # the main stream and written on the side stream, so their memory must not be recycled early)
+    ready_ev = [torch.cuda.Event() for _ in range(8)]     # index list of step j written (side stream)
+    launched = {}   # step -> (idx, count, event): reduce_mask calls issued ahead on the side stream
+    held = []       # index lists stay referenced until the final synchronisation (they were allocated under
+                    # the main stream and are written on the side stream: their memory must not be recycled early)
+    AHEAD = 2       # steps the masks run ahead: the count of step i+1 is on the host before it is needed
 
-    def mask_call(i, ex, mk=None):
-        slot = ex.slot(i) if ex is not None else None
-        if mk is not None:
-            mk[0].record()
-        idx, cnt, _ = mask_fn(w.masks[i % len(w.masks)], slot)
-        if mk is not None:
-            mk[1].record()
-        return idx, cnt
-
-    def mask_ahead(i, ex):
-        idx, cnt = mask_call(i, ex)      # launched on the side stream by handle; returns once the count is on the host
-        ev = ready_ev[i % len(ready_ev)]
+    def launch_mask(j, ex):
+        idx, cnt, _ = mask_fn(w.masks[j % len(w.masks)], ex.slot(j) if ex is not None else None)   # returns at once
+        ev = ready_ev[j % len(ready_ev)]
         fast.record(ev, side)
         held.append(idx)
-        return idx, cnt, ev
+        launched[j] = (idx, cnt, ev)
 
     def step(i, mk=None, ex=None):
         if side is None:
-            idx, cnt = mask_call(i, ex, mk)
+            if mk is not None:
+                mk[0].record()
+            idx, cnt, _ = mask_fn(w.masks[i % len(w.masks)], ex.slot(i) if ex is not None else None)
+            if mk is not None:
+                mk[1].record()
+            nb = int(cnt[0])
         else:
-            if i not in ahead:          # the very first step has nothing computed ahead
-                ahead[i] = mask_ahead(i, ex)
-            idx, cnt, ready = ahead.pop(i)
-            fast.wait(main, ready)      # the gather reads the index list written on the side stream
-        nb = int(cnt[0])
+            # software pipelining over steps: reduce_mask depends on nothing of the steps before it, so
+            # the masks of the next steps are issued ahead on a second stream and their counts come back
+            # through pinned memory without the host ever waiting inside a call.  Every step issues
+            # exactly one reduce_mask, one gather and one scatter (the last steps' reduce_masks serve
+            # steps that are never run)
+            for j in range(i, i + AHEAD):          # only at the very first step is anything missing here
+                if j not in launched:
+                    launch_mask(j, ex)
+            idx, cnt, ready = launched.pop(i)
+            nb = ops.wait_count(cnt)
+            fast.wait(main, ready)                 # the gather reads the index list written on the side stream
         assert nb == w.nB, (nb, w.nB)
         if mk is not None:
             mk[2].record()
@@ -318,12 +322,7 @@ def run_pipeline(torch, dist, ops, w, steps, warmup, world, exchange=None, marks
         if mk is not None:
             mk[3].record()
         if side is not None:
-            # software pipelining over steps: the next step's reduce_mask (it depends on nothing of this
-            # step) is issued on a second stream, so its kernel and the host's wait for its count are off
-            # the critical path; the host runs ahead of the device by as many steps as that lets it.  Every
-            # step issues exactly one reduce_mask, one gather and one scatter (the last step's reduce_mask
-            # serves a step that is never run)
-            ahead[i + 1] = mask_ahead(i + 1, ex)
+            launch_mask(i + AHEAD, ex)
         scatter_fn(cnt, idx)
         if mk is not None:
             mk[4].record()
@@ -1018,7 +1017,7 @@ def main():
     ap.add_argument("--no-sync-free", action="store_true")
     ap.add_argument("--in-order", action="store_true",
                     help="issue every step's reduce_mask behind the previous step's scatter on one stream "
-                         "(default: one step ahead on a second stream)")
+                         "(default: two steps ahead on a second stream, counts fetched without blocking)")
     ap.add_argument("--no-suite", action="store_true", help="skip the op-level table of configurations 2-4 and 5 at 30 percent")
     ap.add_argument("--no-weak", action="store_true", help="N > 1: skip the second pass in the other scaling mode")
     ap.add_argument("--cpu-budget", type=float, default=12.0)

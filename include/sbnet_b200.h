@@ -54,6 +54,9 @@ extern "C" {
 #define SBNET_MASK_STABLE 4   /* the mask is not written by the operation queued just before this call on
                                  `stream`: its loads may overlap the tail of that operation (see below) */
 #define SBNET_COUNT_YIELD 8   /* with SBNET_COUNT_POLL: give the core away between looks at the count */
+#define SBNET_COUNT_NOWAIT 16 /* pinned count_host: return right after the launch; the word reads
+                                 SBNET_COUNT_PENDING until the kernel has stored the count (see below) */
+#define SBNET_COUNT_PENDING INT32_MIN
 
 /* int32 words of device scratch sbnet_reduce_mask needs */
 #define SBNET_REDUCE_MASK_SCRATCH_INTS 4
@@ -92,6 +95,10 @@ const char* sbnet_last_error(void);
  *                         sched_yield() between looks (for hosts that run one such thread per GPU on
  *                         shared cores).  An empty result is reported as ONE block with index (0,0,0),
  *                         as the reference does.
+ *   SBNET_COUNT_NOWAIT    (pinned memory only; other memory is rejected) the call stores SBNET_COUNT_PENDING
+ *                         in *count_host, enqueues the kernel and returns; the kernel stores the count
+ *                         (never negative) there when it is done, and the host looks when it needs it --
+ *                         a loop that issues the next masks ahead never blocks on a count.
  *   SBNET_MASK_STABLE     every kernel of the library is launched with programmatic stream serialization:
  *                         its CTAs may become resident while the kernel queued before it on `stream`
  *                         drains, and touch global memory only once that kernel has completed.  With this

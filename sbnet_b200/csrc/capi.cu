@@ -22,7 +22,7 @@ namespace {
 
 thread_local char g_err[320] = "";
 thread_local const char* g_site = "";
-constexpr int32_t kCountSentinel = INT32_MIN;
+constexpr int32_t kCountSentinel = SBNET_COUNT_PENDING;
 
 int reject(int code, const char* fmt, ...)
 {
@@ -212,7 +212,9 @@ SBNET_EXPORT int sbnet_reduce_mask(const float* mask, int N, int H, int W, float
         else
             (void)cudaGetLastError();
     }
-    if (hostDev != nullptr && (flags & SBNET_COUNT_POLL))
+    if ((flags & SBNET_COUNT_NOWAIT) && hostDev == nullptr)
+        return reject(SBNET_ERR_INVALID_ARGUMENT, "%s: SBNET_COUNT_NOWAIT needs count_host in pinned host memory", op);
+    if (hostDev != nullptr && (flags & (SBNET_COUNT_POLL | SBNET_COUNT_NOWAIT)))
         *count_host = kCountSentinel;
     if (!(flags & SBNET_SCRATCH_CLEAN))
         if (cudaError_t e = cudaMemsetAsync(scratch_dev, 0, sizeof(int32_t) * SBNET_REDUCE_MASK_SCRATCH_INTS, s))
@@ -222,7 +224,7 @@ SBNET_EXPORT int sbnet_reduce_mask(const float* mask, int N, int H, int W, float
                                                   active_block_indices, scratch_dev, hostDev,
                                                   (flags & SBNET_MASK_STABLE) != 0, s))
         return cuda_status(e);
-    if (count_host != nullptr) {
+    if (count_host != nullptr && !(flags & SBNET_COUNT_NOWAIT)) {
         if (hostDev != nullptr && (flags & SBNET_COUNT_POLL)) {
             // The kernel stores the count straight into pinned memory: watching that word is several
             // times quicker than putting the thread to sleep in a stream synchronisation.  A count is

@@ -16,6 +16,8 @@ SBNET_SCRATCH_CLEAN = 1
 SBNET_COUNT_POLL = 2
 SBNET_MASK_STABLE = 4
 SBNET_COUNT_YIELD = 8
+SBNET_COUNT_NOWAIT = 16
+SBNET_COUNT_PENDING = -(2 ** 31)
 SBNET_REDUCE_MASK_SCRATCH_INTS = 4
 
 _i, _f, _p, _sz = C.c_int, C.c_float, C.c_void_p, C.c_size_t

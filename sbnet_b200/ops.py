@@ -372,20 +372,42 @@ def sparse_scatter_var_dyn(x, count_dev: torch.Tensor, max_blocks: int, active_b
 # same geometry -- every layer of a network at inference time -- can bind those once: the returned
 # function takes only what changes from call to call.  Same library entry points, same results.
 
+def count_ready(bin_counts: torch.Tensor) -> bool:
+    """True once the kernel of a ``wait=False`` reduce_mask call has stored its count."""
+    return int(bin_counts[0]) != _lib.SBNET_COUNT_PENDING
+
+
+def wait_count(bin_counts: torch.Tensor, timeout_s: float = 10.0) -> int:
+    """Spins until the count of a ``wait=False`` reduce_mask call is on the host and returns it."""
+    n = int(bin_counts[0])
+    if n != _lib.SBNET_COUNT_PENDING:
+        return n
+    import time
+    t0 = time.perf_counter()
+    while True:
+        n = int(bin_counts[0])
+        if n != _lib.SBNET_COUNT_PENDING:
+            return n
+        if time.perf_counter() - t0 > timeout_s:
+            raise RuntimeError(f"reduce_mask count not delivered within {timeout_s} s")
+
+
 def bind_reduce_mask(mask_like: torch.Tensor, dynamic_bcount, dynamic_bsize, dynamic_bstride, dynamic_boffset, tol,
-                     avgpool=False, mask_stable=False, yield_core=False, stream: int = None):
+                     avgpool=False, mask_stable=False, yield_core=False, stream: int = None, wait: bool = True):
     """Returns ``call(mask, scratch=None) -> (active_block_indices, bin_counts, count_dev)`` for masks of
     ``mask_like``'s shape, dtype and device.  ``stream``: raw handle of the stream to launch on (default:
     torch's current stream at call time).  Every call allocates its index list and takes a fresh pinned
-    count and (unless ``scratch`` is given) a fresh scratch slot, as :func:`reduce_mask` does."""
+    count and (unless ``scratch`` is given) a fresh scratch slot, as :func:`reduce_mask` does.
+    ``wait=False``: the call returns right after the launch (``SBNET_COUNT_NOWAIT``); ``bin_counts`` holds
+    the count once :func:`count_ready` says so (:func:`wait_count` spins for it)."""
     _require_cuda(mask_like, "mask")
     N, H, W = _check_mask(mask_like)
     bch, bcw = _pair(dynamic_bcount, "dynamic_bcount")
     g = _geom(dynamic_bsize, dynamic_bstride, dynamic_boffset)
     device, shape = mask_like.device, tuple(mask_like.shape)
     rows = max(N * bch * bcw, 0)
-    flags = _lib.SBNET_COUNT_POLL | _lib.SBNET_SCRATCH_CLEAN | (_lib.SBNET_MASK_STABLE if mask_stable else 0) \
-        | (_lib.SBNET_COUNT_YIELD if yield_core else 0)
+    flags = _lib.SBNET_SCRATCH_CLEAN | (_lib.SBNET_MASK_STABLE if mask_stable else 0) \
+        | ((_lib.SBNET_COUNT_POLL | (_lib.SBNET_COUNT_YIELD if yield_core else 0)) if wait else _lib.SBNET_COUNT_NOWAIT)
     fn = _lib.load().sbnet_reduce_mask
     head = (N, H, W, float(tol), int(bool(avgpool)), *g, bch, bcw)
     n_scratch = _lib.SBNET_REDUCE_MASK_SCRATCH_INTS

@@ -227,3 +227,29 @@ def test_two_streams_with_their_own_scratch_do_not_interfere(cuda_ops):
             outs.append((ops.reduce_mask_async(b, *g.as_lists(), tol=0.5)[1], nb))
     torch.cuda.synchronize()
     assert all(int(c[0]) == n for c, n in outs)
+
+
+def test_count_without_waiting(cuda_ops):
+    """SBNET_COUNT_NOWAIT: the call returns after the launch, the pinned word reads SBNET_COUNT_PENDING until
+    the kernel stores the count; several calls may be in flight; pageable memory is refused."""
+    import ctypes as C
+    import torch
+    from sbnet_b200 import lib, ops
+    g = cfg.halo_geom(160, 176)
+    masks = [torch.from_numpy(cfg.rect_union_mask(2, 160, 176, seed=s, n_rects=k)).cuda() for s, k in ((1, 4), (2, 0), (3, 19))]
+    expect = [int(ops.reduce_mask(m, *g.as_lists(), tol=0.5)[1][0]) for m in masks]
+    call = ops.bind_reduce_mask(masks[0], *g.as_lists(), tol=0.5, wait=False)
+    for _ in range(50):
+        out = [call(m) for m in masks]                    # three launches in flight, nothing waited for
+        got = [ops.wait_count(cnt) for _, cnt, _ in out]
+        assert got == expect
+        assert all(ops.count_ready(cnt) for _, cnt, _ in out)
+    torch.cuda.synchronize()
+    assert [int(c[0]) for _, _, c in out] == expect       # the device-side counts agree
+    idx = torch.zeros((2 * g.bcount[0] * g.bcount[1], 3), dtype=torch.int16, device="cuda")
+    scratch = torch.zeros(4, dtype=torch.int32, device="cuda")
+    pageable = C.c_int32(5)
+    rc = lib.load().sbnet_reduce_mask(masks[0].data_ptr(), 2, 160, 176, 0.5, 0, g.boffset[0], g.boffset[1], g.bsize[0],
+                                      g.bsize[1], g.bstride[0], g.bstride[1], g.bcount[0], g.bcount[1], idx.data_ptr(),
+                                      scratch.data_ptr(), C.addressof(pageable), lib.SBNET_COUNT_NOWAIT, None)
+    assert rc == -1 and "pinned" in lib.load().sbnet_last_error().decode() and pageable.value == 5
