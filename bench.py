@@ -1025,6 +1025,7 @@ def main():
     ap.add_argument("--arch", choices=["resnet-50", "resnet-v2"], default="resnet-v2", help="--suite topleft: size table")
     ap.add_argument("--topleft-test", choices=["conv", "res"], default="res")
     ap.add_argument("--topleft-dtype", choices=["f16", "f32"], default="f16")
+    ap.add_argument("--topleft-eager", action="store_true", help="--suite topleft: time eager launches instead of CUDA graphs")
     ap.add_argument("--topleft-stage", type=int, default=None, help="--suite topleft: one stage (0-3) instead of all")
     ap.add_argument("--topleft-sparsity", type=float, default=None, help="--suite topleft: one sparsity instead of the list")
     ap.add_argument("--case", default="gather_f16_t1")

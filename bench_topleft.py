@@ -40,18 +40,36 @@ def top_left_mask(N: int, H: int, W: int, sparsity: float) -> np.ndarray:
     return m
 
 
-def _time_runs(torch, fn_of_repeat):
-    """Three warm-ups, then three runs of five repeats each between CUDA events; mean time of one repeat."""
-    for _ in range(N_WARMUP):
+def _time_runs(torch, fn_of_repeat, graph=True):
+    """Three warm-ups, then three runs of five repeats each between CUDA events; mean time of one repeat.
+    The five repeats are captured into one CUDA graph and replayed (the reference's harness runs a
+    TensorFlow graph, which has no per-op interpreter cost either); ``graph=False`` times eager launches."""
+    def run_all():
         for i in range(N_REPEAT):
             fn_of_repeat(i)
+    for _ in range(N_WARMUP):
+        run_all()
     torch.cuda.synchronize()
+    replay = run_all
+    if graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            run_all()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            run_all()
+        replay = g.replay
+        for _ in range(N_WARMUP):
+            replay()
+        torch.cuda.synchronize()
     times = []
     for _ in range(N_RUN):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        for i in range(N_REPEAT):
-            fn_of_repeat(i)
+        replay()
         b.record()
         torch.cuda.synchronize()
         times.append(a.elapsed_time(b) / N_REPEAT)
@@ -91,7 +109,7 @@ def topleft(args):
 
                 def dense(i):
                     return F.conv2d(xs_nchw[i], w, padding=1)
-            dense_ms = _time_runs(torch, dense)
+            dense_ms = _time_runs(torch, dense, graph=not args.topleft_eager)
             for sparsity in sparsities:
                 mask = torch.from_numpy(top_left_mask(BATCH, H, W, sparsity)).to(dev)
                 best = None
@@ -116,7 +134,7 @@ def topleft(args):
                             q = F.conv2d(p, w).contiguous()
                             return ops.sparse_scatter_var(q, cnt, idx, xs[i], bp.bsize_out, bp.bsize_out, [0, 0],
                                                           add=False, transpose=True)
-                    ms = _time_runs(torch, sparse)
+                    ms = _time_runs(torch, sparse, graph=not args.topleft_eager)
                     if best is None or ms < best["sparse_ms"]:
                         best = {"BH": b, "BW": b, "sparse_ms": ms, "block_sparsity": block_sparsity, "active_blocks": nb}
                 print(json.dumps({"case": f"topleft_{args.topleft_test}", "arch": args.arch, "dtype": args.topleft_dtype,
@@ -124,6 +142,7 @@ def topleft(args):
                                   "block_sparsity": round(best["block_sparsity"], 4), "BH": best["BH"], "BW": best["BW"],
                                   "active_blocks": best["active_blocks"], "dense_ms": round(dense_ms, 4),
                                   "sparse_ms": round(best["sparse_ms"], 4),
-                                  "speedup": round(dense_ms / best["sparse_ms"], 3)}), flush=True)
+                                  "speedup": round(dense_ms / best["sparse_ms"], 3),
+                                  "timing": "eager" if args.topleft_eager else "cuda graph of 5 repeats"}), flush=True)
             del xs, xs_nchw
             torch.cuda.empty_cache()

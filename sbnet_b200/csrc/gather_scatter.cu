@@ -287,6 +287,210 @@ __global__ void __launch_bounds__(kThreads, 4) planes_kernel(const BlockArgs a, 
     pdl_launch_dependents();
 }
 
+// ---- [nB,C,R,S] layout, any pixel size: whole image rows staged as raw bytes -----------------------
+// The general kernel above spends ~40 integer instructions per element (two divisions and a 64-bit
+// address per element in each phase) and is issue-bound on the shapes it exists for (pixels that are
+// not a multiple of 16 bytes).  This kernel takes the same shapes whenever a block row's pixels fit
+// the tile: a block row of S pixels x C channels is ONE contiguous run of the image, so it is moved as
+// raw bytes with aligned 16-byte accesses -- whatever C*sizeof(T) is -- into a row buffer that keeps the
+// run's misalignment (the copy "shifts" nothing: byte b of the run lands at offset (address & 15) + b),
+// ragged ends element by element, so nothing outside the clipped run is ever touched.  The transposition
+// then happens between the row buffers and the stack: a warp owns a channel plane at a time and its
+// lanes walk the pixels with running (row, column) counters -- no divisions -- so stack accesses are
+// consecutive elements of one plane.
+constexpr int kRawMaxRows = 256;      // block rows per work item (their phases are kept in shared memory)
+constexpr int kRawUnroll = 4;         // 16-byte slots (image side) / elements (stack side) in flight per thread
+
+struct RawPlan {
+    FastDiv rChunks;       // row chunks per block
+    FastDiv slotsPerRow;   // 16-byte slots a row buffer holds
+    int rowsPerItem;       // block rows per work item
+    int rowBytes;          // S * C * sizeof(T)
+    int rowPitch;          // bytes of one row buffer: rowBytes + its possible misalignment, a multiple of 16
+    int stepS, stepR;      // 32 % S, 32 / S: how (row, column) advance when a lane moves on by 32 pixels
+};
+
+template <int MODE, typename T>
+__global__ void __launch_bounds__(kThreads, 4) planes_rows_kernel(const BlockArgs a, const RawPlan p)
+{
+    pdl_wait();   // nothing is read or written before the kernel queued ahead of this one is done
+    __shared__ __align__(16) unsigned char tile[kTileBytes];
+    __shared__ unsigned char rowPhase[kRawMaxRows];   // (address of the row's first byte) & 15
+    constexpr int SZ = (int)sizeof(T);
+    typedef typename Vec<SZ>::type E;                 // one element as plain bits
+    const int nActive = active_count(a);
+    const long long nItems = (long long)nActive * p.rChunks.div;
+    const int S = a.bSzW, P = a.bSzH * a.bSzW;
+    const long long pixBytes = (long long)a.C * SZ;
+    const uintptr_t imgBase = reinterpret_cast<uintptr_t>(a.image);
+    const uint32_t tileAddr = smem_u32(tile);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    for (long long item = blockIdx.x; item < nItems; item += gridDim.x) {
+        uint32_t ib, rc;
+        p.rChunks.divmod((uint32_t)item, ib, rc);
+        const int r0 = (int)rc * p.rowsPerItem;
+        const int rows = min(p.rowsPerItem, a.bSzH - r0);
+        const int n = a.idx[ib * 3 + 0];
+        const int h0 = a.bOffsH + a.idx[ib * 3 + 1] * a.bStrH + r0;
+        const int w0 = a.bOffsW + a.idx[ib * 3 + 2] * a.bStrW;
+        const int sLo = max(0, -w0), sHi = max(sLo, min(S, a.W - w0));   // in-range pixels of every row: [sLo, sHi)
+        const long long bLo = sLo * pixBytes, bHi = sHi * pixBytes;      // ... as bytes of the row's run
+        // address the run of row rl WOULD start at (its pixel 0 may lie left of the image: never dereferenced there)
+        auto row_start = [&](int rl) -> long long {
+            return (long long)imgBase + (((long long)n * a.H + (h0 + rl)) * a.W + w0) * pixBytes;
+        };
+        if ((int)threadIdx.x < rows)
+            rowPhase[threadIdx.x] = (unsigned char)(row_start((int)threadIdx.x) & 15);
+        T* planes = reinterpret_cast<T*>(a.stack) + (long long)ib * a.C * P + (long long)r0 * S;   // [C][P] view at row r0
+        const int nPix = rows * S;
+
+        // One 16-byte slot of a row buffer and the piece of the row's clipped run it holds.
+        struct Slot {
+            long long lo, hi;   // global byte range [lo, hi) of the slot that belongs to the run (empty: lo >= hi)
+            long long A;        // the slot's global address (16-byte aligned)
+            uint32_t at;        // the slot's shared-memory address
+        };
+        const int nSlots = rows * (int)p.slotsPerRow.div;
+        auto slot_of = [&](int k) -> Slot {
+            Slot t;
+            t.lo = 0, t.hi = 0, t.A = 0, t.at = 0;
+            if (k >= nSlots)
+                return t;
+            uint32_t rl, q;
+            p.slotsPerRow.divmod((uint32_t)k, rl, q);
+            const int h = h0 + (int)rl;
+            if (h < 0 || h >= a.H)
+                return t;
+            const long long g0 = row_start((int)rl);
+            t.A = (g0 & ~15ll) + 16ll * q;
+            t.lo = max(t.A, g0 + bLo), t.hi = min(t.A + 16, g0 + bHi);
+            t.at = tileAddr + rl * (uint32_t)p.rowPitch + 16u * q;
+            return t;
+        };
+        // Lane's pixel px of the item -> (its row buffer address for channel c, in range?); (rl, s) are the
+        // pixel's row and column inside the item and advance by 32 pixels per step without a division.
+        auto advance = [&](int& rl, int& s) {
+            s += p.stepS, rl += p.stepR;
+            if (s >= S)
+                s -= S, ++rl;
+        };
+        auto pixel_at = [&](int rl, int s, int c, bool& inr) -> uint32_t {
+            const int h = h0 + rl, w = w0 + s;
+            inr = h >= 0 && h < a.H && w >= 0 && w < a.W;
+            return tileAddr + (uint32_t)(rl * p.rowPitch) + rowPhase[min(rl, kRawMaxRows - 1)] + (uint32_t)((s * a.C + c) * SZ);
+        };
+        __syncthreads();   // rowPhase is set (and the previous item's buffers are no longer read)
+
+        if constexpr (MODE == kGather) {
+            // image -> row buffers: all loads of a batch are issued before its stores
+            for (int k0 = threadIdx.x; k0 < nSlots; k0 += kThreads * kRawUnroll) {
+                Slot t[kRawUnroll];
+                uint4 v[kRawUnroll];
+#pragma unroll
+                for (int u = 0; u < kRawUnroll; ++u) {
+                    t[u] = slot_of(k0 + u * kThreads);
+                    if (t[u].hi - t[u].lo == 16)
+                        v[u] = ld_stream(reinterpret_cast<const uint4*>(t[u].A));
+                }
+#pragma unroll
+                for (int u = 0; u < kRawUnroll; ++u) {
+                    if (t[u].hi - t[u].lo == 16) {
+                        sts128(t[u].at, v[u]);
+                    } else {   // a ragged end of the run (or nothing): element by element
+                        uint32_t at = t[u].at + (uint32_t)(t[u].lo - t[u].A);
+                        for (long long b = t[u].lo; b < t[u].hi; b += SZ, at += SZ) {
+                            const E e = ld_stream(reinterpret_cast<const E*>(b));
+                            if constexpr (SZ == 4)
+                                sts32(at, e);
+                            else
+                                sts16(at, e);
+                        }
+                    }
+                }
+            }
+            __syncthreads();
+            // row buffers -> stack: a warp writes consecutive pixels of one channel plane
+            for (int c = warp; c < a.C; c += kThreads / 32) {
+                int rl = lane / S, s = lane - rl * S;     // one division per plane, none per element
+                E* plane = reinterpret_cast<E*>(planes) + (long long)c * P;
+                for (int px = lane; px < nPix; px += 32) {
+                    bool inr;
+                    const uint32_t at = pixel_at(rl, s, c, inr);
+                    E e = 0;
+                    if (inr)
+                        e = SZ == 4 ? (E)lds32(at) : (E)lds16(at);
+                    plane[px] = e;
+                    advance(rl, s);
+                }
+            }
+        } else {
+            // stack -> row buffers: a warp reads consecutive pixels of one channel plane, a batch of loads at a time
+            for (int c = warp; c < a.C; c += kThreads / 32) {
+                int rl = lane / S, s = lane - rl * S;
+                const E* plane = reinterpret_cast<const E*>(planes) + (long long)c * P;
+                for (int px0 = lane; px0 < nPix; px0 += 32 * kRawUnroll) {
+                    E e[kRawUnroll];
+                    uint32_t at[kRawUnroll];
+                    bool inr[kRawUnroll];
+#pragma unroll
+                    for (int u = 0; u < kRawUnroll; ++u) {
+                        const int px = px0 + 32 * u;
+                        inr[u] = false, at[u] = 0, e[u] = 0;
+                        if (px < nPix) {
+                            at[u] = pixel_at(rl, s, c, inr[u]);
+                            if (inr[u])
+                                e[u] = ld_stream(plane + px);
+                            advance(rl, s);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < kRawUnroll; ++u) {
+                        if (inr[u]) {
+                            if constexpr (SZ == 4)
+                                sts32(at[u], e[u]);
+                            else
+                                sts16(at[u], e[u]);
+                        }
+                    }
+                }
+            }
+            __syncthreads();
+            // row buffers -> image: whole slots as 16-byte stores / adds / reductions, ragged ends by element
+            for (int k0 = threadIdx.x; k0 < nSlots; k0 += kThreads * kRawUnroll) {
+                Slot t[kRawUnroll];
+                uint4 old[kRawUnroll];
+#pragma unroll
+                for (int u = 0; u < kRawUnroll; ++u) {
+                    t[u] = slot_of(k0 + u * kThreads);
+                    old[u] = make_uint4(0, 0, 0, 0);
+                    if constexpr (MODE == kScatterAdd)
+                        if (t[u].hi - t[u].lo == 16)
+                            old[u] = *reinterpret_cast<const uint4*>(t[u].A);
+                }
+#pragma unroll
+                for (int u = 0; u < kRawUnroll; ++u) {
+                    if (t[u].hi - t[u].lo == 16) {
+                        image_write<16, MODE, T>(reinterpret_cast<uint4*>(t[u].A), lds128(t[u].at), old[u]);
+                    } else {
+                        uint32_t at = t[u].at + (uint32_t)(t[u].lo - t[u].A);
+                        for (long long b = t[u].lo; b < t[u].hi; b += SZ, at += SZ) {
+                            E* g = reinterpret_cast<E*>(b);
+                            const E e = SZ == 4 ? (E)lds32(at) : (E)lds16(at);
+                            E prev = 0;
+                            if constexpr (MODE == kScatterAdd)
+                                prev = *g;
+                            image_write<SZ, MODE, T>(g, e, prev);
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();   // the row buffers are reused by the next item
+    }
+    pdl_launch_dependents();
+}
+
 // ---- host side -----------------------------------------------------------------------------------
 int sm_count()
 {
@@ -350,9 +554,37 @@ static void launch_rows(const BlockArgs& a, cudaStream_t stream)
     }
 }
 
+// Whole block rows as raw bytes (planes_rows_kernel) whenever one row's pixels fit the tile.
+template <int MODE, typename T> static bool launch_planes_rows(const BlockArgs& a, cudaStream_t stream)
+{
+    const long long rowBytes = (long long)a.bSzW * a.C * (long long)sizeof(T);
+    const long long rowPitch = ((rowBytes + 15 + 15) / 16) * 16;   // the run, its misalignment (< 16), rounded up
+    if (rowPitch > kTileBytes)
+        return false;
+    RawPlan p;
+    p.rowBytes = (int)rowBytes, p.rowPitch = (int)rowPitch;
+    int rows = (int)(kTileBytes / rowPitch);
+    rows = rows < a.bSzH ? rows : a.bSzH;
+    rows = rows < kRawMaxRows ? rows : kRawMaxRows;
+    const int nChunks = (a.bSzH + rows - 1) / rows;
+    p.rowsPerItem = (a.bSzH + nChunks - 1) / nChunks;               // the fewest, nearly equal chunks of rows
+    p.rChunks = FastDiv((uint32_t)((a.bSzH + p.rowsPerItem - 1) / p.rowsPerItem));
+    p.slotsPerRow = FastDiv((uint32_t)(rowPitch / 16));
+    p.stepS = 32 % a.bSzW, p.stepR = 32 / a.bSzW;
+    const long long nItems = (long long)a.numActive * p.rChunks.div;
+    static const int perSm = ctas_per_sm(planes_rows_kernel<MODE, T>, kThreads);
+    const int wave = perSm * sm_count();
+    const bool perItem = a.num_active_dev == nullptr && nItems <= 0x7fffffffll;
+    const unsigned grid = (unsigned)(perItem ? nItems : (nItems < wave ? nItems : wave));
+    launch_pdl(planes_rows_kernel<MODE, T>, dim3(grid), dim3(kThreads), 0, stream, a, p);
+    return true;
+}
+
 template <int VB, int MODE, typename T>
 static void launch_planes(const BlockArgs& a, cudaStream_t stream)
 {
+    if (options().planes != 4 && launch_planes_rows<MODE, T>(a, stream))   // option planes=4 keeps the element-wise kernel
+        return;
     const int itemsize = (int)sizeof(T);
     PlanePlan p;
     const int RS = a.bSzH * a.bSzW;

@@ -14,8 +14,16 @@ from atomic_check import check_atomic_add
 # channel counts chosen to hit every vector width: C*sizeof(T) in {2,4,6,8,12,14,16,30,48,...}
 @pytest.mark.parametrize("dtype", [np.float32, np.float16], ids=["f32", "f16"])
 @pytest.mark.parametrize("C", [1, 2, 3, 4, 6, 7, 8, 15, 24, 40])
-@pytest.mark.parametrize("transpose", [False, True], ids=["rows", "planes"])
+@pytest.mark.parametrize("transpose", [False, True, "elementwise"], ids=["rows", "planes", "planes_elementwise"])
 def test_mode_matrix(cuda_ops, oracle_port, dtype, C, transpose):
+    """``planes``: pixels that are not 16-byte multiples run the raw-row kernel of the general path;
+    ``planes_elementwise`` sends the same calls through its element-wise kernel."""
+    from conftest import library_options
+    with library_options(planes=4 if transpose == "elementwise" else 0):
+        _mode_matrix(cuda_ops, oracle_port, dtype, C, bool(transpose))
+
+
+def _mode_matrix(cuda_ops, oracle_port, dtype, C, transpose):
     N, H, W = 2, 23, 31
     bsize, bstride, boffset = (5, 4), (3, 4), (-2, -1)      # rows overlap, columns touch
     g = cfg.geom_for(H, W, bsize, bstride, boffset)

@@ -59,15 +59,15 @@ def _ids():
     return [f"{np.dtype(s[0]).name}_C{s[4]}_b{s[5][0]}x{s[5][1]}_s{s[6][0]}x{s[6][1]}" for s in SHAPES]
 
 
-@pytest.fixture(params=["default", "tma_tile", "tile_ctas", "tma_pipeline", "general"])
+@pytest.fixture(params=["default", "tma_tile", "tile_ctas", "tma_pipeline", "general", "general_elementwise"])
 def tma_off(request):
     """Selects which plane-layout implementation takes the call: the default dispatch (which sends
     launches as small as these tests' gathers to the TMA pipeline where the shape allows), the tile CTAs
     fed by TMA whatever the launch size, the tile CTAs with plain loads, the persistent TMA pipeline, or the
-    general kernel."""
+    general kernels (whole rows as raw bytes; element-wise)."""
     from conftest import library_options
-    planes = {"default": 0, "general": 0, "tma_pipeline": 1, "tile_ctas": 2, "tma_tile": 3}[request.param]
-    with library_options(planes=planes, disable_tma=int(request.param == "general"), tile_blocks=0):
+    planes = {"default": 0, "general": 0, "tma_pipeline": 1, "tile_ctas": 2, "tma_tile": 3, "general_elementwise": 4}[request.param]
+    with library_options(planes=planes, disable_tma=int(request.param.startswith("general")), tile_blocks=0):
         yield request.param
 
 
