@@ -261,7 +261,7 @@ class Workload:
 
 
 def run_pipeline(torch, dist, ops, w, steps, warmup, world, exchange=None, marks=False, common_start=True,
-                 prefetch=False):
+                 prefetch=False, ahead=2):
     """`warmup` untimed and `steps` timed passes of reduce_mask -> gather -> scatter over workload `w`.
     Returns (ms of the timed region on this rank, blocks processed, per-op event times or None, wall-clock
     window).  The timed steps carry no per-op events (they cost host time between the launches); a
@@ -282,17 +282,24 @@ def run_pipeline(torch, dist, ops, w, steps, warmup, world, exchange=None, marks
     gather_fn = ops.bind_sparse_gather(w.x, w.stack, g_in.bsize, g_in.bstride, g_in.boffset, transpose=True)
     scatter_fn = ops.bind_sparse_scatter_var(w.q, w.x, g_out.bsize, g_out.bstride, g_out.boffset, add=True, transpose=True)
     fast = FastEvents(torch)
-    ready_ev = [torch.cuda.Event() for _ in range(8)]     # index list of step j written (side stream)
+    RING = 8
+    ready_ev = [torch.cuda.Event() for _ in range(RING)]  # index list of step j written (side stream)
+    free_ev = [torch.cuda.Event() for _ in range(RING)]   # index list of step j read for the last time (main stream)
+    # the index lists rotate through a few buffers allocated once (a fresh tensor per step would send the
+    # first pass over a new batch through the caching allocator's slow path every few steps); a buffer is
+    # rewritten only after the scatter that read it last, which the side stream waits for
+    idx_ring = [torch.empty((w.N * g_in.bcount[0] * g_in.bcount[1], 3), dtype=torch.int16, device=w.x.device)
+                for _ in range(RING)] if side is not None else None
     launched = {}   # step -> (idx, count, event): reduce_mask calls issued ahead on the side stream
-    held = []       # index lists stay referenced until the final synchronisation (they were allocated under
-                    # the main stream and are written on the side stream: their memory must not be recycled early)
-    AHEAD = 2       # steps the masks run ahead: the count of step i+1 is on the host before it is needed
+    AHEAD = ahead   # steps the masks run ahead: the count of step i+1 is on the host before it is needed
 
     def launch_mask(j, ex):
-        idx, cnt, _ = mask_fn(w.masks[j % len(w.masks)], ex.slot(j) if ex is not None else None)   # returns at once
-        ev = ready_ev[j % len(ready_ev)]
+        if j >= RING:
+            fast.wait(side, free_ev[j % RING])             # recorded behind the scatter of step j - RING
+        idx, cnt, _ = mask_fn(w.masks[j % len(w.masks)], ex.slot(j) if ex is not None else None,
+                              idx_ring[j % RING])          # returns at once
+        ev = ready_ev[j % RING]
         fast.record(ev, side)
-        held.append(idx)
         launched[j] = (idx, cnt, ev)
 
     def step(i, mk=None, ex=None):
@@ -324,6 +331,8 @@ def run_pipeline(torch, dist, ops, w, steps, warmup, world, exchange=None, marks
         if side is not None:
             launch_mask(i + AHEAD, ex)
         scatter_fn(cnt, idx)
+        if side is not None:
+            fast.record(free_ev[i % RING], main)
         if mk is not None:
             mk[4].record()
         if ex is not None:

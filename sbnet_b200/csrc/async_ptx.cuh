@@ -3,6 +3,8 @@
 // and the programmatic-dependent-launch controls.
 #pragma once
 #include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <stdint.h>
 
 namespace sbnet {
@@ -18,6 +20,39 @@ __device__ __forceinline__ void bulk_store_1d(void* dst, uint32_t src, uint32_t 
 {
     asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes)
                  : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+// The same copy without closing the group: several copies, then one bulk_commit().
+__device__ __forceinline__ void bulk_store_1d_nocommit(void* dst, uint32_t src, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes)
+                 : "memory");
+}
+// dst[i] += src[i] for every element of the run, each an addition performed in L2 (round to nearest even,
+// 16-bit types without flushing subnormals), like red.global.add.  Both addresses 16-byte aligned, size a
+// multiple of 16 bytes.  T: float, __half or __nv_bfloat16.
+template <typename T> __device__ __forceinline__ void bulk_reduce_add_1d(void* dst, uint32_t src, uint32_t bytes);
+template <> __device__ __forceinline__ void bulk_reduce_add_1d<float>(void* dst, uint32_t src, uint32_t bytes)
+{
+    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst), "r"(src),
+                 "r"(bytes)
+                 : "memory");
+}
+template <> __device__ __forceinline__ void bulk_reduce_add_1d<__half>(void* dst, uint32_t src, uint32_t bytes)
+{
+    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.f16 [%0], [%1], %2;" ::"l"(dst),
+                 "r"(src), "r"(bytes)
+                 : "memory");
+}
+template <> __device__ __forceinline__ void bulk_reduce_add_1d<__nv_bfloat16>(void* dst, uint32_t src, uint32_t bytes)
+{
+    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.bf16 [%0], [%1], %2;" ::"l"(dst),
+                 "r"(src), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit()
+{
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 

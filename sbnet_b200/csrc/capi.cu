@@ -124,7 +124,7 @@ Options& options()
     static std::once_flag once;
     std::call_once(once, [] {
         const char* planes = getenv("SBNET_PLANES");
-        opt.planes = (planes && planes[0] == 't') ? (planes[1] == 'i' ? 2 : 1) : 0;
+        opt.planes = (planes && planes[0] == 't') ? (planes[1] == 'i' ? 2 : 1) : env_number("SBNET_PLANES", 0);   // tma | tile | 0..5
         opt.disableTma = env_number("SBNET_DISABLE_TMA", 0) == 1;
         opt.tileBlocks = env_number("SBNET_TILE_BLOCKS", 0);
         opt.rmKernel = env_number("SBNET_RM_KERNEL", 0);
@@ -353,11 +353,13 @@ SBNET_EXPORT int sbnet_wait_timeouts(unsigned int* count)
 {
     if (count == nullptr)
         return reject(SBNET_ERR_INVALID_ARGUMENT, "sbnet_wait_timeouts: null output");
-    unsigned int planes = 0, mask = 0;
+    unsigned int planes = 0, mask = 0, rows = 0;
     if (cudaError_t e = sbnet::read_wait_timeouts(&planes))
         return cuda_status(e);
     if (cudaError_t e = sbnet::read_rm_wait_timeouts(&mask))
         return cuda_status(e);
-    *count = planes + mask;
+    if (cudaError_t e = sbnet::read_rows_wait_timeouts(&rows))
+        return cuda_status(e);
+    *count = planes + mask + rows;
     return SBNET_OK;
 }

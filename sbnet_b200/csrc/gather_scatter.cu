@@ -13,10 +13,12 @@
 //    the widest vector (16/8/4/2 bytes) that divides C*sizeof(T), several per thread in flight, no
 //    shared memory.
 //  * [nB, C, R, S] ("planes", transpose=true): pixels of a multiple of 16 bytes go to the kernels of
-//    planes_simt.cu / planes_tma.cu.  The kernel here takes every other shape: a CTA stages a tile
-//    of pixels x channels (128 bytes of channels per pixel) in shared memory with an odd word pitch,
-//    so that the image side moves channel runs and the stack side moves runs of consecutive pixels
-//    of one channel plane, both conflict-free.
+//    planes_simt.cu / planes_tma.cu.  The kernels here take every other shape.  planes_rows_kernel:
+//    whole block rows travel between the image and shared memory as raw bytes through the TMA
+//    engine (untiled bulk copies, bulk stores / reductions), and warps transpose between those row
+//    buffers and the stack.  planes_kernel (block rows too long for the tile; the A/B option): a CTA
+//    stages a tile of pixels x channels in shared memory with an odd word pitch and moves both sides
+//    element-wise.
 // Scatter has three write modes: overwrite, read-add-write (legal only for disjoint blocks) and
 // vector reductions (red.global.add .v4.f32 / .v4.f16x2 / .v4.bf16x2 and narrower) for overlapping halos.
 //
@@ -291,40 +293,67 @@ __global__ void __launch_bounds__(kThreads, 4) planes_kernel(const BlockArgs a, 
 // The general kernel above spends ~40 integer instructions per element (two divisions and a 64-bit
 // address per element in each phase) and is issue-bound on the shapes it exists for (pixels that are
 // not a multiple of 16 bytes).  This kernel takes the same shapes whenever a block row's pixels fit
-// the tile: a block row of S pixels x C channels is ONE contiguous run of the image, so it is moved as
-// raw bytes with aligned 16-byte accesses -- whatever C*sizeof(T) is -- into a row buffer that keeps the
-// run's misalignment (the copy "shifts" nothing: byte b of the run lands at offset (address & 15) + b),
-// ragged ends element by element, so nothing outside the clipped run is ever touched.  The transposition
-// then happens between the row buffers and the stack: a warp owns a channel plane at a time and its
-// lanes walk the pixels with running (row, column) counters -- no divisions -- so stack accesses are
-// consecutive elements of one plane.
-constexpr int kRawMaxRows = 256;      // block rows per work item (their phases are kept in shared memory)
-constexpr int kRawUnroll = 4;         // 16-byte slots (image side) / elements (stack side) in flight per thread
+// the tile.  A block row of S pixels x C channels is ONE contiguous run of the image, so whatever
+// C*sizeof(T) is, the run moves between the image and a row buffer as raw bytes through the TMA
+// engine -- one untiled bulk copy per block row, no thread touches it: the buffer keeps the run's
+// misalignment (byte b of the run lands at offset (address & 15) + b), which makes both ends of the
+// copy 16-byte aligned.
+//   image -> buffer: the 16-byte vectors that hold the run clipped to the image (a vector that holds
+//     one byte of the tensor lies in the same page as that byte, so the few bytes read beside the run
+//     belong to the same allocation; they are never used).
+//   buffer -> image: the whole 16-byte vectors inside the clipped run as one bulk store -- or one
+//     bulk reduction (cp.reduce.async.bulk .add), element-wise adds in L2 like red.global.add, for
+//     overlapping blocks -- and the run's two ragged ends (< 16 bytes each) element by element, so
+//     nothing outside the run is written.  Read-add-write of fp32 (kept apart from the reduction,
+//     which flushes subnormals) loads the rows first, adds in shared memory and stores them.
+// The transposition happens between the row buffers and the stack: a warp takes 32 consecutive pixels
+// x a group of channels at a time, one pixel per lane -- one division and one range test per task,
+// then only constant offsets on the shared-memory side and one plane pitch per channel on the stack
+// side, whose accesses are 32 consecutive elements of one plane.
+constexpr int kRawMaxRows = 1024;     // block rows per work item (a bound on the loop of the issuing warp)
+template <typename T> struct RawChans { static constexpr int n = sizeof(T) == 4 ? 12 : 16; };   // channels per task
+
+__device__ unsigned int g_rows_wait_timeouts = 0;   // bounded waits of planes_rows_kernel that gave up
 
 struct RawPlan {
     FastDiv rChunks;       // row chunks per block
-    FastDiv slotsPerRow;   // 16-byte slots a row buffer holds
+    FastDiv blockW;        // S
+    FastDiv chanGroups;    // channel groups per pixel group
+    int chansPerGroup;     // channels of one group (the last may hold fewer), <= RawChans<T>::n
     int rowsPerItem;       // block rows per work item
-    int rowBytes;          // S * C * sizeof(T)
-    int rowPitch;          // bytes of one row buffer: rowBytes + its possible misalignment, a multiple of 16
-    int stepS, stepR;      // 32 % S, 32 / S: how (row, column) advance when a lane moves on by 32 pixels
+    int rowPitch;          // bytes of one row buffer: S*C*sizeof(T) + its possible misalignment, a multiple of 16
 };
 
-template <int MODE, typename T>
+// Q: consecutive pixels of one channel plane a lane moves at a time on the stack side -- 1 (any shape), or the
+// 16 bytes' worth (4 / 8 pixels as ONE 16-byte access) when every plane of an item starts on a 16-byte boundary.
+template <int MODE, typename T, int Q>
 __global__ void __launch_bounds__(kThreads, 4) planes_rows_kernel(const BlockArgs a, const RawPlan p)
 {
-    pdl_wait();   // nothing is read or written before the kernel queued ahead of this one is done
-    __shared__ __align__(16) unsigned char tile[kTileBytes];
-    __shared__ unsigned char rowPhase[kRawMaxRows];   // (address of the row's first byte) & 15
+    __shared__ __align__(128) unsigned char tile[kTileBytes];
+    __shared__ __align__(8) unsigned long long barWord;
+    __shared__ int abortFlag;
     constexpr int SZ = (int)sizeof(T);
+    constexpr int G = RawChans<T>::n;
+    constexpr bool kLoads = MODE == kGather || MODE == kScatterAdd;   // image rows come into the buffers
     typedef typename Vec<SZ>::type E;                 // one element as plain bits
+    const uint32_t tileAddr = smem_u32(tile), bar = smem_u32(&barWord);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        abortFlag = 0;
+        if constexpr (kLoads) {
+            mbar_init(bar, 1);
+            mbar_init_fence();
+        }
+    }
+    __syncthreads();
+    pdl_wait();   // nothing is read or written before the kernel queued ahead of this one is done
     const int nActive = active_count(a);
     const long long nItems = (long long)nActive * p.rChunks.div;
     const int S = a.bSzW, P = a.bSzH * a.bSzW;
-    const long long pixBytes = (long long)a.C * SZ;
-    const uintptr_t imgBase = reinterpret_cast<uintptr_t>(a.image);
-    const uint32_t tileAddr = smem_u32(tile);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int pixBytes = a.C * SZ;
+    const long long imgRowBytes = (long long)a.W * pixBytes;
+    const int rowMis = (int)(imgRowBytes & 15);       // how the misalignment moves from one image row to the next
+    uint32_t parity = 0;
 
     for (long long item = blockIdx.x; item < nItems; item += gridDim.x) {
         uint32_t ib, rc;
@@ -335,156 +364,274 @@ __global__ void __launch_bounds__(kThreads, 4) planes_rows_kernel(const BlockArg
         const int h0 = a.bOffsH + a.idx[ib * 3 + 1] * a.bStrH + r0;
         const int w0 = a.bOffsW + a.idx[ib * 3 + 2] * a.bStrW;
         const int sLo = max(0, -w0), sHi = max(sLo, min(S, a.W - w0));   // in-range pixels of every row: [sLo, sHi)
-        const long long bLo = sLo * pixBytes, bHi = sHi * pixBytes;      // ... as bytes of the row's run
-        // address the run of row rl WOULD start at (its pixel 0 may lie left of the image: never dereferenced there)
-        auto row_start = [&](int rl) -> long long {
-            return (long long)imgBase + (((long long)n * a.H + (h0 + rl)) * a.W + w0) * pixBytes;
-        };
-        if ((int)threadIdx.x < rows)
-            rowPhase[threadIdx.x] = (unsigned char)(row_start((int)threadIdx.x) & 15);
+        const int bLo = sLo * pixBytes, bHi = sHi * pixBytes;            // ... as bytes of the row's run
+        // address the run of row 0 WOULD start at: its pixel 0 may lie left of, above or below the image; such an
+        // address only tells the alignment and is never dereferenced
+        const long long g00 = (long long)reinterpret_cast<uintptr_t>(a.image)
+            + (((long long)n * a.H + h0) * a.W + w0) * (long long)pixBytes;
+        const int ph0 = (int)(g00 & 15);
         T* planes = reinterpret_cast<T*>(a.stack) + (long long)ib * a.C * P + (long long)r0 * S;   // [C][P] view at row r0
         const int nPix = rows * S;
+        const int nTasks = ((nPix + 32 * Q - 1) / (32 * Q)) * (int)p.chanGroups.div;
 
-        // One 16-byte slot of a row buffer and the piece of the row's clipped run it holds.
-        struct Slot {
-            long long lo, hi;   // global byte range [lo, hi) of the slot that belongs to the run (empty: lo >= hi)
-            long long A;        // the slot's global address (16-byte aligned)
-            uint32_t at;        // the slot's shared-memory address
+        // Row rl of the item: the clipped run [lo, hi) as global addresses and the shared-memory address
+        // of the 16-byte vector that holds the run's (unclipped) first byte.
+        struct Row {
+            long long lo, hi;   // lo >= hi: nothing of the row is inside the image
+            long long base;     // global address of that first vector
+            uint32_t buf;       // its shared-memory address
         };
-        const int nSlots = rows * (int)p.slotsPerRow.div;
-        auto slot_of = [&](int k) -> Slot {
-            Slot t;
-            t.lo = 0, t.hi = 0, t.A = 0, t.at = 0;
-            if (k >= nSlots)
-                return t;
-            uint32_t rl, q;
-            p.slotsPerRow.divmod((uint32_t)k, rl, q);
-            const int h = h0 + (int)rl;
-            if (h < 0 || h >= a.H)
-                return t;
-            const long long g0 = row_start((int)rl);
-            t.A = (g0 & ~15ll) + 16ll * q;
-            t.lo = max(t.A, g0 + bLo), t.hi = min(t.A + 16, g0 + bHi);
-            t.at = tileAddr + rl * (uint32_t)p.rowPitch + 16u * q;
-            return t;
+        auto row_of = [&](int rl) -> Row {
+            Row r;
+            const long long g0 = g00 + rl * imgRowBytes;
+            r.base = g0 & ~15ll;
+            r.buf = tileAddr + (uint32_t)(rl * p.rowPitch);
+            r.lo = g0 + bLo, r.hi = g0 + bHi;
+            if ((unsigned)(h0 + rl) >= (unsigned)a.H)
+                r.hi = r.lo;
+            return r;
         };
-        // Lane's pixel px of the item -> (its row buffer address for channel c, in range?); (rl, s) are the
-        // pixel's row and column inside the item and advance by 32 pixels per step without a division.
-        auto advance = [&](int& rl, int& s) {
-            s += p.stepS, rl += p.stepR;
-            if (s >= S)
-                s -= S, ++rl;
+        // A task of the transposition: 32 consecutive pixels of the item (one per lane) x one channel group.
+        struct Task {
+            uint32_t at;        // row-buffer address of the lane's pixel, first channel of the group
+            E* g;               // the same element in the stack; channel c + 1 lies P elements further
+            int nc;             // channels of the group; 0 for a lane beyond the item's last pixel
+            bool inr;           // the pixel lies inside the image
         };
-        auto pixel_at = [&](int rl, int s, int c, bool& inr) -> uint32_t {
-            const int h = h0 + rl, w = w0 + s;
-            inr = h >= 0 && h < a.H && w >= 0 && w < a.W;
-            return tileAddr + (uint32_t)(rl * p.rowPitch) + rowPhase[min(rl, kRawMaxRows - 1)] + (uint32_t)((s * a.C + c) * SZ);
+        auto task_of = [&](int t) -> Task {
+            Task k;
+            uint32_t pg, cg, rl, s;
+            p.chanGroups.divmod((uint32_t)t, pg, cg);
+            const int px = (int)pg * 32 + lane, c0 = (int)cg * p.chansPerGroup;
+            k.nc = px < nPix ? min(p.chansPerGroup, a.C - c0) : 0;
+            p.blockW.divmod((uint32_t)min(px, nPix - 1), rl, s);
+            k.inr = (unsigned)(h0 + (int)rl) < (unsigned)a.H && (unsigned)(w0 + (int)s) < (unsigned)a.W;
+            k.at = tileAddr + rl * (uint32_t)p.rowPitch + (uint32_t)((ph0 + (int)rl * rowMis) & 15)
+                + (uint32_t)(((int)s * a.C + c0) * SZ);
+            k.g = reinterpret_cast<E*>(planes) + (long long)c0 * P + px;
+            return k;
         };
-        __syncthreads();   // rowPhase is set (and the previous item's buffers are no longer read)
 
-        if constexpr (MODE == kGather) {
-            // image -> row buffers: all loads of a batch are issued before its stores
-            for (int k0 = threadIdx.x; k0 < nSlots; k0 += kThreads * kRawUnroll) {
-                Slot t[kRawUnroll];
-                uint4 v[kRawUnroll];
-#pragma unroll
-                for (int u = 0; u < kRawUnroll; ++u) {
-                    t[u] = slot_of(k0 + u * kThreads);
-                    if (t[u].hi - t[u].lo == 16)
-                        v[u] = ld_stream(reinterpret_cast<const uint4*>(t[u].A));
+        if constexpr (kLoads) {
+            // image -> row buffers: warp 0 announces the bytes and issues one bulk copy per row
+            if (warp == 0) {
+                uint32_t bytes = 0;
+                for (int rl = lane; rl < rows; rl += 32) {
+                    const Row r = row_of(rl);
+                    if (r.lo < r.hi)
+                        bytes += (uint32_t)(((r.hi + 15) & ~15ll) - (r.lo & ~15ll));
                 }
-#pragma unroll
-                for (int u = 0; u < kRawUnroll; ++u) {
-                    if (t[u].hi - t[u].lo == 16) {
-                        sts128(t[u].at, v[u]);
-                    } else {   // a ragged end of the run (or nothing): element by element
-                        uint32_t at = t[u].at + (uint32_t)(t[u].lo - t[u].A);
-                        for (long long b = t[u].lo; b < t[u].hi; b += SZ, at += SZ) {
-                            const E e = ld_stream(reinterpret_cast<const E*>(b));
-                            if constexpr (SZ == 4)
-                                sts32(at, e);
-                            else
-                                sts16(at, e);
-                        }
+                bytes = __reduce_add_sync(0xffffffffu, bytes);
+                if (lane == 0)
+                    mbar_expect_tx(bar, bytes);
+                __syncwarp();
+                for (int rl = lane; rl < rows; rl += 32) {
+                    const Row r = row_of(rl);
+                    if (r.lo < r.hi) {
+                        const long long src = r.lo & ~15ll;
+                        bulk_load_1d(r.buf + (uint32_t)(src - r.base), reinterpret_cast<const void*>(src),
+                                     (uint32_t)(((r.hi + 15) & ~15ll) - src), bar);
                     }
                 }
             }
-            __syncthreads();
-            // row buffers -> stack: a warp writes consecutive pixels of one channel plane
-            for (int c = warp; c < a.C; c += kThreads / 32) {
-                int rl = lane / S, s = lane - rl * S;     // one division per plane, none per element
-                E* plane = reinterpret_cast<E*>(planes) + (long long)c * P;
-                for (int px = lane; px < nPix; px += 32) {
-                    bool inr;
-                    const uint32_t at = pixel_at(rl, s, c, inr);
-                    E e = 0;
-                    if (inr)
-                        e = SZ == 4 ? (E)lds32(at) : (E)lds16(at);
-                    plane[px] = e;
-                    advance(rl, s);
+            // every warp waits (bounded); one that gives up waits once more, again bounded, so that the copies are
+            // not left in flight over shared memory this CTA has given back
+            int ok = 1;
+            if (lane == 0) {
+                ok = mbar_wait_bounded(bar, parity, &abortFlag, &g_rows_wait_timeouts) ? 1 : 0;
+                if (!ok) {
+                    int again = 0;
+                    (void)mbar_wait_bounded(bar, parity, &again, &g_rows_wait_timeouts);
                 }
+            }
+            if (!__shfl_sync(0xffffffffu, ok, 0))
+                break;
+            parity ^= 1u;
+        }
+
+        if constexpr (Q > 1) {
+            // ---- vector stack accesses: a lane owns Q consecutive pixels (NW words), the channels of its group in
+            // batches of kB
+            constexpr int kB = 4, NW = Q * SZ / 4;
+            typedef typename Vec<4 * NW>::type V;
+            for (int t = warp; t < nTasks; t += kThreads / 32) {
+                uint32_t pg, cg, rl, sx;
+                p.chanGroups.divmod((uint32_t)t, pg, cg);
+                const int px0 = ((int)pg * 32 + lane) * Q, c0 = (int)cg * p.chansPerGroup;
+                const int nc = px0 < nPix ? min(p.chansPerGroup, a.C - c0) : 0;   // nPix is a multiple of Q
+                p.blockW.divmod((uint32_t)min(px0, nPix - Q), rl, sx);
+                uint32_t at[Q], inMask = 0;      // row-buffer address of every pixel (first channel of the group); in the image?
+#pragma unroll
+                for (int j = 0; j < Q; ++j) {
+                    at[j] = tileAddr + rl * (uint32_t)p.rowPitch + (uint32_t)((ph0 + (int)rl * rowMis) & 15)
+                        + (uint32_t)(((int)sx * a.C + c0) * SZ);
+                    if ((unsigned)(h0 + (int)rl) < (unsigned)a.H && (unsigned)(w0 + (int)sx) < (unsigned)a.W)
+                        inMask |= 1u << j;
+                    if (++sx == (uint32_t)S)
+                        sx = 0, ++rl;
+                }
+                V* g = reinterpret_cast<V*>(reinterpret_cast<E*>(planes) + (long long)c0 * P + px0);
+                const long long planeVecs = (long long)P / Q;     // P is a multiple of Q here
+                for (int u0 = 0; u0 < nc; u0 += kB, g += kB * planeVecs) {
+                    uint32_t w[kB][NW];
+                    if constexpr (MODE == kGather) {
+#pragma unroll
+                        for (int u = 0; u < kB; ++u) {
+                            if (u0 + u < nc) {
+#pragma unroll
+                                for (int j = 0; j < NW; ++j) {
+                                    if constexpr (SZ == 4) {
+                                        const uint32_t e = lds32(at[j] + (uint32_t)(u * SZ));
+                                        w[u][j] = ((inMask >> j) & 1u) ? e : 0u;
+                                    } else {
+                                        const uint32_t lo = lds16(at[2 * j] + (uint32_t)(u * SZ));
+                                        const uint32_t hi = lds16(at[2 * j + 1] + (uint32_t)(u * SZ));
+                                        w[u][j] = (((inMask >> (2 * j)) & 1u) ? lo : 0u)
+                                            | ((((inMask >> (2 * j + 1)) & 1u) ? hi : 0u) << 16);
+                                    }
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < kB; ++u) {
+                            if (u0 + u < nc) {
+                                if constexpr (NW == 4)
+                                    g[u * planeVecs] = make_uint4(w[u][0], w[u][1], w[u][2], w[u][3]);
+                                else
+                                    g[u * planeVecs] = w[u][0];
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int u = 0; u < kB; ++u) {
+                            if (u0 + u < nc) {
+                                const V v = ld_stream(g + u * planeVecs);
+                                if constexpr (NW == 4)
+                                    w[u][0] = v.x, w[u][1] = v.y, w[u][2] = v.z, w[u][3] = v.w;
+                                else
+                                    w[u][0] = v;
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < kB; ++u) {
+                            if (u0 + u < nc) {
+#pragma unroll
+                                for (int j = 0; j < Q; ++j) {
+                                    const uint32_t dst = at[j] + (uint32_t)(u * SZ);
+                                    E e = SZ == 4 ? (E)w[u][j] : (E)((j & 1) ? (w[u][j >> 1] >> 16) : (w[u][j >> 1] & 0xffffu));
+                                    if constexpr (MODE == kScatterAdd)   // the buffer holds the image's value
+                                        e = vadd<T>(SZ == 4 ? (E)lds32(dst) : (E)lds16(dst), e);
+                                    if constexpr (SZ == 4)
+                                        sts32(dst, e);
+                                    else
+                                        sts16(dst, e);
+                                }
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < Q; ++j)
+                        at[j] += kB * SZ;
+                }
+            }
+        } else if constexpr (MODE == kGather) {
+            // row buffers -> stack; pixels outside the image are zeros
+            for (int t = warp; t < nTasks; t += kThreads / 32) {
+                const Task k = task_of(t);
+                E e[G];
+#pragma unroll
+                for (int u = 0; u < G; ++u) {
+                    e[u] = 0;
+                    if (u < k.nc && k.inr)
+                        e[u] = SZ == 4 ? (E)lds32(k.at + u * SZ) : (E)lds16(k.at + u * SZ);
+                }
+#pragma unroll
+                for (int u = 0; u < G; ++u)
+                    if (u < k.nc)
+                        k.g[(long long)u * P] = e[u];
             }
         } else {
-            // stack -> row buffers: a warp reads consecutive pixels of one channel plane, a batch of loads at a time
-            for (int c = warp; c < a.C; c += kThreads / 32) {
-                int rl = lane / S, s = lane - rl * S;
-                const E* plane = reinterpret_cast<const E*>(planes) + (long long)c * P;
-                for (int px0 = lane; px0 < nPix; px0 += 32 * kRawUnroll) {
-                    E e[kRawUnroll];
-                    uint32_t at[kRawUnroll];
-                    bool inr[kRawUnroll];
+            // stack -> row buffers (pixels outside the image too: the stack holds them, the image never gets them)
+            for (int t = warp; t < nTasks; t += kThreads / 32) {
+                const Task k = task_of(t);
+                E e[G];
 #pragma unroll
-                    for (int u = 0; u < kRawUnroll; ++u) {
-                        const int px = px0 + 32 * u;
-                        inr[u] = false, at[u] = 0, e[u] = 0;
-                        if (px < nPix) {
-                            at[u] = pixel_at(rl, s, c, inr[u]);
-                            if (inr[u])
-                                e[u] = ld_stream(plane + px);
-                            advance(rl, s);
-                        }
-                    }
+                for (int u = 0; u < G; ++u)
+                    if (u < k.nc)
+                        e[u] = ld_stream(k.g + (long long)u * P);
 #pragma unroll
-                    for (int u = 0; u < kRawUnroll; ++u) {
-                        if (inr[u]) {
-                            if constexpr (SZ == 4)
-                                sts32(at[u], e[u]);
-                            else
-                                sts16(at[u], e[u]);
-                        }
+                for (int u = 0; u < G; ++u) {
+                    if (u < k.nc) {
+                        E v = e[u];
+                        if constexpr (MODE == kScatterAdd)   // the buffer holds the image's value
+                            v = vadd<T>(SZ == 4 ? (E)lds32(k.at + u * SZ) : (E)lds16(k.at + u * SZ), v);
+                        if constexpr (SZ == 4)
+                            sts32(k.at + u * SZ, v);
+                        else
+                            sts16(k.at + u * SZ, v);
                     }
                 }
             }
+        }
+        if constexpr (MODE != kGather) {
+            fence_async_smem();   // the bulk copies below read what the threads wrote
             __syncthreads();
-            // row buffers -> image: whole slots as 16-byte stores / adds / reductions, ragged ends by element
-            for (int k0 = threadIdx.x; k0 < nSlots; k0 += kThreads * kRawUnroll) {
-                Slot t[kRawUnroll];
-                uint4 old[kRawUnroll];
-#pragma unroll
-                for (int u = 0; u < kRawUnroll; ++u) {
-                    t[u] = slot_of(k0 + u * kThreads);
-                    old[u] = make_uint4(0, 0, 0, 0);
-                    if constexpr (MODE == kScatterAdd)
-                        if (t[u].hi - t[u].lo == 16)
-                            old[u] = *reinterpret_cast<const uint4*>(t[u].A);
+            // row buffers -> image: whole vectors inside the clipped run by the TMA engine ...
+            constexpr bool kEngine = !(MODE == kScatterAtomic && SZ == 2);
+            if constexpr (!kEngine) {
+                // ... except 16-bit accumulation: the engine's reduction adds one 16-bit element at a time (measured
+                // 2-3 times slower than the packed form), so a warp takes a row and reduces 16 bytes per lane
+                // (red.global.add.noftz.v4.f16x2 / .bf16x2)
+                for (int rl = warp; rl < rows; rl += kThreads / 32) {
+                    const Row r = row_of(rl);
+                    const long long aLo = (r.lo + 15) & ~15ll, aHi = r.hi & ~15ll;
+                    if (r.lo < r.hi)
+                        for (long long b = aLo + 16 * lane; b < aHi; b += 16 * 32)
+                            Red<T>::add(reinterpret_cast<uint4*>(b), lds128(r.buf + (uint32_t)(b - r.base)));
                 }
-#pragma unroll
-                for (int u = 0; u < kRawUnroll; ++u) {
-                    if (t[u].hi - t[u].lo == 16) {
-                        image_write<16, MODE, T>(reinterpret_cast<uint4*>(t[u].A), lds128(t[u].at), old[u]);
+            } else if (warp == 0) {
+                for (int rl = lane; rl < rows; rl += 32) {
+                    const Row r = row_of(rl);
+                    const long long aLo = (r.lo + 15) & ~15ll, aHi = r.hi & ~15ll;
+                    if (r.lo < r.hi && aLo < aHi) {
+                        if constexpr (MODE == kScatterAtomic)
+                            bulk_reduce_add_1d<T>(reinterpret_cast<void*>(aLo), r.buf + (uint32_t)(aLo - r.base), (uint32_t)(aHi - aLo));
+                        else
+                            bulk_store_1d_nocommit(reinterpret_cast<void*>(aLo), r.buf + (uint32_t)(aLo - r.base), (uint32_t)(aHi - aLo));
+                    }
+                }
+                bulk_commit();
+            }
+            // ... and the two ragged ends of every run element by element (side 0: head, side 1: tail)
+            for (int t = threadIdx.x; t < 2 * rows; t += kThreads) {
+                const Row r = row_of(t >> 1);
+                if (r.lo >= r.hi)
+                    continue;
+                const long long aLo = (r.lo + 15) & ~15ll, aHi = r.hi & ~15ll;
+                long long b, end;
+                if (aLo >= aHi)            // no whole vector inside the run: all of it is the head
+                    b = r.lo, end = (t & 1) ? r.lo : r.hi;
+                else if (t & 1)
+                    b = aHi, end = r.hi;
+                else
+                    b = r.lo, end = aLo;
+                constexpr int kEnd = MODE == kScatterAtomic ? kScatterAtomic : kScatterSet;
+                while (b < end) {
+                    const uint32_t at = r.buf + (uint32_t)(b - r.base);
+                    if (SZ == 2 && (b & 3) == 0 && b + 4 <= end) {
+                        // two 16-bit elements as one word (a packed reduction; the one-element form is far slower)
+                        const uint32_t e2 = lds32(at);
+                        image_write<4, kEnd, T>(reinterpret_cast<uint32_t*>(b), e2, e2);
+                        b += 4;
                     } else {
-                        uint32_t at = t[u].at + (uint32_t)(t[u].lo - t[u].A);
-                        for (long long b = t[u].lo; b < t[u].hi; b += SZ, at += SZ) {
-                            E* g = reinterpret_cast<E*>(b);
-                            const E e = SZ == 4 ? (E)lds32(at) : (E)lds16(at);
-                            E prev = 0;
-                            if constexpr (MODE == kScatterAdd)
-                                prev = *g;
-                            image_write<SZ, MODE, T>(g, e, prev);
-                        }
+                        const E e = SZ == 4 ? (E)lds32(at) : (E)lds16(at);
+                        image_write<SZ, kEnd, T>(reinterpret_cast<E*>(b), e, e);
+                        b += SZ;
                     }
                 }
             }
+            if (kEngine && warp == 0)
+                bulk_wait_read<0>();   // the engine has read the buffers
         }
         __syncthreads();   // the row buffers are reused by the next item
     }
@@ -562,33 +709,68 @@ template <int MODE, typename T> static bool launch_planes_rows(const BlockArgs& 
     if (rowPitch > kTileBytes)
         return false;
     RawPlan p;
-    p.rowBytes = (int)rowBytes, p.rowPitch = (int)rowPitch;
+    p.rowPitch = (int)rowPitch;
     int rows = (int)(kTileBytes / rowPitch);
     rows = rows < a.bSzH ? rows : a.bSzH;
     rows = rows < kRawMaxRows ? rows : kRawMaxRows;
     const int nChunks = (a.bSzH + rows - 1) / rows;
     p.rowsPerItem = (a.bSzH + nChunks - 1) / nChunks;               // the fewest, nearly equal chunks of rows
     p.rChunks = FastDiv((uint32_t)((a.bSzH + p.rowsPerItem - 1) / p.rowsPerItem));
-    p.slotsPerRow = FastDiv((uint32_t)(rowPitch / 16));
-    p.stepS = 32 % a.bSzW, p.stepR = 32 / a.bSzW;
+    p.blockW = FastDiv((uint32_t)a.bSzW);
+    // vector stack accesses when every plane of every item starts on the vector's boundary and holds whole vectors:
+    // 16 bytes, else (16-bit elements) 4 bytes
+    constexpr int kQuad = 16 / (int)sizeof(T);
+    const long long planeBytes = (long long)a.bSzH * a.bSzW * (long long)sizeof(T);
+    const long long itemBytes = (long long)p.rowsPerItem * a.bSzW * (long long)sizeof(T);
+    auto fits = [&](int vb) {
+        return (reinterpret_cast<uintptr_t>(a.stack) & (vb - 1)) == 0 && planeBytes % vb == 0
+            && (p.rChunks.div == 1 || itemBytes % vb == 0) && options().planes != 6;
+    };
+    const bool wide = fits(16);
+    const int q = wide ? kQuad : (sizeof(T) == 2 && fits(4) ? 2 : 1);
+    // channel groups: a warp task is 32 lanes x q pixels x one group.  Fewest rounds of the CTA's warps first, then
+    // the fewest tasks (each pays its address arithmetic once); the narrow path keeps a group in registers.
+    const int pixGroups = (p.rowsPerItem * a.bSzW + 32 * q - 1) / (32 * q);
+    const int warps = kThreads / 32, maxGroup = q > 1 ? a.C : RawChans<T>::n;
+    long long bestCost = -1;
+    int bestGroups = 1;
+    for (int groups = (a.C + maxGroup - 1) / maxGroup; groups <= a.C; ++groups) {
+        const int per = (a.C + groups - 1) / groups;
+        if ((long long)(groups - 1) * per >= a.C)
+            continue;                                                // an empty last group
+        const long long rounds = ((long long)pixGroups * groups + warps - 1) / warps;
+        const long long cost = rounds * ((long long)per * q * 3 + 60);   // ~3 instructions per element, ~60 per task
+        if (bestCost < 0 || cost < bestCost)
+            bestCost = cost, bestGroups = groups;
+    }
+    p.chanGroups = FastDiv((uint32_t)bestGroups);
+    p.chansPerGroup = (a.C + bestGroups - 1) / bestGroups;
     const long long nItems = (long long)a.numActive * p.rChunks.div;
-    static const int perSm = ctas_per_sm(planes_rows_kernel<MODE, T>, kThreads);
-    const int wave = perSm * sm_count();
     const bool perItem = a.num_active_dev == nullptr && nItems <= 0x7fffffffll;
-    const unsigned grid = (unsigned)(perItem ? nItems : (nItems < wave ? nItems : wave));
-    launch_pdl(planes_rows_kernel<MODE, T>, dim3(grid), dim3(kThreads), 0, stream, a, p);
+    auto go = [&](auto kernel) {
+        const int wave = ctas_per_sm(kernel, kThreads) * sm_count();
+        const unsigned grid = (unsigned)(perItem ? nItems : (nItems < wave ? nItems : wave));
+        launch_pdl(kernel, dim3(grid), dim3(kThreads), 0, stream, a, p);
+    };
+    if (wide) {
+        go(planes_rows_kernel<MODE, T, kQuad>);
+    } else if (q == 2) {
+        if constexpr (sizeof(T) == 2)
+            go(planes_rows_kernel<MODE, T, 2>);
+    } else {
+        go(planes_rows_kernel<MODE, T, 1>);
+    }
     return true;
 }
 
 template <int VB, int MODE, typename T>
 static void launch_planes(const BlockArgs& a, cudaStream_t stream)
 {
-    // 32-bit elements only: measured on [8,512,512,C] at 20 %, C = 33 fp32 gains (gather 61 -> 53 us, atomic
-    // scatter 66 -> 64 us) while C = 100 fp16 loses (92 -> 117 us, 115 -> 164 us: 2-byte accesses on both sides of
-    // the transposition).  Option planes=4 keeps the element-wise kernel for every shape.
-    if constexpr (sizeof(T) == 4)
-        if (options().planes != 4 && launch_planes_rows<MODE, T>(a, stream))
-            return;
+    // The raw-row kernel takes every shape whose block row fits its tile: measured on [8,512,512,C] at 20 %
+    // against the element-wise kernel below, C = 33 fp32 gather 65 -> 33 us, atomic scatter 70 -> 44 us; C = 100 fp16
+    // gather 93 -> 53 us, atomic scatter 117 -> 92 us.  Option planes=4 keeps the element-wise kernel.
+    if (options().planes != 4 && launch_planes_rows<MODE, T>(a, stream))
+        return;
     const int itemsize = (int)sizeof(T);
     PlanePlan p;
     const int RS = a.bSzH * a.bSzW;
@@ -709,6 +891,11 @@ cudaError_t launch_blocks(const BlockArgs& a, int dtype, int mode, bool transpos
     else
         dispatch_mode<__half>(a, mode, transpose, vb, stream);
     return cudaGetLastError();
+}
+
+cudaError_t read_rows_wait_timeouts(unsigned int* out)
+{
+    return cudaMemcpyFromSymbol(out, g_rows_wait_timeouts, sizeof(unsigned int));
 }
 
 // ---- flat copy (the non-Var scatter's "y = ybase") -----------------------------------------------

@@ -19,6 +19,7 @@ cudaError_t read_rm_wait_timeouts(unsigned int* out);
 // mode: 0 gather, 1 scatter overwrite, 2 scatter add (disjoint blocks), 3 scatter atomic add
 cudaError_t launch_blocks(const BlockArgs& a, int dtype, int mode, bool transpose,
                           cudaStream_t stream);
+cudaError_t read_rows_wait_timeouts(unsigned int* out);   // bounded waits of the raw-row plane kernel that gave up
 
 // Plane-layout fast path (TMA pipeline); *taken tells whether it accepted the call.
 cudaError_t launch_planes_tma(const BlockArgs& a, int dtype, int mode, cudaStream_t stream, bool* taken);

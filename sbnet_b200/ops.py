@@ -394,10 +394,12 @@ def wait_count(bin_counts: torch.Tensor, timeout_s: float = 10.0) -> int:
 
 def bind_reduce_mask(mask_like: torch.Tensor, dynamic_bcount, dynamic_bsize, dynamic_bstride, dynamic_boffset, tol,
                      avgpool=False, mask_stable=False, yield_core=False, stream: int = None, wait: bool = True):
-    """Returns ``call(mask, scratch=None) -> (active_block_indices, bin_counts, count_dev)`` for masks of
-    ``mask_like``'s shape, dtype and device.  ``stream``: raw handle of the stream to launch on (default:
-    torch's current stream at call time).  Every call allocates its index list and takes a fresh pinned
-    count and (unless ``scratch`` is given) a fresh scratch slot, as :func:`reduce_mask` does.
+    """Returns ``call(mask, scratch=None, out=None) -> (active_block_indices, bin_counts, count_dev)`` for
+    masks of ``mask_like``'s shape, dtype and device.  ``stream``: raw handle of the stream to launch on
+    (default: torch's current stream at call time).  Every call takes a fresh pinned count and (unless
+    ``scratch`` is given) a fresh scratch slot, as :func:`reduce_mask` does, and allocates its index list
+    unless ``out`` (int16 ``[N*bcount_h*bcount_w, 3]``, contiguous) is given: a caller that rotates a few
+    such buffers keeps the caching allocator out of its steps, and orders their reuse itself.
     ``wait=False``: the call returns right after the launch (``SBNET_COUNT_NOWAIT``); ``bin_counts`` holds
     the count once :func:`count_ready` says so (:func:`wait_count` spins for it)."""
     _require_cuda(mask_like, "mask")
@@ -412,11 +414,16 @@ def bind_reduce_mask(mask_like: torch.Tensor, dynamic_bcount, dynamic_bsize, dyn
     head = (N, H, W, float(tol), int(bool(avgpool)), *g, bch, bcw)
     n_scratch = _lib.SBNET_REDUCE_MASK_SCRATCH_INTS
 
-    def call(mask, scratch=None):
+    def call(mask, scratch=None, out=None):
         if tuple(mask.shape) != shape or mask.dtype != torch.float32 or mask.device != device or not mask.is_contiguous():
             raise ValueError("mask differs from the one this call was bound for")
         st = stream if stream is not None else _stream(device)
-        idx = torch.empty((rows, 3), dtype=torch.int16, device=device)
+        if out is None:
+            idx = torch.empty((rows, 3), dtype=torch.int16, device=device)
+        elif out.dtype != torch.int16 or tuple(out.shape) != (rows, 3) or out.device != device or not out.is_contiguous():
+            raise ValueError(f"out must be a contiguous int16 [{rows}, 3] tensor on the mask's device")
+        else:
+            idx = out
         counts = _pinned_count()
         if scratch is None:
             scratch = scratch_for(device, st)[0]

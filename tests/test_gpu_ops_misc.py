@@ -14,12 +14,14 @@ from atomic_check import check_atomic_add
 # channel counts chosen to hit every vector width: C*sizeof(T) in {2,4,6,8,12,14,16,30,48,...}
 @pytest.mark.parametrize("dtype", [np.float32, np.float16], ids=["f32", "f16"])
 @pytest.mark.parametrize("C", [1, 2, 3, 4, 6, 7, 8, 15, 24, 40])
-@pytest.mark.parametrize("transpose", [False, True, "elementwise"], ids=["rows", "planes", "planes_elementwise"])
+@pytest.mark.parametrize("transpose", [False, True, "elementwise", "raw_rows_narrow"],
+                         ids=["rows", "planes", "planes_elementwise", "planes_raw_rows_narrow"])
 def test_mode_matrix(cuda_ops, oracle_port, dtype, C, transpose):
     """``planes``: pixels that are not 16-byte multiples run the raw-row kernel of the general path;
-    ``planes_elementwise`` sends the same calls through its element-wise kernel."""
+    ``planes_elementwise`` sends the same calls through its element-wise kernel, ``planes_raw_rows_narrow``
+    through the raw-row kernel with element-wide stack accesses."""
     from conftest import library_options
-    with library_options(planes=4 if transpose == "elementwise" else 0):
+    with library_options(planes={"elementwise": 4, "raw_rows_narrow": 6}.get(transpose, 0)):
         _mode_matrix(cuda_ops, oracle_port, dtype, C, bool(transpose))
 
 
@@ -259,6 +261,17 @@ def test_bound_calls_match_the_ordinary_wrappers(cuda_ops):
                                    transpose=True)
         torch.cuda.synchronize()
         assert torch.equal(y, ref)
+    # an index list of the caller's: written in place, same list as a fresh one
+    mine = torch.full((cap, 3), -7, dtype=torch.int16, device=dev)
+    idx2, cnt2, _ = rm(masks[1], None, mine)
+    torch.cuda.synchronize()
+    assert idx2 is mine and int(cnt2[0]) == n
+    assert sorted(map(tuple, mine[:n].tolist())) == sorted(map(tuple, idx[:n].tolist()))
+    assert bool((mine[n:] == -7).all())
+    with pytest.raises(ValueError):
+        rm(masks[1], None, mine[:-1])
+    with pytest.raises(ValueError):
+        rm(masks[1], None, mine.to(torch.int32))
     with pytest.raises(ValueError):
         rm(masks[0][:1])
     with pytest.raises(ValueError):

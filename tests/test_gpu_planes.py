@@ -59,14 +59,16 @@ def _ids():
     return [f"{np.dtype(s[0]).name}_C{s[4]}_b{s[5][0]}x{s[5][1]}_s{s[6][0]}x{s[6][1]}" for s in SHAPES]
 
 
-@pytest.fixture(params=["default", "tma_tile", "tile_ctas", "tma_pipeline", "general", "general_elementwise"])
+@pytest.fixture(params=["default", "tma_tile", "tile_ctas", "tma_pipeline", "general", "general_elementwise",
+                        "general_raw_rows_narrow"])
 def tma_off(request):
     """Selects which plane-layout implementation takes the call: the default dispatch (which sends
     launches as small as these tests' gathers to the TMA pipeline where the shape allows), the tile CTAs
     fed by TMA whatever the launch size, the tile CTAs with plain loads, the persistent TMA pipeline, or the
-    general kernels (whole rows as raw bytes; element-wise)."""
+    general kernels (whole rows as raw bytes; element-wise; raw rows with element-wide stack accesses)."""
     from conftest import library_options
-    planes = {"default": 0, "general": 0, "tma_pipeline": 1, "tile_ctas": 2, "tma_tile": 3, "general_elementwise": 4}[request.param]
+    planes = {"default": 0, "general": 0, "tma_pipeline": 1, "tile_ctas": 2, "tma_tile": 3, "general_elementwise": 4,
+              "general_raw_rows_narrow": 6}[request.param]
     with library_options(planes=planes, disable_tma=int(request.param.startswith("general")), tile_blocks=0):
         yield request.param
 
