@@ -21,7 +21,7 @@
  *    caches (the last error text, the last few TMA tensor maps -- keyed by base address, shape and
  *    element size, so a buffer freed and re-allocated at the same address with the same shape reuses
  *    a still-valid map -- and which kernels already had their shared-memory limit raised); per-device
- *    caches (SM count, resolved address of the static scratch); two device-side counters of bounded
+ *    caches (SM count, resolved address of the static scratch); three device-side counters of bounded
  *    waits that gave up (sbnet_wait_timeouts); the process-wide option table (sbnet_set_option), which
  *    is initialised from the environment once, at first use; and the fixed scratch array of
  *    sbnet_reduce_mask_static, which all calls of that one entry point on a GPU share.
