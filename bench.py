@@ -292,11 +292,12 @@ def run_pipeline(torch, dist, ops, w, steps, warmup, world, exchange=None, marks
                 for _ in range(RING)] if side is not None else None
     launched = {}   # step -> (idx, count, event): reduce_mask calls issued ahead on the side stream
     AHEAD = ahead   # steps the masks run ahead: the count of step i+1 is on the host before it is needed
+    assert 1 <= AHEAD < RING - 1
 
     def launch_mask(j, ex):
         if j >= RING:
             fast.wait(side, free_ev[j % RING])             # recorded behind the scatter of step j - RING
-        idx, cnt, _ = mask_fn(w.masks[j % len(w.masks)], ex.slot(j) if ex is not None else None,
+        idx, cnt, _ = mask_fn(w.masks[j % len(w.masks)], ex.slot(j, side) if ex is not None else None,
                               idx_ring[j % RING])          # returns at once
         ev = ready_ev[j % RING]
         fast.record(ev, side)
@@ -366,6 +367,7 @@ def run_pipeline(torch, dist, ops, w, steps, warmup, world, exchange=None, marks
     for i in range(steps):
         blocks += step(warmup + i, mks[i] if marks else None, exchange)
     t1.record()
+    run_pipeline.host_issue_s = time.time() - wall0     # how long the host took to queue the timed steps
     torch.cuda.synchronize()
     wall1 = time.time()
     fence()
@@ -418,7 +420,7 @@ def run_ours(args):
 
     def exchange():
         # The only exchange of the path: every rank's block count per step, read from device memory.
-        return sbdist.CountExchange(dev, depth=8, timeout_s=60.0) if world > 1 else None
+        return sbdist.CountExchange(dev, depth=32, timeout_s=60.0) if world > 1 else None
 
     clocks = ClockSampler(local).start()
     ex = exchange()
@@ -533,7 +535,7 @@ def run_ours(args):
                 "active_blocks_per_rank": w.nB, "candidate_blocks_per_rank": w.N * w.g_in.bcount[0] * w.g_in.bcount[1],
                 "l2": "x (72 MB per image) exceeds L2 from two images on; masks rotate through copies and are evicted by the x traffic between uses",
                 "parallelism": f"dp{world}", "global_blocks_per_step": global_blocks if world > 1 else w.nB,
-                "collective": "all-gather of the ranks' int32 block counts, eight steps per call (NCCL), off the critical path",
+                "collective": "all-gather of the ranks' int32 block counts, 32 steps per call (NCCL), off the critical path",
             },
             "ops": {k: {"us": med_slowest[k] * 1e3, "us_rank0": med0[k] * 1e3, "algorithmic_bytes": w.bytes[k], "GB/s": gbs[k],
                         "frac_of_" + peak_kind: gbs[k] / peak} for k in med_slowest},

@@ -11,6 +11,7 @@ for device tensors, gloo for CPU tests).
 from __future__ import annotations
 
 import datetime
+import time
 from typing import List, Optional, Sequence, Tuple
 
 import torch
@@ -78,7 +79,13 @@ class CountExchange:
     wait for a ring's all-gather happens ``depth`` steps later, just before its slots are reused --
     by then it has long finished, and no rank ever waits for a slower peer inside a step.  On a CUDA
     device the collective is issued on a side stream behind an event recorded after the step's last
-    launch, so its kernel does not run beside the step's own kernels.
+    launch, so its kernel does not run beside the step's own kernels, and nothing here ever blocks
+    the HOST inside the loop: the stream that rewrites a ring's slots waits for the exchange in stream
+    order (a host that waits for a collective with a timeout is put to sleep a millisecond at a time
+    by the process-group library -- longer than the few queued steps of a short loop last, which
+    would drain the GPU's queue every ring).  ``timeout_s`` is then enforced where the host may wait:
+    in ``finish()``, and on an exchange still incomplete when its ring comes round a second time.
+    Building one is collective on a CUDA device (it runs a first, empty exchange).
     """
 
     SLOT = 4   # int32 words of one reduce_mask scratch slot; word 0 is the count
@@ -88,19 +95,33 @@ class CountExchange:
         self.world = dist.get_world_size(group)
         n = self.depth * self.SLOT
         self.rings = [torch.zeros(n, dtype=torch.int32, device=self.device) for _ in range(2)]
+        self.slots = [[r[k * self.SLOT:(k + 1) * self.SLOT] for k in range(self.depth)] for r in self.rings]
         self.gathered = [torch.zeros(self.world * n, dtype=torch.int32, device=self.device) for _ in range(2)]
-        self.work = [None, None]
+        self.work = [None, None]          # CPU: the collective's work; CUDA: (done event, count table)
+        self.pending = []                 # CUDA: (done event, time it was handed to a stream) not yet seen complete
         self.first_step = [None, None]
         self.history: List[torch.Tensor] = []    # [world, depth] count tables of finished rings
         self.side = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
+        if self.side is not None:
+            # One exchange of each ring before any step (the constructor is therefore collective: every rank
+            # builds its CountExchange at the same point).  The first collective on a new stream and the first
+            # allocation under it take 0.6 ms and at times tens of ms of host time (measured), more than the few
+            # queued steps of a short loop last; afterwards an exchange costs the host about 0.1 ms.
+            with torch.cuda.stream(self.side):
+                for b in range(2):
+                    work = dist.all_gather_into_tensor(self.gathered[b], self.rings[b], group=self.group, async_op=True)
+                    work.wait()
+                    self.gathered[b].view(self.world, self.depth, self.SLOT)[:, :, 0].clone()
+            self.side.synchronize()
 
-    def slot(self, step: int) -> torch.Tensor:
-        """The 4-word scratch slot of ``step``; waits (in stream order on a GPU) for the exchange that
-        last read this slot's ring."""
+    def slot(self, step: int, stream=None) -> torch.Tensor:
+        """The 4-word scratch slot of ``step``.  The exchange that last read this slot's ring is waited
+        for first: by the host on a CPU group, in stream order on a GPU -- ``stream`` is the torch stream
+        the reduce_mask writing the slot will run on (default: the current stream)."""
         b, k = (step // self.depth) % 2, step % self.depth
         if k == 0:
-            self._collect(b)
-        return self.rings[b][k * self.SLOT:(k + 1) * self.SLOT]
+            self._collect(b, stream)
+        return self.slots[b][k]
 
     def step_done(self, step: int, steps_total: Optional[int] = None) -> None:
         """Call after the step's last launch.  Starts the ring's all-gather when the ring is full (or
@@ -115,16 +136,38 @@ class CountExchange:
             ev.record()
             with torch.cuda.stream(self.side):
                 self.side.wait_event(ev)
-                self.work[b] = dist.all_gather_into_tensor(self.gathered[b], self.rings[b], group=self.group, async_op=True)
+                work = dist.all_gather_into_tensor(self.gathered[b], self.rings[b], group=self.group, async_op=True)
+                work.wait()   # no timeout: the side STREAM waits for the collective, the host does not
+                table = self.gathered[b].view(self.world, self.depth, self.SLOT)[:, :, 0].clone()
+                done = torch.cuda.Event()
+                done.record(self.side)
+            self.work[b] = (done, table)
         else:
             self.work[b] = dist.all_gather_into_tensor(self.gathered[b], self.rings[b], group=self.group, async_op=True)
 
-    def _collect(self, b: int) -> None:
+    def _host_wait(self, done, since: float) -> None:
+        """Host-side wait for an exchange's event, bounded by ``timeout_s`` counted from ``since``."""
+        while not done.query():
+            if self.timeout_s is not None and time.time() - since > self.timeout_s:
+                raise RankFailure(f"count exchange: not complete after {self.timeout_s} s")
+            time.sleep(0.0005)
+
+    def _collect(self, b: int, stream=None) -> None:
         if self.work[b] is None:
             return
-        wait_for(self.work[b], self.timeout_s)
+        if self.side is None:
+            wait_for(self.work[b], self.timeout_s)
+            table = self.gathered[b].view(self.world, self.depth, self.SLOT)[:, :, 0].clone()
+        else:
+            done, table = self.work[b]
+            # an exchange handed to a stream a whole round of both rings ago must be complete by now
+            for ev, since in self.pending:
+                self._host_wait(ev, since)
+            self.pending = []
+            if not done.query():
+                (stream if stream is not None else torch.cuda.current_stream(self.device)).wait_event(done)
+                self.pending.append((done, time.time()))
         self.work[b] = None
-        table = self.gathered[b].view(self.world, self.depth, self.SLOT)[:, :, 0].clone()
         self.history.append((self.first_step[b], table))
 
     def finish(self):
@@ -132,6 +175,11 @@ class CountExchange:
         for every step exchanged so far (a partly filled last ring reports its unused slots as 0)."""
         for b in range(2):
             self._collect(b)
+        for ev, since in self.pending:
+            self._host_wait(ev, since)
+        self.pending = []
+        if self.side is not None:
+            self.side.synchronize()
         out = {}
         for first, table in self.history:
             t = table.cpu().tolist()
