@@ -310,6 +310,11 @@ __global__ void __launch_bounds__(kThreads, 4) planes_kernel(const BlockArgs a, 
 // x a group of channels at a time, one pixel per lane -- one division and one range test per task,
 // then only constant offsets on the shared-memory side and one plane pitch per channel on the stack
 // side, whose accesses are 32 consecutive elements of one plane.
+// A CTA of the raw-row kernel: 128 threads and 24 KB of row buffers, eight per SM.  (256 threads and 44 KB, four per
+// SM, measured 3-8 % slower on C = 33 fp32 and C = 100 fp16: a CTA's load and transposition phases do not overlap,
+// so more and smaller CTAs interleave them better.)
+constexpr int kRawThreads = 128;
+constexpr int kRawTileBytes = 24576;
 constexpr int kRawMaxRows = 1024;     // block rows per work item (a bound on the loop of the issuing warp)
 template <typename T> struct RawChans { static constexpr int n = sizeof(T) == 4 ? 12 : 16; };   // channels per task
 
@@ -327,9 +332,9 @@ struct RawPlan {
 // Q: consecutive pixels of one channel plane a lane moves at a time on the stack side -- 1 (any shape), or the
 // 16 bytes' worth (4 / 8 pixels as ONE 16-byte access) when every plane of an item starts on a 16-byte boundary.
 template <int MODE, typename T, int Q>
-__global__ void __launch_bounds__(kThreads, 4) planes_rows_kernel(const BlockArgs a, const RawPlan p)
+__global__ void __launch_bounds__(kRawThreads, 8) planes_rows_kernel(const BlockArgs a, const RawPlan p)
 {
-    __shared__ __align__(128) unsigned char tile[kTileBytes];
+    __shared__ __align__(128) unsigned char tile[kRawTileBytes];
     __shared__ __align__(8) unsigned long long barWord;
     __shared__ int abortFlag;
     constexpr int SZ = (int)sizeof(T);
@@ -454,7 +459,7 @@ __global__ void __launch_bounds__(kThreads, 4) planes_rows_kernel(const BlockArg
             // batches of kB
             constexpr int kB = 4, NW = Q * SZ / 4;
             typedef typename Vec<4 * NW>::type V;
-            for (int t = warp; t < nTasks; t += kThreads / 32) {
+            for (int t = warp; t < nTasks; t += kRawThreads / 32) {
                 uint32_t pg, cg, rl, sx;
                 p.chanGroups.divmod((uint32_t)t, pg, cg);
                 const int px0 = ((int)pg * 32 + lane) * Q, c0 = (int)cg * p.chansPerGroup;
@@ -536,7 +541,7 @@ __global__ void __launch_bounds__(kThreads, 4) planes_rows_kernel(const BlockArg
             }
         } else if constexpr (MODE == kGather) {
             // row buffers -> stack; pixels outside the image are zeros
-            for (int t = warp; t < nTasks; t += kThreads / 32) {
+            for (int t = warp; t < nTasks; t += kRawThreads / 32) {
                 const Task k = task_of(t);
                 E e[G];
 #pragma unroll
@@ -552,7 +557,7 @@ __global__ void __launch_bounds__(kThreads, 4) planes_rows_kernel(const BlockArg
             }
         } else {
             // stack -> row buffers (pixels outside the image too: the stack holds them, the image never gets them)
-            for (int t = warp; t < nTasks; t += kThreads / 32) {
+            for (int t = warp; t < nTasks; t += kRawThreads / 32) {
                 const Task k = task_of(t);
                 E e[G];
 #pragma unroll
@@ -582,7 +587,7 @@ __global__ void __launch_bounds__(kThreads, 4) planes_rows_kernel(const BlockArg
                 // ... except 16-bit accumulation: the engine's reduction adds one 16-bit element at a time (measured
                 // 2-3 times slower than the packed form), so a warp takes a row and reduces 16 bytes per lane
                 // (red.global.add.noftz.v4.f16x2 / .bf16x2)
-                for (int rl = warp; rl < rows; rl += kThreads / 32) {
+                for (int rl = warp; rl < rows; rl += kRawThreads / 32) {
                     const Row r = row_of(rl);
                     const long long aLo = (r.lo + 15) & ~15ll, aHi = r.hi & ~15ll;
                     if (r.lo < r.hi)
@@ -603,7 +608,7 @@ __global__ void __launch_bounds__(kThreads, 4) planes_rows_kernel(const BlockArg
                 bulk_commit();
             }
             // ... and the two ragged ends of every run element by element (side 0: head, side 1: tail)
-            for (int t = threadIdx.x; t < 2 * rows; t += kThreads) {
+            for (int t = threadIdx.x; t < 2 * rows; t += kRawThreads) {
                 const Row r = row_of(t >> 1);
                 if (r.lo >= r.hi)
                     continue;
@@ -706,15 +711,24 @@ template <int MODE, typename T> static bool launch_planes_rows(const BlockArgs& 
 {
     const long long rowBytes = (long long)a.bSzW * a.C * (long long)sizeof(T);
     const long long rowPitch = ((rowBytes + 15 + 15) / 16) * 16;   // the run, its misalignment (< 16), rounded up
-    if (rowPitch > kTileBytes)
+    if (rowPitch > kRawTileBytes)
         return false;
     RawPlan p;
     p.rowPitch = (int)rowPitch;
-    int rows = (int)(kTileBytes / rowPitch);
+    int rows = (int)(kRawTileBytes / rowPitch);
     rows = rows < a.bSzH ? rows : a.bSzH;
     rows = rows < kRawMaxRows ? rows : kRawMaxRows;
     const int nChunks = (a.bSzH + rows - 1) / rows;
     p.rowsPerItem = (a.bSzH + nChunks - 1) / nChunks;               // the fewest, nearly equal chunks of rows
+    // ... of a row count that keeps every item's planes on 16-byte boundaries (vector stack accesses), if that fits
+    if (nChunks > 1) {
+        int m = 1;
+        while (((long long)m * a.bSzW * (long long)sizeof(T)) % 16 != 0)
+            m *= 2;
+        const int rounded = ((p.rowsPerItem + m - 1) / m) * m;
+        if (rounded <= rows)
+            p.rowsPerItem = rounded;
+    }
     p.rChunks = FastDiv((uint32_t)((a.bSzH + p.rowsPerItem - 1) / p.rowsPerItem));
     p.blockW = FastDiv((uint32_t)a.bSzW);
     // vector stack accesses when every plane of every item starts on the vector's boundary and holds whole vectors:
@@ -731,7 +745,7 @@ template <int MODE, typename T> static bool launch_planes_rows(const BlockArgs& 
     // channel groups: a warp task is 32 lanes x q pixels x one group.  Fewest rounds of the CTA's warps first, then
     // the fewest tasks (each pays its address arithmetic once); the narrow path keeps a group in registers.
     const int pixGroups = (p.rowsPerItem * a.bSzW + 32 * q - 1) / (32 * q);
-    const int warps = kThreads / 32, maxGroup = q > 1 ? a.C : RawChans<T>::n;
+    const int warps = kRawThreads / 32, maxGroup = q > 1 ? a.C : RawChans<T>::n;
     long long bestCost = -1;
     int bestGroups = 1;
     for (int groups = (a.C + maxGroup - 1) / maxGroup; groups <= a.C; ++groups) {
@@ -748,9 +762,9 @@ template <int MODE, typename T> static bool launch_planes_rows(const BlockArgs& 
     const long long nItems = (long long)a.numActive * p.rChunks.div;
     const bool perItem = a.num_active_dev == nullptr && nItems <= 0x7fffffffll;
     auto go = [&](auto kernel) {
-        const int wave = ctas_per_sm(kernel, kThreads) * sm_count();
+        const int wave = ctas_per_sm(kernel, kRawThreads) * sm_count();
         const unsigned grid = (unsigned)(perItem ? nItems : (nItems < wave ? nItems : wave));
-        launch_pdl(kernel, dim3(grid), dim3(kThreads), 0, stream, a, p);
+        launch_pdl(kernel, dim3(grid), dim3(kRawThreads), 0, stream, a, p);
     };
     if (wide) {
         go(planes_rows_kernel<MODE, T, kQuad>);
@@ -767,8 +781,8 @@ template <int VB, int MODE, typename T>
 static void launch_planes(const BlockArgs& a, cudaStream_t stream)
 {
     // The raw-row kernel takes every shape whose block row fits its tile: measured on [8,512,512,C] at 20 %
-    // against the element-wise kernel below, C = 33 fp32 gather 65 -> 33 us, atomic scatter 70 -> 44 us; C = 100 fp16
-    // gather 93 -> 53 us, atomic scatter 117 -> 92 us.  Option planes=4 keeps the element-wise kernel.
+    // against the element-wise kernel below, C = 33 fp32 gather 65 -> 31 us, atomic scatter 70 -> 43 us; C = 100 fp16
+    // gather 93 -> 49 us, atomic scatter 117 -> 86 us.  Option planes=4 keeps the element-wise kernel.
     if (options().planes != 4 && launch_planes_rows<MODE, T>(a, stream))
         return;
     const int itemsize = (int)sizeof(T);
