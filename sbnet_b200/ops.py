@@ -128,6 +128,8 @@ def _count(bin_counts) -> int:
     if isinstance(bin_counts, torch.Tensor):
         if bin_counts.is_cuda:
             raise ValueError("bin_counts lives in host memory (use the *_dyn functions for a device count)")
+        if bin_counts.numel() == 1:
+            return int(bin_counts.item())       # the usual case, without building a view first
         return int(bin_counts.reshape(-1)[0])
     return int(list(bin_counts)[0]) if not isinstance(bin_counts, int) else int(bin_counts)
 
