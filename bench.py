@@ -476,7 +476,7 @@ def run_ours(args):
         suite["c5_occ30_step"] = {"us": round(ms30 / 20 * 1e3, 2), "blocks": w30.nB, "blocks/s": round(b30 / (ms30 * 1e-3))}
         del w30
         torch.cuda.empty_cache()
-        suite.update(bench_ops.suite_table(torch, dev, steps=20, warmup=5, quiet=True))
+        suite.update(bench_ops.suite_table(torch, dev, steps=20, warmup=5, quiet=True, other_shapes=True))
 
     # ---- reduce over ranks: max time, summed blocks; per-op medians of the slowest rank ----
     med_local = [statistics.median(op_ms[k]) for k in ("reduce_mask", "gather", "scatter")]

@@ -470,9 +470,10 @@ def copy_rows(tb, tm, torch, dev):
     tb.emit("yardstick_torch_copy_1GiB", med, mn, 2 << 30, {})
 
 
-def suite_table(torch, dev, steps=20, warmup=5, quiet=True, extended=False):
-    """All rows of the op-level table as {case: row}.  ``extended`` adds the large-block / odd-channel
-    and copy rows (``--suite ops`` prints them; the benchmark line keeps to the configured cases)."""
+def suite_table(torch, dev, steps=20, warmup=5, quiet=True, extended=False, other_shapes=False):
+    """All rows of the op-level table as {case: row}.  ``other_shapes`` adds the large-block and odd-channel
+    rows (shapes outside the configured cases that run other kernels), ``extended`` those and the copy rows
+    (``--suite ops`` prints them all)."""
     from sbnet_b200 import build
     build.build_library()
     tm = Timer(torch, dev, steps, warmup)
@@ -480,8 +481,9 @@ def suite_table(torch, dev, steps=20, warmup=5, quiet=True, extended=False):
     reduce_mask_rows(tb, tm, torch, dev)
     gather_rows(tb, tm, torch, dev)
     scatter_rows(tb, tm, torch, dev)
-    if extended:
+    if extended or other_shapes:
         large_block_rows(tb, tm, torch, dev)
+    if extended:
         copy_rows(tb, tm, torch, dev)
     del tm
     torch.cuda.empty_cache()
