@@ -308,3 +308,55 @@ def test_device_count_calls_on_general_shapes_loop_over_items(cuda_ops, dtype, C
         assert torch.equal(y1, y2), (add, atomic)
     from sbnet_b200 import lib
     assert lib.wait_timeouts() == 0
+
+
+def _carve(torch, shape, dtype, dev, lead, fill):
+    """A contiguous tensor of ``shape`` that starts ``lead`` elements into a larger buffer (so its address is
+    element-aligned only), and the buffer, pre-filled with ``fill`` as a guard band on both sides."""
+    n = int(np.prod(shape))
+    buf = torch.full((n + lead + 37,), fill, dtype=dtype, device=dev)
+    return buf[lead:lead + n].view(*shape), buf
+
+
+@pytest.mark.parametrize("transpose", [False, True], ids=["rows", "planes"])
+@pytest.mark.parametrize("dtype,C,lead_x,lead_s", [(np.float32, 8, 1, 3), (np.float32, 33, 3, 1), (np.float16, 100, 1, 5),
+                                                   (np.float16, 64, 7, 2), (np.float16, 9, 3, 3)])
+def test_buffers_aligned_to_an_element_only(cuda_ops, dtype, C, lead_x, lead_s, transpose):
+    """Image and stack that start at odd element offsets of their allocations (views into larger buffers): same
+    results as on aligned copies, and nothing written outside the views (guard bands on both sides)."""
+    import torch
+    from sbnet_b200 import ops
+    dev = torch.device("cuda:0")
+    N, H, W = 2, 50, 44
+    bsize, bstride, boffset = (10, 12), (10, 12), (-3, -5)      # blocks do not overlap; they hang over every border
+    g = cfg.geom_for(H, W, bsize, bstride, boffset)
+    idx_h, cnt_h = cfg.random_block_list(N, g.bcount, 0.8, seed=3)
+    nb = int(cnt_h[0])
+    idx, cnt = torch.from_numpy(idx_h).to(dev), torch.from_numpy(cnt_h)
+    tdt = torch.float32 if dtype == np.float32 else torch.float16
+    x_al = torch.from_numpy(cfg.normal((N, H, W, C), 41, dtype)).to(dev)
+    sshape = (nb, C, *bsize) if transpose else (nb, *bsize, C)
+    s_al = torch.from_numpy(cfg.normal(sshape, 42, dtype)).to(dev)
+    x, xbuf = _carve(torch, (N, H, W, C), tdt, dev, lead_x, 77.0)
+    x.copy_(x_al)
+    s, sbuf = _carve(torch, sshape, tdt, dev, lead_s, 55.0)
+    assert x.data_ptr() % 16 != 0 and s.data_ptr() % 16 != 0
+
+    def guards_intact(buf, lead, n, fill):
+        return bool((buf[:lead] == fill).all()) and bool((buf[lead + n:] == fill).all())
+
+    ref = ops.sparse_gather(x_al, cnt, idx, bsize, bstride, boffset, transpose=transpose)
+    ops.sparse_gather(x, cnt, idx, bsize, bstride, boffset, transpose=transpose, out=s)
+    torch.cuda.synchronize()
+    assert torch.equal(s, ref)
+    assert guards_intact(sbuf, lead_s, s.numel(), 55.0)
+    s.copy_(s_al)
+    for add, atomic in ((False, False), (True, False), (True, True)):
+        y_ref = ops.sparse_scatter_var(s_al, cnt, idx, x_al.clone(), bsize, bstride, boffset, add=add, atomic=atomic,
+                                       transpose=transpose)
+        x.copy_(x_al)
+        y = ops.sparse_scatter_var(s, cnt, idx, x, bsize, bstride, boffset, add=add, atomic=atomic, transpose=transpose)
+        torch.cuda.synchronize()
+        assert y.data_ptr() == x.data_ptr()
+        assert torch.equal(y, y_ref), (add, atomic)
+        assert guards_intact(xbuf, lead_x, x.numel(), 77.0), (add, atomic)
