@@ -8,7 +8,9 @@ bit-equal, transposed == transpose of untransposed, scattered outputs bit-equal)
 * sparse_scatter / sparse_scatter_var fp32 atomic add over overlapping 18x18 halos onto [8,512,512,64]
   (order dependent: both results inside the fp64 exact-sum bars, image by image);
 * the sparse bottleneck's block ops on x fp16 [32,400,352,256] at 10 % and 30 % mask occupancy:
-  reduce_mask, transposed gather with its halo rows, non-atomic transposed add.
+  reduce_mask, transposed gather with its halo rows, non-atomic transposed add;
+* pixels that are not 16-byte multiples ([8,512,512,33] fp32, [8,512,512,100] fp16): gather, overwrite,
+  read-add-write, atomic add.
 
 Size-independent properties of the same launches (layout identities, round trips, exact coverage
 counts from atomic adds of ones) ride along.  Tensors of a gigabyte and more are compared on the
@@ -197,3 +199,48 @@ def test_config5_pipeline_whole_launches_against_cpu(cuda_ops, oracle_port, occu
                                transpose=True)
         cov = torch.from_numpy(_coverage(idx_h, nb, gi, N, H, W) > 0).to(DEV)
         assert torch.equal(x[cov], x0[cov] * 2) and torch.equal(x[~cov], x0[~cov])
+
+
+@pytest.mark.parametrize("dtype,C", [(np.float32, 33), (np.float16, 100)], ids=["f32_C33", "f16_C100"])
+def test_pixels_that_are_not_16_byte_multiples_whole_launches_against_cpu(cuda_ops, oracle_port, dtype, C):
+    """[8,512,512,C] with C = 33 (fp32) and C = 100 (fp16) at 20 % of the blocks -- the shapes of the benchmark
+    table's odd-channel rows, which run the raw-row kernel in the plane layout and the narrow-vector kernel in the
+    row layout: gather in both layouts, overwrite and read-add-write of the 16x16 interiors (disjoint blocks), all
+    bit-equal to the CPU checker; atomic add of the 18x18 halos inside the exact-sum bars."""
+    from sbnet_b200 import ops
+    N, H, W = 8, 512, 512
+    g, gi = cfg.halo_geom(H, W), cfg.inner_geom(H, W)
+    xh = cfg.normal((N, H, W, C), 51, dtype)
+    xd = torch.from_numpy(xh).to(DEV)
+    idx_h, cnt_h = cfg.random_block_list(N, g.bcount, 0.20, seed=52)
+    nb = int(cnt_h[0])
+    assert _border_blocks_present(idx_h, nb, g.bcount)
+    idx, cnt = torch.from_numpy(idx_h).to(DEV), torch.from_numpy(cnt_h)
+    oracle_port.set_threads(oracle_port.max_threads())
+    rows = ops.sparse_gather(xd, cnt, idx, g.bsize, g.bstride, g.boffset, transpose=False)
+    planes = ops.sparse_gather(xd, cnt, idx, g.bsize, g.bstride, g.boffset, transpose=True)
+    exp = oracle_port.sparse_gather(xh, cnt_h, idx_h, g.bsize, g.bstride, g.boffset, transpose=True)
+    assert _same_bits(planes, exp)
+    del exp
+    assert torch.equal(planes, rows.permute(0, 3, 1, 2))
+    del rows, planes
+    for tr in (False, True):
+        sshape = (nb, C, 16, 16) if tr else (nb, 16, 16, C)
+        stack_h = cfg.normal(sshape, 53, dtype)
+        stack_d = torch.from_numpy(stack_h).to(DEV)
+        for add in (False, True):
+            y = ops.sparse_scatter_var(stack_d, cnt, idx, xd.clone(), gi.bsize, gi.bstride, gi.boffset, add=add, transpose=tr)
+            exp = oracle_port.sparse_scatter_var(stack_h, cnt_h, idx_h, xh.copy(), gi.bsize, gi.bstride, gi.boffset,
+                                                 add=add, transpose=tr)
+            assert _same_bits(y, exp), (tr, add)
+            del y, exp
+    # overlapping halos, one image's blocks at a time (fp64 work arrays stay small)
+    halo_h = cfg.normal((nb, C, 18, 18), 54, dtype)
+    y = ops.sparse_scatter_var(torch.from_numpy(halo_h).to(DEV), cnt, idx, xd.clone(), g.bsize, g.bstride, g.boffset,
+                               add=True, atomic=True, transpose=True).cpu().numpy()
+    for n in (0, N - 1):
+        sel = np.flatnonzero(idx_h[:nb, 0] == n)
+        sub_idx = idx_h[sel].copy()
+        sub_idx[:, 0] = 0
+        check_atomic_add({"cuda": y[n:n + 1]}, halo_h[sel], [len(sel)], sub_idx, xh[n:n + 1], g.bsize, g.bstride,
+                         g.boffset, True)
