@@ -306,10 +306,13 @@ __global__ void __launch_bounds__(kThreads, 4) planes_kernel(const BlockArgs a, 
 //     overlapping blocks -- and the run's two ragged ends (< 16 bytes each) element by element, so
 //     nothing outside the run is written.  Read-add-write of fp32 (kept apart from the reduction,
 //     which flushes subnormals) loads the rows first, adds in shared memory and stores them.
-// The transposition happens between the row buffers and the stack: a warp takes 32 consecutive pixels
-// x a group of channels at a time, one pixel per lane -- one division and one range test per task,
-// then only constant offsets on the shared-memory side and one plane pitch per channel on the stack
-// side, whose accesses are 32 consecutive elements of one plane.
+// The transposition happens between the row buffers and the stack: a warp takes 32 consecutive runs
+// of Q pixels x a group of channels at a time, one run per lane -- one division and one range test
+// per task, then only constant offsets on the shared-memory side and one plane pitch per channel on
+// the stack side, where a warp access covers 32 consecutive runs of one plane (Q pixels = 16 bytes
+// per lane where the planes are aligned for it, 4 bytes for 16-bit planes on 4-byte boundaries, else
+// one element).  16-bit accumulation reduces with packed red.global.add (.v4.f16x2 / .bf16x2) from
+// the row buffers instead of the engine's reduction, which adds one 16-bit element at a time.
 // A CTA of the raw-row kernel: 128 threads and 24 KB of row buffers, eight per SM.  (256 threads and 44 KB, four per
 // SM, measured 3-8 % slower on C = 33 fp32 and C = 100 fp16: a CTA's load and transposition phases do not overlap,
 // so more and smaller CTAs interleave them better.)
@@ -329,8 +332,9 @@ struct RawPlan {
     int rowPitch;          // bytes of one row buffer: S*C*sizeof(T) + its possible misalignment, a multiple of 16
 };
 
-// Q: consecutive pixels of one channel plane a lane moves at a time on the stack side -- 1 (any shape), or the
-// 16 bytes' worth (4 / 8 pixels as ONE 16-byte access) when every plane of an item starts on a 16-byte boundary.
+// Q: consecutive pixels of one channel plane a lane moves at a time on the stack side -- 1 (any shape), 2 (16-bit
+// planes on 4-byte boundaries), or the 16 bytes' worth (4 / 8 pixels as ONE 16-byte access) when every plane of an
+// item starts on a 16-byte boundary.
 template <int MODE, typename T, int Q>
 __global__ void __launch_bounds__(kRawThreads, 8) planes_rows_kernel(const BlockArgs a, const RawPlan p)
 {
