@@ -516,9 +516,11 @@ def run_ours(args):
 
     global_blocks = None
     if global_counts:
-        per_step = [sum(v) for k, v in sorted(global_counts.items()) if k >= args.warmup]
+        # the timed steps only: a partly filled last ring also reports its unused slots
+        per_step = [sum(v) for k, v in sorted(global_counts.items()) if args.warmup <= k < args.warmup + args.steps]
         global_blocks = per_step[0]
-        assert all(p == global_blocks for p in per_step) and global_blocks * args.steps == int(blocks_all), \
+        assert len(per_step) == args.steps and all(p == global_blocks for p in per_step) \
+            and global_blocks * args.steps == int(blocks_all), \
             (per_step[:4], blocks_all)
     if rank == 0:
         peak, peak_kind = measured_peak()
