@@ -8,7 +8,8 @@
  *
  * Conventions
  *  - All tensor pointers are DEVICE pointers unless a parameter says "host".  The caller owns every
- *    buffer; the library allocates nothing.
+ *    buffer; the library allocates nothing.  A tensor pointer must be a multiple of its element size
+ *    (rejected otherwise); beyond that any alignment is served, wider alignment by faster kernels.
  *  - Geometry is passed as in the reference functors: offsets may be negative, strides may be
  *    smaller (overlap) or larger (gaps) than sizes, blocks may hang over any image border.
  *  - `stream` is a cudaStream_t passed as void*.  Work is enqueued on it; only sbnet_reduce_mask with

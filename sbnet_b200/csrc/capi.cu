@@ -80,6 +80,11 @@ int blocks_call(const char* op, int mode, int dtype, int N, int H, int W, int C,
         return SBNET_OK;
     if (image == nullptr || stack == nullptr || idx == nullptr)
         return reject(SBNET_ERR_INVALID_ARGUMENT, "%s: null tensor pointer", op);
+    // a pointer off its element's boundary would be a misaligned access on the device, not an error code
+    const uintptr_t elem = dtype == SBNET_F32 ? 4 : 2;
+    if (((reinterpret_cast<uintptr_t>(image) | reinterpret_cast<uintptr_t>(stack)) & (elem - 1)) != 0 ||
+        (reinterpret_cast<uintptr_t>(idx) & 1) != 0 || (reinterpret_cast<uintptr_t>(numActiveDev) & 3) != 0)
+        return reject(SBNET_ERR_INVALID_ARGUMENT, "%s: tensor pointer not aligned to its element size", op);
     const long long lim = 1ll << 31;
     const long long blockElems = (long long)bSzH * bSzW * C;
     const long long chunks = ((long long)C * 4 + 127) / 128;
@@ -201,6 +206,8 @@ SBNET_EXPORT int sbnet_reduce_mask(const float* mask, int N, int H, int W, float
         return reject(SBNET_ERR_INVALID_ARGUMENT, "%s: null tensor pointer", op);
     if (reinterpret_cast<uintptr_t>(scratch_dev) & 15)
         return reject(SBNET_ERR_INVALID_ARGUMENT, "%s: scratch_dev must be 16-byte aligned", op);
+    if ((reinterpret_cast<uintptr_t>(mask) & 3) != 0 || (reinterpret_cast<uintptr_t>(active_block_indices) & 1) != 0)
+        return reject(SBNET_ERR_INVALID_ARGUMENT, "%s: tensor pointer not aligned to its element size", op);
 
     cudaStream_t s = (cudaStream_t)stream;
     int32_t* hostDev = nullptr;   // device-visible alias of count_host when it is pinned

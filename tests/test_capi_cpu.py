@@ -66,6 +66,23 @@ def test_null_pointers_and_dtype_are_rejected(handle):
     assert handle.sbnet_copy_tensor(None, None, 16, None) == -1
 
 
+def test_pointers_off_their_element_boundary_are_rejected(handle):
+    """A tensor pointer that is not a multiple of its element size would be a misaligned access on the device;
+    the entry points turn it into an argument error before anything is launched (no GPU needed to see it)."""
+    import ctypes as C
+    P = lambda a: C.c_void_p(a)  # noqa: E731 - made-up addresses, never dereferenced
+    ok = 0x10000
+    for image, stack, idx, dtype in ((ok + 2, ok, ok, 0), (ok, ok + 1, ok, 0), (ok + 1, ok, ok, 1), (ok, ok, ok + 1, 1)):
+        rc = handle.sbnet_sparse_gather(P(image), dtype, 1, 8, 8, 1, P(stack), 0, 0, 2, 2, 2, 2, 1, P(idx), 0, None)
+        assert rc == -1 and b"aligned" in handle.sbnet_last_error(), (image, stack, idx, dtype)
+    rc = handle.sbnet_sparse_scatter(P(ok + 2), 0, 1, 8, 8, 1, P(ok), 0, 0, 2, 2, 2, 2, 1, P(ok), 0, 0, 0, None)
+    assert rc == -1 and b"aligned" in handle.sbnet_last_error()
+    rc = handle.sbnet_reduce_mask(P(ok + 2), 1, 8, 8, 0.5, 0, 0, 0, 2, 2, 2, 2, 4, 4, P(ok), P(ok), None, 0, None)
+    assert rc == -1 and b"aligned" in handle.sbnet_last_error()
+    rc = handle.sbnet_reduce_mask(P(ok), 1, 8, 8, 0.5, 0, 0, 0, 2, 2, 2, 2, 4, 4, P(ok + 1), P(ok), None, 0, None)
+    assert rc == -1 and b"aligned" in handle.sbnet_last_error()
+
+
 def test_missing_library_fails_loudly(monkeypatch):
     from sbnet_b200 import lib
     monkeypatch.setattr(lib, "_lib", None)
