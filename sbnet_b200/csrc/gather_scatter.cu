@@ -11,7 +11,8 @@
 //  * [nB, R, S, C] ("rows"): a block row of S pixels is one contiguous run of S*C elements both in
 //    the NHWC image and in the stack, so the op is a clipped copy of contiguous runs.  Threads move
 //    the widest vector (16/8/4/2 bytes) that divides C*sizeof(T), several per thread in flight, no
-//    shared memory.
+//    shared memory.  Where that vector is only 4 or 2 bytes the raw-row kernel below takes the call:
+//    bulk copies on the image side, 16-byte vectors aligned to the stack on the stack side.
 //  * [nB, C, R, S] ("planes", transpose=true): pixels of a multiple of 16 bytes go to the kernels of
 //    planes_simt.cu / planes_tma.cu.  The kernels here take every other shape.  planes_rows_kernel:
 //    whole block rows travel between the image and shared memory as raw bytes through the TMA
@@ -330,6 +331,8 @@ struct RawPlan {
     int chansPerGroup;     // channels of one group (the last may hold fewer), <= RawChans<T>::n
     int rowsPerItem;       // block rows per work item
     int rowPitch;          // bytes of one row buffer: S*C*sizeof(T) + its possible misalignment, a multiple of 16
+    int rowBytes;          // S*C*sizeof(T)
+    FastDiv stackSlots;    // row layout of the stack: 16-byte vectors a row can touch there
 };
 
 // Q: consecutive pixels of one channel plane a lane moves at a time on the stack side -- 1 (any shape), 2 (16-bit
@@ -381,7 +384,7 @@ __global__ void __launch_bounds__(kRawThreads, 8) planes_rows_kernel(const Block
         const int ph0 = (int)(g00 & 15);
         T* planes = reinterpret_cast<T*>(a.stack) + (long long)ib * a.C * P + (long long)r0 * S;   // [C][P] view at row r0
         const int nPix = rows * S;
-        const int nTasks = ((nPix + 32 * Q - 1) / (32 * Q)) * (int)p.chanGroups.div;
+        const int nTasks = Q == 0 ? 0 : ((nPix + 32 * (Q ? Q : 1) - 1) / (32 * (Q ? Q : 1))) * (int)p.chanGroups.div;
 
         // Row rl of the item: the clipped run [lo, hi) as global addresses and the shared-memory address
         // of the 16-byte vector that holds the run's (unclipped) first byte.
@@ -458,7 +461,113 @@ __global__ void __launch_bounds__(kRawThreads, 8) planes_rows_kernel(const Block
             parity ^= 1u;
         }
 
-        if constexpr (Q > 1) {
+        if constexpr (Q == 0) {
+            // ---- [nB,R,S,C] stack: the item's rows are one contiguous run of the stack, each row a copy of its row
+            // buffer at another alignment.  A thread takes a 16-byte vector of the STACK (aligned there) and the
+            // 4 words -- or, 16-bit elements an odd half away, 8 halves -- of the row buffer that belong to it; the
+            // partial vectors at a row's two ends go element by element.
+            const long long sItem = (long long)reinterpret_cast<uintptr_t>(a.stack)
+                + ((long long)ib * a.bSzH + r0) * (long long)p.rowBytes;
+            const int nSlots = rows * (int)p.stackSlots.div;
+            struct Slot {
+                long long A;          // the vector's address in the stack (16-byte aligned)
+                uint32_t src;         // row-buffer address of the vector's first byte that belongs to the row
+                int lo, hi;           // [lo, hi): the vector's bytes that belong to the row (empty: lo >= hi)
+                int off;              // offset of byte lo inside the row's run
+                bool rowIn;           // the row lies inside the image (gather zero-fills otherwise)
+            };
+            auto slot_of = [&](int k) -> Slot {
+                Slot t;
+                t.A = 0, t.src = 0, t.lo = t.hi = t.off = 0, t.rowIn = false;
+                if (k >= nSlots)
+                    return t;
+                uint32_t rl, q;
+                p.stackSlots.divmod((uint32_t)k, rl, q);
+                const long long sRow = sItem + (long long)rl * p.rowBytes;
+                const int ph2 = (int)(sRow & 15), b0 = 16 * (int)q;
+                t.A = (sRow & ~15ll) + b0;
+                t.lo = max(b0, ph2) - b0, t.hi = max(t.lo, min(b0 + 16, ph2 + p.rowBytes) - b0);
+                t.off = b0 + t.lo - ph2;
+                t.src = tileAddr + rl * (uint32_t)p.rowPitch + (uint32_t)((ph0 + (int)rl * rowMis) & 15) + (uint32_t)t.off;
+                t.rowIn = (unsigned)(h0 + (int)rl) < (unsigned)a.H;
+                return t;
+            };
+            auto read16 = [&](uint32_t src) -> uint4 {   // 16 bytes of a row buffer from an element-aligned address
+                uint4 v;
+                if (SZ == 4 || (src & 3u) == 0) {
+                    v.x = lds32(src), v.y = lds32(src + 4), v.z = lds32(src + 8), v.w = lds32(src + 12);
+                } else {
+                    v.x = lds16(src) | (lds16(src + 2) << 16), v.y = lds16(src + 4) | (lds16(src + 6) << 16);
+                    v.z = lds16(src + 8) | (lds16(src + 10) << 16), v.w = lds16(src + 12) | (lds16(src + 14) << 16);
+                }
+                return v;
+            };
+            if constexpr (MODE == kGather) {
+                for (int k = threadIdx.x; k < nSlots; k += kRawThreads) {
+                    const Slot t = slot_of(k);
+                    if (t.lo >= t.hi)
+                        continue;
+                    const bool allIn = t.rowIn && t.off >= bLo && t.off + (t.hi - t.lo) <= bHi;
+                    if (t.hi - t.lo == 16 && allIn) {
+                        *reinterpret_cast<uint4*>(t.A) = read16(t.src);
+                    } else {   // a row's end, or a stretch outside the image (zeros): element by element
+                        for (int b = t.lo; b < t.hi; b += SZ) {
+                            const int o = t.off + (b - t.lo);
+                            E e = 0;
+                            if (t.rowIn && o >= bLo && o < bHi)
+                                e = SZ == 4 ? (E)lds32(t.src + (uint32_t)(b - t.lo)) : (E)lds16(t.src + (uint32_t)(b - t.lo));
+                            *reinterpret_cast<E*>(t.A + b) = e;
+                        }
+                    }
+                }
+            } else {
+                constexpr int kSU = 4;   // stack vectors in flight per thread
+                for (int k0 = threadIdx.x; k0 < nSlots; k0 += kRawThreads * kSU) {
+                    Slot t[kSU];
+                    uint4 v[kSU];
+#pragma unroll
+                    for (int u = 0; u < kSU; ++u) {
+                        t[u] = slot_of(k0 + u * kRawThreads);
+                        if (t[u].hi - t[u].lo == 16)
+                            v[u] = ld_stream(reinterpret_cast<const uint4*>(t[u].A));
+                    }
+#pragma unroll
+                    for (int u = 0; u < kSU; ++u) {
+                        if (t[u].hi - t[u].lo == 16) {
+                            const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+                            if (SZ == 4 || (t[u].src & 3u) == 0) {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    uint32_t e = w[j];
+                                    if constexpr (MODE == kScatterAdd)   // the buffer holds the image's value
+                                        e = vadd<T>(lds32(t[u].src + 4 * j), e);
+                                    sts32(t[u].src + 4 * j, e);
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    uint32_t e = (j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xffffu);
+                                    if constexpr (MODE == kScatterAdd)
+                                        e = vadd<T>((E)lds16(t[u].src + 2 * j), (E)e);
+                                    sts16(t[u].src + 2 * j, e);
+                                }
+                            }
+                        } else {
+                            for (int b = t[u].lo; b < t[u].hi; b += SZ) {
+                                const uint32_t dst = t[u].src + (uint32_t)(b - t[u].lo);
+                                E e = ld_stream(reinterpret_cast<const E*>(t[u].A + b));
+                                if constexpr (MODE == kScatterAdd)
+                                    e = vadd<T>(SZ == 4 ? (E)lds32(dst) : (E)lds16(dst), e);
+                                if constexpr (SZ == 4)
+                                    sts32(dst, e);
+                                else
+                                    sts16(dst, e);
+                            }
+                        }
+                    }
+                }
+            }
+        } else if constexpr (Q > 1) {
             // ---- vector stack accesses: a lane owns Q consecutive pixels (NW words), the channels of its group in
             // batches of kB
             constexpr int kB = 4, NW = Q * SZ / 4;
@@ -685,9 +794,19 @@ static int pick_vector_bytes(const BlockArgs& a, int itemsize)
     return itemsize;
 }
 
+template <int MODE, typename T> static bool launch_planes_rows(const BlockArgs& a, cudaStream_t stream, bool rowsLayout);
+
 template <int VB, int MODE, typename T>
 static void launch_rows(const BlockArgs& a, cudaStream_t stream)
 {
+    // Vectors of 4 or 2 bytes (pixels that are not 8-byte multiples, or buffers aligned no better): the raw-row
+    // kernel, which moves 16-byte vectors on both sides whatever the pixel size, where a block row fits its tile.
+    // Measured on [8,512,512,C] at 20 %, this kernel -> raw rows: C = 33 fp32 gather 38.9 -> 32.7 us, overwrite
+    // 40.9 -> 30.7 us, atomic add 45.1 -> 45.0 us; C = 33 fp16 (2-byte vectors, one-element reductions) atomic add
+    // 191 -> 38.9 us, overwrite 37.0 -> 20.4 us.  8-byte vectors stay here (C = 100 fp16: 41.0 vs 42.9 us gather,
+    // 57.4 vs 69.7 us atomic add).  Option planes=4 keeps this kernel for every width.
+    if (VB <= 4 && options().planes != 4 && launch_planes_rows<MODE, T>(a, stream, true))
+        return;
     const int itemsize = (int)sizeof(T);
     RowPlan p;
     p.vecsPerPixel = (int)((size_t)a.C * itemsize / VB);
@@ -711,7 +830,7 @@ static void launch_rows(const BlockArgs& a, cudaStream_t stream)
 }
 
 // Whole block rows as raw bytes (planes_rows_kernel) whenever one row's pixels fit the tile.
-template <int MODE, typename T> static bool launch_planes_rows(const BlockArgs& a, cudaStream_t stream)
+template <int MODE, typename T> static bool launch_planes_rows(const BlockArgs& a, cudaStream_t stream, bool rowsLayout)
 {
     const long long rowBytes = (long long)a.bSzW * a.C * (long long)sizeof(T);
     const long long rowPitch = ((rowBytes + 15 + 15) / 16) * 16;   // the run, its misalignment (< 16), rounded up
@@ -719,13 +838,15 @@ template <int MODE, typename T> static bool launch_planes_rows(const BlockArgs& 
         return false;
     RawPlan p;
     p.rowPitch = (int)rowPitch;
+    p.rowBytes = (int)rowBytes;
+    p.stackSlots = FastDiv((uint32_t)((rowBytes + 15 + 15) / 16));
     int rows = (int)(kRawTileBytes / rowPitch);
     rows = rows < a.bSzH ? rows : a.bSzH;
     rows = rows < kRawMaxRows ? rows : kRawMaxRows;
     const int nChunks = (a.bSzH + rows - 1) / rows;
     p.rowsPerItem = (a.bSzH + nChunks - 1) / nChunks;               // the fewest, nearly equal chunks of rows
     // ... of a row count that keeps every item's planes on 16-byte boundaries (vector stack accesses), if that fits
-    if (nChunks > 1) {
+    if (nChunks > 1 && !rowsLayout) {
         int m = 1;
         while (((long long)m * a.bSzW * (long long)sizeof(T)) % 16 != 0)
             m *= 2;
@@ -770,7 +891,9 @@ template <int MODE, typename T> static bool launch_planes_rows(const BlockArgs& 
         const unsigned grid = (unsigned)(perItem ? nItems : (nItems < wave ? nItems : wave));
         launch_pdl(kernel, dim3(grid), dim3(kRawThreads), 0, stream, a, p);
     };
-    if (wide) {
+    if (rowsLayout) {
+        go(planes_rows_kernel<MODE, T, 0>);
+    } else if (wide) {
         go(planes_rows_kernel<MODE, T, kQuad>);
     } else if (q == 2) {
         if constexpr (sizeof(T) == 2)
@@ -787,7 +910,7 @@ static void launch_planes(const BlockArgs& a, cudaStream_t stream)
     // The raw-row kernel takes every shape whose block row fits its tile: measured on [8,512,512,C] at 20 %
     // against the element-wise kernel below, C = 33 fp32 gather 65 -> 31 us, atomic scatter 70 -> 43 us; C = 100 fp16
     // gather 93 -> 49 us, atomic scatter 117 -> 86 us.  Option planes=4 keeps the element-wise kernel.
-    if (options().planes != 4 && launch_planes_rows<MODE, T>(a, stream))
+    if (options().planes != 4 && launch_planes_rows<MODE, T>(a, stream, false))
         return;
     const int itemsize = (int)sizeof(T);
     PlanePlan p;

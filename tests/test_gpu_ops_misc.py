@@ -14,15 +14,15 @@ from atomic_check import check_atomic_add
 # channel counts chosen to hit every vector width: C*sizeof(T) in {2,4,6,8,12,14,16,30,48,...}
 @pytest.mark.parametrize("dtype", [np.float32, np.float16], ids=["f32", "f16"])
 @pytest.mark.parametrize("C", [1, 2, 3, 4, 6, 7, 8, 15, 24, 40])
-@pytest.mark.parametrize("transpose", [False, True, "elementwise", "raw_rows_narrow"],
-                         ids=["rows", "planes", "planes_elementwise", "planes_raw_rows_narrow"])
+@pytest.mark.parametrize("transpose", [False, "rows_vectors", True, "elementwise", "raw_rows_narrow"],
+                         ids=["rows", "rows_vector_kernel", "planes", "planes_elementwise", "planes_raw_rows_narrow"])
 def test_mode_matrix(cuda_ops, oracle_port, dtype, C, transpose):
-    """``planes``: pixels that are not 16-byte multiples run the raw-row kernel of the general path;
-    ``planes_elementwise`` sends the same calls through its element-wise kernel, ``planes_raw_rows_narrow``
-    through the raw-row kernel with element-wide stack accesses."""
+    """``rows`` / ``planes``: pixels that are not 8- / 16-byte multiples run the raw-row kernel of the general
+    path; ``rows_vector_kernel`` and ``planes_elementwise`` send the same calls through the kernels it replaced,
+    ``planes_raw_rows_narrow`` through the raw-row kernel with element-wide stack accesses."""
     from conftest import library_options
-    with library_options(planes={"elementwise": 4, "raw_rows_narrow": 6}.get(transpose, 0)):
-        _mode_matrix(cuda_ops, oracle_port, dtype, C, bool(transpose))
+    with library_options(planes={"rows_vectors": 4, "elementwise": 4, "raw_rows_narrow": 6}.get(transpose, 0)):
+        _mode_matrix(cuda_ops, oracle_port, dtype, C, transpose not in (False, "rows_vectors"))
 
 
 def _mode_matrix(cuda_ops, oracle_port, dtype, C, transpose):
