@@ -274,8 +274,9 @@ def test_shared_memory_limit_is_consistent_across_host_threads(cuda_ops):
         assert torch.equal(gather("big"), ref_big)          # failed with "invalid argument" when limits were cached per thread
 
 
+@pytest.mark.parametrize("transpose", [True, False], ids=["planes", "rows"])
 @pytest.mark.parametrize("dtype,C", [(np.float32, 5), (np.float16, 6), (np.float16, 7)])
-def test_device_count_calls_on_general_shapes_loop_over_items(cuda_ops, dtype, C):
+def test_device_count_calls_on_general_shapes_loop_over_items(cuda_ops, dtype, C, transpose):
     """Pixels that are not a multiple of 16 bytes with the block count on the device: the raw-row kernel runs as
     one resident wave whose CTAs each take several blocks in turn (4,000 blocks on about 1,200 CTAs), reusing
     their row buffers and their barrier.  Every mode must give what the host-count call (one CTA per block) gives."""
@@ -291,19 +292,19 @@ def test_device_count_calls_on_general_shapes_loop_over_items(cuda_ops, dtype, C
     idx, cnt = torch.from_numpy(idx_h).to(dev), torch.from_numpy(cnt_h)
     cnt_dev = cnt.to(dev)
     x = torch.from_numpy(cfg.normal((N, H, W, C), 31, dtype)).to(dev)
-    ref = ops.sparse_gather(x, cnt, idx, bsize, bstride, boffset, transpose=True)
-    out = torch.full((max_blocks, C, 6, 6), -3.0, dtype=x.dtype, device=dev)
-    ops.sparse_gather_dyn(x, cnt_dev, max_blocks, idx, bsize, bstride, boffset, transpose=True, out=out)
+    ref = ops.sparse_gather(x, cnt, idx, bsize, bstride, boffset, transpose=transpose)
+    out = torch.full((max_blocks, C, 6, 6) if transpose else (max_blocks, 6, 6, C), -3.0, dtype=x.dtype, device=dev)
+    ops.sparse_gather_dyn(x, cnt_dev, max_blocks, idx, bsize, bstride, boffset, transpose=transpose, out=out)
     torch.cuda.synchronize()
     assert torch.equal(out[:nb], ref) and bool((out[nb:] == -3.0).all())
     base = torch.from_numpy(cfg.normal((N, H, W, C), 32, dtype)).to(dev)
     src = torch.from_numpy(cfg.normal(tuple(ref.shape), 33, dtype)).to(dev)
-    full = torch.cat([src, torch.full((max_blocks - nb, C, 6, 6), float("nan"), dtype=x.dtype, device=dev)])
+    full = torch.cat([src, torch.full((max_blocks - nb,) + tuple(ref.shape[1:]), float("nan"), dtype=x.dtype, device=dev)])
     for add, atomic in ((False, False), (True, False), (True, True)):      # the blocks do not overlap: all bit-exact
         y1 = ops.sparse_scatter_var_dyn(full, cnt_dev, max_blocks, idx, base.clone(), bsize, bstride, boffset,
-                                        add=add, atomic=atomic, transpose=True)
+                                        add=add, atomic=atomic, transpose=transpose)
         y2 = ops.sparse_scatter_var(src, cnt, idx, base.clone(), bsize, bstride, boffset, add=add, atomic=atomic,
-                                    transpose=True)
+                                    transpose=transpose)
         torch.cuda.synchronize()
         assert torch.equal(y1, y2), (add, atomic)
     from sbnet_b200 import lib
