@@ -193,7 +193,8 @@ int sbnet_wait_timeouts(unsigned int* count);
  * brackets; afterwards only these calls change them.  Not synchronised with launches in flight on other
  * threads.  Unknown names are rejected with SBNET_ERR_INVALID_ARGUMENT.
  *   "planes"          0 default dispatch, 1 persistent TMA pipeline, 2 tile CTAs with plain loads [SBNET_PLANES=tma|tile],
- *                     3 tile CTAs fed by TMA whatever the launch size, 4 general shapes on the element-wise kernel,
+ *                     3 tile CTAs fed by TMA whatever the launch size, 4 general shapes on the element-wise / narrow-vector
+ *                     kernels instead of the raw-row kernel,
  *                     6 general shapes on the raw-row kernel with element-wide accesses on the stack side
  *   "disable_tma"     1: plane layouts run the general kernel only                               [SBNET_DISABLE_TMA]
  *   "tile_blocks"     > 0: small blocks sharing one tile, whatever the launch size               [SBNET_TILE_BLOCKS]

@@ -9,7 +9,8 @@ namespace sbnet {
 struct Options {
     int planes;        // plane-layout dispatch: 0 default, 1 persistent TMA pipeline, 2 tile CTAs with plain loads
                        //   (SBNET_PLANES=tma|tile), 3 tile CTAs fed by TMA whatever the launch size,
-                       //   4 general shapes run the element-wise kernel instead of the raw-row kernel,
+                       //   4 general shapes run the element-wise (planes) / narrow-vector (rows) kernels instead of
+                       //   the raw-row kernel,
                        //   6 the raw-row kernel with element-wide (never vector) accesses on the stack side
     int disableTma;    // 1: plane layouts run the general kernel only (SBNET_DISABLE_TMA=1)
     int tileBlocks;    // > 0: blocks per shared tile regardless of the launch size (SBNET_TILE_BLOCKS)
