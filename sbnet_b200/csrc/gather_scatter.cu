@@ -615,6 +615,8 @@ __global__ void __launch_bounds__(kRawThreads, 8) planes_rows_kernel(const Block
                             if (u0 + u < nc) {
                                 if constexpr (NW == 4)
                                     g[u * planeVecs] = make_uint4(w[u][0], w[u][1], w[u][2], w[u][3]);
+                                else if constexpr (NW == 2)
+                                    g[u * planeVecs] = make_uint2(w[u][0], w[u][1]);
                                 else
                                     g[u * planeVecs] = w[u][0];
                             }
@@ -626,6 +628,8 @@ __global__ void __launch_bounds__(kRawThreads, 8) planes_rows_kernel(const Block
                                 const V v = ld_stream(g + u * planeVecs);
                                 if constexpr (NW == 4)
                                     w[u][0] = v.x, w[u][1] = v.y, w[u][2] = v.z, w[u][3] = v.w;
+                                else if constexpr (NW == 2)
+                                    w[u][0] = v.x, w[u][1] = v.y;
                                 else
                                     w[u][0] = v;
                             }
@@ -857,7 +861,7 @@ template <int MODE, typename T> static bool launch_planes_rows(const BlockArgs& 
     p.rChunks = FastDiv((uint32_t)((a.bSzH + p.rowsPerItem - 1) / p.rowsPerItem));
     p.blockW = FastDiv((uint32_t)a.bSzW);
     // vector stack accesses when every plane of every item starts on the vector's boundary and holds whole vectors:
-    // 16 bytes, else (16-bit elements) 4 bytes
+    // 16 bytes, else (16-bit elements) 8 or 4 bytes
     constexpr int kQuad = 16 / (int)sizeof(T);
     const long long planeBytes = (long long)a.bSzH * a.bSzW * (long long)sizeof(T);
     const long long itemBytes = (long long)p.rowsPerItem * a.bSzW * (long long)sizeof(T);
@@ -866,7 +870,10 @@ template <int MODE, typename T> static bool launch_planes_rows(const BlockArgs& 
             && (p.rChunks.div == 1 || itemBytes % vb == 0) && options().planes != 6;
     };
     const bool wide = fits(16);
-    const int q = wide ? kQuad : (sizeof(T) == 2 && fits(4) ? 2 : 1);
+    // (8-byte vectors for the scatter modes only: measured on C = 100 fp16 18x18 blocks against 4-byte vectors, atomic
+    // scatter 86 -> 72 us, but gather 49 -> 53 us -- four pixel runs of 200 bytes apart per lane fall on four banks)
+    const int q = wide ? kQuad
+                       : (sizeof(T) == 2 && MODE != kGather && fits(8) ? 4 : (sizeof(T) == 2 && fits(4) ? 2 : 1));
     // channel groups: a warp task is 32 lanes x q pixels x one group.  Fewest rounds of the CTA's warps first, then
     // the fewest tasks (each pays its address arithmetic once); the narrow path keeps a group in registers.
     const int pixGroups = (p.rowsPerItem * a.bSzW + 32 * q - 1) / (32 * q);
@@ -895,6 +902,9 @@ template <int MODE, typename T> static bool launch_planes_rows(const BlockArgs& 
         go(planes_rows_kernel<MODE, T, 0>);
     } else if (wide) {
         go(planes_rows_kernel<MODE, T, kQuad>);
+    } else if (q == 4) {
+        if constexpr (sizeof(T) == 2)
+            go(planes_rows_kernel<MODE, T, 4>);
     } else if (q == 2) {
         if constexpr (sizeof(T) == 2)
             go(planes_rows_kernel<MODE, T, 2>);
