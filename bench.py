@@ -404,8 +404,19 @@ def run_ours(args):
         build.build_library()
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
-        dist.barrier()
+        # the communicator's banner ("NCCL version ...") goes to the process's stdout, which is to carry the one
+        # JSON line and nothing else: file descriptor 1 points at stderr while the communicator comes up
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=dev)
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
     lib.load()
 
     H, W, C = args.height, args.width, args.channels
